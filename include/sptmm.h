@@ -1,0 +1,156 @@
+/*
+ * sptmm.h -- C ABI of the B200 (sm_100a) ternary sparse matmul library.
+ *
+ * Computes C = X * W for W in {-1,0,+1}^(K x N) stored as per-column sorted row-index lists
+ * (one list for the +1 rows, one for the -1 rows) with add/subtract-only gathers.
+ * It replaces, for that one path, the reference program Ogiwara-CostlierRain464/SpTMM
+ * (a single main.cu); each entry point cites the reference lines it stands in for.
+ *
+ * Conventions
+ *  - every function returns 0 on success or a negative sptmm_status; sptmm_last_error()
+ *    gives the message of the calling thread's last failure.  Nothing here calls exit/abort.
+ *  - "device pointer" = memory of the CUDA device current at the call; `stream` is a
+ *    cudaStream_t passed as void* (NULL = default stream, which is what the reference uses,
+ *    main.cu:1861).  Launches are asynchronous unless stated otherwise.
+ *  - X is M x K, C is M x N.  Row-major unless a layout flag says otherwise
+ *    (reference "rcr" build, script/make_rcr.sh:6).
+ */
+#ifndef SPTMM_H
+#define SPTMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum sptmm_status {
+    SPTMM_OK = 0,
+    SPTMM_ERR_INVALID = -1,      /* bad argument / shape constraint violated              */
+    SPTMM_ERR_CUDA = -2,         /* a CUDA runtime call failed                            */
+    SPTMM_ERR_UNSUPPORTED = -3,  /* valid request this build cannot serve                 */
+    SPTMM_ERR_LOSSY = -4,        /* encoding cannot represent the matrix exactly          */
+    SPTMM_ERR_NOMEM = -5,
+    SPTMM_ERR_STATE = -6         /* e.g. weights not uploaded to the current device       */
+} sptmm_status;
+
+typedef enum sptmm_format {
+    /* reference layout W_map_{8,16,32}_div (main.cu:345-373): u16, [chunk][column][split]   */
+    SPTMM_FMT_U16_DIV = 1,
+    /* reference layout W_map_delta2_div256 (main.cu:376-413): u8 gaps, [block][column][256] */
+    SPTMM_FMT_DELTA_DIV256 = 2,
+    /* native: u16, 256-entry blocks pre-interleaved for 16-byte-per-lane loads              */
+    SPTMM_FMT_U16_V256 = 3,
+    /* native: per-lane u16 base + 14 u8 lane-strided gaps per 16 bytes (480 entries/512 B)  */
+    SPTMM_FMT_DELTA_LANE = 4,
+    /* comparator: 2-bit codes, 16 rows per 32-bit word (bitnet_kernels.cuh:52-72)           */
+    SPTMM_FMT_I2S = 5
+} sptmm_format;
+
+typedef enum sptmm_dtype { SPTMM_I8 = 0, SPTMM_F16 = 1, SPTMM_F32 = 2 } sptmm_dtype;
+
+/* bit flags for the `flags` argument of the launch functions */
+enum {
+    SPTMM_X_COLMAJOR = 1,   /* X(m,k) at k*M+m  (reference "ccc" build, script/make_ccc.sh:6) */
+    SPTMM_C_COLMAJOR = 2,   /* C(m,n) at n*M+m                                               */
+    SPTMM_LAUNCH_PDL = 4    /* programmatic dependent launch: this call's weight prefetch may
+                               overlap the tail of the previous kernel in the stream; X is read
+                               and C written only after that kernel has completed             */
+};
+
+typedef struct sptmm_weights sptmm_weights;   /* opaque, host-owned encoded matrix */
+
+typedef struct sptmm_weights_info {
+    uint32_t K, N;
+    uint32_t format;        /* sptmm_format                                                  */
+    uint32_t split;         /* U16_DIV: 8/16/32; DELTA_LANE: lane stride; else 0             */
+    uint32_t S;             /* 2 x padded per-sign list capacity (reference -S) where uniform */
+    uint32_t max_count;     /* longest single-sign list                                      */
+    uint64_t nnz;           /* non-zeros of W                                                */
+    uint64_t stream_bytes;  /* bytes of encoded arrays one matmul reads (roofline numerator) */
+    uint64_t lossy_entries; /* DELTA_DIV256: entries whose 8-bit store lost information      */
+    uint32_t n_arrays;      /* number of encoded arrays, see sptmm_weights_array             */
+    int32_t  device;        /* device the arrays are uploaded to, -1 if none                 */
+} sptmm_weights_info;
+
+const char *sptmm_last_error(void);
+int sptmm_version(void);
+
+/* ---- weight generation (host).  W is column-major K x N int8 (W_MAJOR = MAJOR_COL).        */
+
+/* Reference generator, bit-exact: S/2 entries -1 and S/2 entries +1 per column, Fisher-Yates
+ * with xorshift32 seeded 0xCAFEBABE ^ column (main.cu:248-265, macro.cuh:69-76). */
+int sptmm_gen_ternary_fixed(uint32_t K, uint32_t N, uint32_t S, int8_t *W);
+
+/* No counterpart in the reference: i.i.d. entries, P(0)=p_zero, P(+1)=P(-1), splitmix64 per column. */
+int sptmm_gen_ternary_iid(uint32_t K, uint32_t N, double p_zero, uint64_t seed, int8_t *W);
+
+/* ---- encoding (host).  Replaces the device-side encoder prepareW_map (main.cu:202-489).    */
+
+/* S = 0 derives the per-sign capacity from the longest list (rounded up as the format needs);
+ * S > 0 fixes it at S/2 as the reference's -S flag does and fails if a column has more.
+ * `split`: U16_DIV 8|16|32 (reference -row_split3_small values, main.cu:998-1059);
+ *          DELTA_LANE 0 = choose the widest lane stride whose gaps fit 8 bits; others ignore it. */
+int sptmm_encode(const int8_t *W, uint32_t K, uint32_t N, uint32_t format, uint32_t split,
+                 uint32_t S, sptmm_weights **out);
+int sptmm_weights_info_get(const sptmm_weights *w, sptmm_weights_info *info);
+/* Encoded array `i` on the host (byte-for-byte what is uploaded).  For U16_DIV: 0 = +1 lists,
+ * 1 = -1 lists; DELTA_DIV256 likewise.  Native formats: 0 = payload, then metadata arrays. */
+int sptmm_weights_array(const sptmm_weights *w, uint32_t i, const void **host_ptr,
+                        const void **device_ptr, uint64_t *bytes, const char **name);
+/* Copy the arrays to the current device (one cudaMalloc per array; synchronous). */
+int sptmm_weights_upload(sptmm_weights *w);
+/* Upload `copies` independent replicas (for cold-cache timing); replica r is selected per call. */
+int sptmm_weights_upload_replicas(sptmm_weights *w, uint32_t copies);
+int sptmm_weights_free(sptmm_weights *w);
+
+/* ---- the matmul ---------------------------------------------------------------------------- */
+
+/* C = X*W with uploaded weights of any format.  X: device, `dtype` elements; C: device, int32
+ * for SPTMM_I8 (exact), float for F16/F32 (fp32 accumulation).  `replica` picks the weight copy
+ * (0 unless upload_replicas was used).  No allocation, no synchronisation on this path.
+ * Stands in for the launches of main.cu:993-1460 / 1463-1846 / 1864-1961. */
+int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M, void *C,
+               uint32_t flags, uint32_t replica, void *stream);
+
+/* Same, but X and C are HOST buffers: copies X in, runs, copies C out, waits.  Uses pinned
+ * staging owned by the handle (not re-entrant per handle). */
+int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
+                    uint32_t flags);
+
+/* Raw-pointer forms with the reference's kernel argument convention (X, W_pos, W_neg, C), for a
+ * caller that built the reference layouts itself.
+ * rowWiseSplit3Small4<M,K,N,S,SPLIT><<<...>>>(X, W_map_SPLIT_div, W_map_negative_SPLIT_div, C)
+ * (main.cu:556-594, launches main.cu:1000-1448). */
+int sptmm_row_split3_small(const int8_t *X, const uint16_t *W_pos_div, const uint16_t *W_neg_div,
+                           int32_t *C, uint32_t M, uint32_t K, uint32_t N, uint32_t S,
+                           uint32_t split, void *stream);
+/* rowWiseSplit2DeltaSmallAsync2/3<M,K,N,S,32><<<...>>>(X, W_map_delta2_div256,
+ * W_map_negative_delta2_div256, C) (main.cu:599-764, launches main.cu:1468-1830).  Indices are
+ * rebuilt modulo 65536 exactly as the reference does; a rebuilt index >= K contributes 0. */
+int sptmm_row_split_delta2(const int8_t *X, const uint8_t *W_pos_delta, const uint8_t *W_neg_delta,
+                           int32_t *C, uint32_t M, uint32_t K, uint32_t N, uint32_t S,
+                           uint32_t split, void *stream);
+
+/* ---- comparators --------------------------------------------------------------------------- */
+
+/* Dense int8 x int8 -> int32 through cublasGemmEx, column-major operands as main.cu:856-867
+ * (X: M x K lda=M, W: K x N ldb=K, C: M x N ldc=M).  W_dense is a device pointer the caller
+ * filled (the reference passes a null W, main.cu:837,863).  Reported reference only. */
+int sptmm_dense_cublas_gemm(const int8_t *X_colmajor, const int8_t *W_dense, int32_t *C_colmajor,
+                            uint32_t M, uint32_t K, uint32_t N, void *stream);
+
+/* ---- small device helpers so a C caller needs no CUDA headers ------------------------------ */
+int sptmm_device_count(int *count);
+int sptmm_set_device(int device);
+int sptmm_dev_alloc(void **ptr, uint64_t bytes);
+int sptmm_dev_free(void *ptr);
+int sptmm_memcpy_h2d(void *dst, const void *src, uint64_t bytes);
+int sptmm_memcpy_d2h(void *dst, const void *src, uint64_t bytes);
+int sptmm_device_sync(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPTMM_H */

@@ -1,0 +1,199 @@
+"""sptmm_b200 -- thin Python binding over libsptmm.so (the C ABI in include/sptmm.h).
+
+The library is the product; this module only marshals arguments with ctypes.  There is no
+Python or CPU fallback: importing without a built library raises, and every compute call goes
+through the C ABI into the CUDA kernels.
+
+Names follow the reference program's operator surface (Ogiwara-CostlierRain464/SpTMM main.cu):
+``row_split3_small`` / ``row_split_delta2`` are its two SpTMM modes (flags at main.cu:39-40),
+``i2s`` its 2-bit comparator (main.cu:41).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libsptmm.so")
+
+FMT_U16_DIV, FMT_DELTA_DIV256, FMT_U16_V256, FMT_DELTA_LANE, FMT_I2S = 1, 2, 3, 4, 5
+I8, F16, F32 = 0, 1, 2
+X_COLMAJOR, C_COLMAJOR, LAUNCH_PDL = 1, 2, 4
+
+_NP_DTYPE = {I8: np.int8, F16: np.float16, F32: np.float32}
+_OUT_DTYPE = {I8: np.int32, F16: np.float32, F32: np.float32}
+
+
+class SptmmError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__("sptmm error %d: %s" % (code, message))
+        self.code = code
+        self.message = message
+
+
+class WeightsInfo(C.Structure):
+    _fields_ = [("K", C.c_uint32), ("N", C.c_uint32), ("format", C.c_uint32), ("split", C.c_uint32),
+                ("S", C.c_uint32), ("max_count", C.c_uint32), ("nnz", C.c_uint64),
+                ("stream_bytes", C.c_uint64), ("lossy_entries", C.c_uint64), ("n_arrays", C.c_uint32),
+                ("device", C.c_int32)]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("libsptmm.so is not built: run `python -m sptmm_b200.build` (needs nvcc)")
+    lib = C.CDLL(LIB_PATH)
+    u32, u64, vp, i32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int
+    sigs = {
+        "sptmm_last_error": (C.c_char_p, []),
+        "sptmm_version": (i32, []),
+        "sptmm_gen_ternary_fixed": (i32, [u32, u32, u32, vp]),
+        "sptmm_gen_ternary_iid": (i32, [u32, u32, C.c_double, u64, vp]),
+        "sptmm_encode": (i32, [vp, u32, u32, u32, u32, u32, C.POINTER(vp)]),
+        "sptmm_weights_info_get": (i32, [vp, C.POINTER(WeightsInfo)]),
+        "sptmm_weights_array": (i32, [vp, u32, C.POINTER(vp), C.POINTER(vp), C.POINTER(u64), C.POINTER(C.c_char_p)]),
+        "sptmm_weights_upload": (i32, [vp]),
+        "sptmm_weights_upload_replicas": (i32, [vp, u32]),
+        "sptmm_weights_free": (i32, [vp]),
+        "sptmm_gemv": (i32, [vp, vp, u32, u32, vp, u32, u32, vp]),
+        "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32]),
+        "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
+        "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
+        "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
+        "sptmm_device_count": (i32, [C.POINTER(C.c_int)]),
+        "sptmm_set_device": (i32, [C.c_int]),
+        "sptmm_dev_alloc": (i32, [C.POINTER(vp), u64]),
+        "sptmm_dev_free": (i32, [vp]),
+        "sptmm_memcpy_h2d": (i32, [vp, vp, u64]),
+        "sptmm_memcpy_d2h": (i32, [vp, vp, u64]),
+        "sptmm_device_sync": (i32, []),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)          # AttributeError if the header and the library disagree
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
+           "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
+           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_host",
+           "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
+           "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
+           "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise SptmmError(rc, lib.sptmm_last_error().decode("utf-8", "replace"))
+
+
+def _ptr(x) -> int:
+    """Address of a numpy array (host), a torch tensor (host or device) or a raw integer."""
+    if isinstance(x, (int, np.integer)):
+        return int(x)
+    if isinstance(x, np.ndarray):
+        return x.ctypes.data
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    raise TypeError("expected numpy array, torch tensor or address, got %r" % type(x))
+
+
+def device_count() -> int:
+    n = C.c_int(0)
+    rc = lib.sptmm_device_count(C.byref(n))
+    return n.value if rc == 0 else 0
+
+
+def gen_ternary_fixed(K: int, N: int, S: int) -> np.ndarray:
+    """Reference generator (main.cu:248-265): returns W as int8 array of shape (N, K), i.e.
+    column-major K x N -- W[c] is column c."""
+    W = np.empty((N, K), dtype=np.int8)
+    check(lib.sptmm_gen_ternary_fixed(K, N, S, W.ctypes.data))
+    return W
+
+
+def gen_ternary_iid(K: int, N: int, p_zero: float, seed: int) -> np.ndarray:
+    W = np.empty((N, K), dtype=np.int8)
+    check(lib.sptmm_gen_ternary_iid(K, N, float(p_zero), int(seed), W.ctypes.data))
+    return W
+
+
+class Weights:
+    """An encoded ternary matrix (host-owned handle; optionally uploaded to the current device)."""
+
+    def __init__(self, W_colmajor: np.ndarray, fmt: int = FMT_U16_V256, split: int = 32, S: int = 0):
+        W = np.ascontiguousarray(W_colmajor, dtype=np.int8)
+        if W.ndim != 2:
+            raise ValueError("W must be 2-D with shape (N, K): one row per column of the K x N matrix")
+        N, K = W.shape
+        h = C.c_void_p()
+        check(lib.sptmm_encode(W.ctypes.data, K, N, fmt, split, S, C.byref(h)))
+        self._h = h
+        self.info = self._info()
+
+    def _info(self) -> WeightsInfo:
+        info = WeightsInfo()
+        check(lib.sptmm_weights_info_get(self._h, C.byref(info)))
+        return info
+
+    @property
+    def K(self) -> int: return self.info.K
+    @property
+    def N(self) -> int: return self.info.N
+    @property
+    def stream_bytes(self) -> int: return self.info.stream_bytes
+
+    def array(self, i: int) -> tuple[str, np.ndarray, Optional[int]]:
+        """(name, host bytes as uint8 array copy, device address of replica 0 or None)."""
+        hp, dp, nb, name = C.c_void_p(), C.c_void_p(), C.c_uint64(), C.c_char_p()
+        check(lib.sptmm_weights_array(self._h, i, C.byref(hp), C.byref(dp), C.byref(nb), C.byref(name)))
+        buf = (C.c_uint8 * nb.value).from_address(hp.value) if nb.value else (C.c_uint8 * 0)()
+        return name.value.decode(), np.frombuffer(buf, dtype=np.uint8).copy(), dp.value
+
+    def upload(self, replicas: int = 1) -> "Weights":
+        check(lib.sptmm_weights_upload_replicas(self._h, replicas))
+        self.info = self._info()
+        return self
+
+    def gemv(self, X, M: int, out, dtype: int = I8, flags: int = 0, replica: int = 0, stream: int = 0) -> None:
+        """C = X*W on the device; X and out are device tensors (or addresses)."""
+        check(lib.sptmm_gemv(self._h, _ptr(X), dtype, M, _ptr(out), flags, replica, stream))
+
+    def gemv_host(self, X: np.ndarray, dtype: int = I8, flags: int = 0) -> np.ndarray:
+        """Host-buffer call: copies X to the device, runs, copies C back."""
+        X = np.ascontiguousarray(X, dtype=_NP_DTYPE[dtype])
+        M = X.shape[0] if X.ndim == 2 else 1
+        if flags & X_COLMAJOR:
+            M = X.shape[1]
+        out = np.empty((self.N, M) if flags & C_COLMAJOR else (M, self.N), dtype=_OUT_DTYPE[dtype])
+        check(lib.sptmm_gemv_host(self._h, X.ctypes.data, dtype, M, out.ctypes.data, flags))
+        return out
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            lib.sptmm_weights_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def row_split3_small(X, W_pos_div, W_neg_div, out, M: int, K: int, N: int, S: int, split: int, stream: int = 0) -> None:
+    """Raw-pointer form of the reference's -row_split3_small launch (main.cu:556-594)."""
+    check(lib.sptmm_row_split3_small(_ptr(X), _ptr(W_pos_div), _ptr(W_neg_div), _ptr(out), M, K, N, S, split, stream))
+
+
+def row_split_delta2(X, W_pos_delta, W_neg_delta, out, M: int, K: int, N: int, S: int, split: int = 32, stream: int = 0) -> None:
+    """Raw-pointer form of the reference's -row_split_delta2 launch (main.cu:599-764)."""
+    check(lib.sptmm_row_split_delta2(_ptr(X), _ptr(W_pos_delta), _ptr(W_neg_delta), _ptr(out), M, K, N, S, split, stream))
+
+
+def dense_cublas_gemm(X_colmajor, W_dense, out_colmajor, M: int, K: int, N: int, stream: int = 0) -> None:
+    check(lib.sptmm_dense_cublas_gemm(_ptr(X_colmajor), _ptr(W_dense), _ptr(out_colmajor), M, K, N, stream))

@@ -1,0 +1,245 @@
+// device_api.cu -- the C ABI's device side: upload, launch dispatch, host-buffer convenience
+// call, raw-pointer entry points and small helpers.
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "device_common.cuh"
+
+namespace sptmm {
+
+const Tune &tune()
+{
+    static Tune t = [] {
+        Tune v{1, 512, 8, 0};
+        const char *s = getenv("SPTMM_TUNE");
+        if (s) {
+            std::string str(s);
+            size_t pos = 0;
+            while (pos < str.size()) {
+                size_t end = str.find(',', pos);
+                if (end == std::string::npos) end = str.size();
+                std::string kv = str.substr(pos, end - pos);
+                size_t eq = kv.find('=');
+                if (eq != std::string::npos) {
+                    std::string k = kv.substr(0, eq);
+                    int val = atoi(kv.c_str() + eq + 1);
+                    if (k == "ctas_per_sm" && val >= 1 && val <= 8) v.ctas_per_sm = val;
+                    else if (k == "threads" && val >= 32 && val <= 512 && val % 32 == 0) v.threads = val;
+                    else if (k == "prefetch" && val >= 1 && val <= 16) v.prefetch = val;
+                    else if (k == "evict_first") v.evict_first = val != 0;
+                }
+                pos = end + 1;
+            }
+        }
+        return v;
+    }();
+    return t;
+}
+
+static void free_device_side(sptmm_weights *w)
+{
+    if (w->device >= 0) {
+        int cur = 0;
+        cudaGetDevice(&cur);
+        cudaSetDevice(w->device);
+        for (auto &rep : w->dev) for (void *p : rep) if (p) cudaFree(p);
+        if (w->plan.d_ctas) cudaFree(w->plan.d_ctas);
+        if (w->stage_x) cudaFree(w->stage_x);
+        if (w->stage_c) cudaFree(w->stage_c);
+        if (w->pin_x) cudaFreeHost(w->pin_x);
+        if (w->pin_c) cudaFreeHost(w->pin_c);
+        if (w->stage_stream) cudaStreamDestroy((cudaStream_t)w->stage_stream);
+        cudaSetDevice(cur);
+    }
+    w->dev.clear();
+    w->plan = LaunchPlan();
+    w->stage_x = w->stage_c = w->pin_x = w->pin_c = w->stage_stream = nullptr;
+    w->stage_x_bytes = w->stage_c_bytes = 0;
+    w->device = -1;
+}
+
+// Give each of `grid` CTAs a contiguous run of whole columns holding about total/grid blocks.
+static void make_plan(sptmm_weights *w)
+{
+    LaunchPlan &pl = w->plan;
+    const Tune &t = tune();
+    pl.grid = w->sm_count * t.ctas_per_sm;
+    pl.threads = t.threads;
+    const uint32_t *off = (const uint32_t *)w->arrays[1].data.data();
+    const uint32_t N = w->N;
+    const uint64_t total = w->total_blocks;
+    pl.ctas.resize(pl.grid);
+    uint32_t c = 0;
+    pl.max_cols = 1;
+    for (uint32_t i = 0; i < pl.grid; i++) {
+        const uint64_t target = total * (i + 1) / pl.grid;
+        uint32_t c1 = c;
+        if (i + 1 == pl.grid) c1 = N;
+        else {
+            while (c1 < N && off[2 * (size_t)(c1 + 1)] <= target) c1++;
+            // take one more column if that lands closer to the target
+            if (c1 < N && (int64_t)off[2 * (size_t)(c1 + 1)] - (int64_t)target < (int64_t)target - (int64_t)off[2 * (size_t)c1]) c1++;
+        }
+        pl.ctas[i] = CtaPlan{c, c1, off[2 * (size_t)c], off[2 * (size_t)c1]};
+        pl.max_cols = std::max(pl.max_cols, c1 - c);
+        c = c1;
+    }
+}
+
+}  // namespace sptmm
+
+using namespace sptmm;
+
+extern "C" int sptmm_weights_upload_replicas(sptmm_weights *w, uint32_t copies)
+{
+    if (!w) return fail(SPTMM_ERR_INVALID, "weights_upload: null handle");
+    if (copies == 0 || copies > 4096) return fail(SPTMM_ERR_INVALID, "weights_upload: copies=%u", copies);
+    free_device_side(w);
+    int dev = 0, sms = 0;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    SPTMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    w->device = dev;
+    w->sm_count = (uint32_t)sms;
+    w->dev.assign(copies, std::vector<void *>(w->arrays.size(), nullptr));
+    for (uint32_t r = 0; r < copies; r++)
+        for (size_t a = 0; a < w->arrays.size(); a++) {
+            const size_t bytes = std::max<size_t>(w->arrays[a].data.size(), 16);
+            cudaError_t e = cudaMalloc(&w->dev[r][a], bytes);
+            if (e == cudaSuccess)
+                e = cudaMemcpy(w->dev[r][a], w->arrays[a].data.data(), w->arrays[a].data.size(), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) {
+                free_device_side(w);
+                return fail(SPTMM_ERR_CUDA, "weights_upload: %s", cudaGetErrorString(e));
+            }
+        }
+    if (w->format == SPTMM_FMT_U16_V256 || w->format == SPTMM_FMT_DELTA_LANE) {
+        make_plan(w);
+        const size_t bytes = w->plan.ctas.size() * sizeof(CtaPlan);
+        cudaError_t e = cudaMalloc(&w->plan.d_ctas, bytes);
+        if (e == cudaSuccess) e = cudaMemcpy(w->plan.d_ctas, w->plan.ctas.data(), bytes, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            free_device_side(w);
+            return fail(SPTMM_ERR_CUDA, "weights_upload: %s", cudaGetErrorString(e));
+        }
+    }
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_weights_upload(sptmm_weights *w) { return sptmm_weights_upload_replicas(w, 1); }
+
+extern "C" int sptmm_weights_free(sptmm_weights *w)
+{
+    if (!w) return SPTMM_OK;
+    free_device_side(w);
+    delete w;
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M, void *C,
+                          uint32_t flags, uint32_t replica, void *stream)
+{
+    if (!w || !X || !C) return fail(SPTMM_ERR_INVALID, "gemv: null pointer");
+    if (M == 0) return fail(SPTMM_ERR_INVALID, "gemv: M must be at least 1");
+    if (dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv: unknown dtype %u", dtype);
+    if (w->device < 0 || w->dev.empty()) return fail(SPTMM_ERR_STATE, "gemv: weights are not uploaded");
+    if (replica >= w->dev.size()) return fail(SPTMM_ERR_INVALID, "gemv: replica %u of %zu", replica, w->dev.size());
+    int dev = -1;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != w->device) return fail(SPTMM_ERR_STATE, "gemv: weights live on device %d, current device is %d", w->device, dev);
+    const void *const *arr = w->dev[replica].data();
+    GemvArgs a{w, arr, X, C, dtype, M, flags, stream};
+    switch (w->format) {
+        case SPTMM_FMT_U16_V256: return launch_native_u16(a);
+        case SPTMM_FMT_DELTA_LANE: return launch_native_delta(a);
+        case SPTMM_FMT_I2S: return launch_i2s(a);
+        case SPTMM_FMT_U16_DIV:
+            return launch_div(X, (const uint16_t *)arr[0], (const uint16_t *)arr[1], C, dtype, M, w->K, w->N, w->S,
+                              w->split, flags, stream);
+        case SPTMM_FMT_DELTA_DIV256:
+            return launch_delta256(X, (const uint8_t *)arr[0], (const uint8_t *)arr[1], C, dtype, M, w->K, w->N, w->S,
+                                   flags, stream);
+    }
+    return fail(SPTMM_ERR_UNSUPPORTED, "gemv: format %u", w->format);
+}
+
+extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
+                               uint32_t flags)
+{
+    if (!w || !X_host || !C_host) return fail(SPTMM_ERR_INVALID, "gemv_host: null pointer");
+    if (M == 0 || dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv_host: bad M or dtype");
+    if (w->device < 0) return fail(SPTMM_ERR_STATE, "gemv_host: weights are not uploaded");
+    const size_t xb = (size_t)M * w->K * dtype_size(dtype), cb = (size_t)M * w->N * 4;
+    if (!w->stage_stream) {
+        cudaStream_t s;
+        SPTMM_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        w->stage_stream = s;
+    }
+    if (xb > w->stage_x_bytes) {
+        if (w->stage_x) cudaFree(w->stage_x);
+        if (w->pin_x) cudaFreeHost(w->pin_x);
+        w->stage_x = w->pin_x = nullptr; w->stage_x_bytes = 0;
+        SPTMM_CUDA_TRY(cudaMalloc(&w->stage_x, xb));
+        SPTMM_CUDA_TRY(cudaMallocHost(&w->pin_x, xb));
+        w->stage_x_bytes = xb;
+    }
+    if (cb > w->stage_c_bytes) {
+        if (w->stage_c) cudaFree(w->stage_c);
+        if (w->pin_c) cudaFreeHost(w->pin_c);
+        w->stage_c = w->pin_c = nullptr; w->stage_c_bytes = 0;
+        SPTMM_CUDA_TRY(cudaMalloc(&w->stage_c, cb));
+        SPTMM_CUDA_TRY(cudaMallocHost(&w->pin_c, cb));
+        w->stage_c_bytes = cb;
+    }
+    cudaStream_t st = (cudaStream_t)w->stage_stream;
+    memcpy(w->pin_x, X_host, xb);
+    SPTMM_CUDA_TRY(cudaMemcpyAsync(w->stage_x, w->pin_x, xb, cudaMemcpyHostToDevice, st));
+    int rc = sptmm_gemv(w, w->stage_x, dtype, M, w->stage_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, 0, st);
+    if (rc != SPTMM_OK) return rc;
+    SPTMM_CUDA_TRY(cudaMemcpyAsync(w->pin_c, w->stage_c, cb, cudaMemcpyDeviceToHost, st));
+    SPTMM_CUDA_TRY(cudaStreamSynchronize(st));
+    memcpy(C_host, w->pin_c, cb);
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_row_split3_small(const int8_t *X, const uint16_t *W_pos_div, const uint16_t *W_neg_div,
+                                      int32_t *C, uint32_t M, uint32_t K, uint32_t N, uint32_t S,
+                                      uint32_t split, void *stream)
+{
+    return launch_div(X, W_pos_div, W_neg_div, C, SPTMM_I8, M, K, N, S, split, 0, stream);
+}
+
+extern "C" int sptmm_row_split_delta2(const int8_t *X, const uint8_t *W_pos_delta, const uint8_t *W_neg_delta,
+                                      int32_t *C, uint32_t M, uint32_t K, uint32_t N, uint32_t S,
+                                      uint32_t split, void *stream)
+{
+    if (split != 32) return fail(SPTMM_ERR_INVALID, "Wrong split size");     // main.cu:1837-1839
+    return launch_delta256(X, W_pos_delta, W_neg_delta, C, SPTMM_I8, M, K, N, S, 0, stream);
+}
+
+extern "C" int sptmm_device_count(int *count)
+{
+    if (!count) return fail(SPTMM_ERR_INVALID, "device_count: null pointer");
+    cudaError_t e = cudaGetDeviceCount(count);
+    if (e != cudaSuccess) { *count = 0; return fail(SPTMM_ERR_CUDA, "cudaGetDeviceCount: %s", cudaGetErrorString(e)); }
+    return SPTMM_OK;
+}
+extern "C" int sptmm_set_device(int device) { SPTMM_CUDA_TRY(cudaSetDevice(device)); return SPTMM_OK; }
+extern "C" int sptmm_dev_alloc(void **ptr, uint64_t bytes)
+{
+    if (!ptr) return fail(SPTMM_ERR_INVALID, "dev_alloc: null pointer");
+    SPTMM_CUDA_TRY(cudaMalloc(ptr, bytes ? bytes : 1));
+    return SPTMM_OK;
+}
+extern "C" int sptmm_dev_free(void *ptr) { SPTMM_CUDA_TRY(cudaFree(ptr)); return SPTMM_OK; }
+extern "C" int sptmm_memcpy_h2d(void *dst, const void *src, uint64_t bytes)
+{
+    SPTMM_CUDA_TRY(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    return SPTMM_OK;
+}
+extern "C" int sptmm_memcpy_d2h(void *dst, const void *src, uint64_t bytes)
+{
+    SPTMM_CUDA_TRY(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    return SPTMM_OK;
+}
+extern "C" int sptmm_device_sync(void) { SPTMM_CUDA_TRY(cudaDeviceSynchronize()); return SPTMM_OK; }

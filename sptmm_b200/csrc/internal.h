@@ -1,0 +1,78 @@
+// internal.h -- structures shared by the host encoder, the device API and the kernel launchers.
+#pragma once
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/sptmm.h"
+
+namespace sptmm {
+
+int fail(int code, const char *fmt, ...);        // records the message, returns `code`
+
+struct HostArray {
+    std::string name;
+    std::vector<uint8_t> data;
+    bool streamed;      // read once per matmul (counts toward stream_bytes)
+};
+
+// One CTA's share of a native-format matrix: columns [c0,c1) and their blocks [b0,b1).
+struct CtaPlan { uint32_t c0, c1, b0, b1; };
+
+struct LaunchPlan {                   // derived at upload time from the device's SM count
+    uint32_t grid = 0;                // CTAs along x
+    uint32_t threads = 0;             // threads per CTA
+    uint32_t max_cols = 0;            // most columns any CTA owns
+    std::vector<CtaPlan> ctas;
+    void *d_ctas = nullptr;
+};
+
+}  // namespace sptmm
+
+struct sptmm_weights {
+    uint32_t K = 0, N = 0, format = 0, split = 0, S = 0, max_count = 0;
+    uint64_t nnz = 0, stream_bytes = 0, lossy = 0;
+    uint32_t total_blocks = 0;        // native formats
+    uint32_t entries_per_block = 0;
+    std::vector<sptmm::HostArray> arrays;
+
+    int device = -1;
+    uint32_t sm_count = 0;
+    std::vector<std::vector<void *>> dev;   // [replica][array]
+    sptmm::LaunchPlan plan;
+
+    // pinned / device staging for sptmm_gemv_host
+    void *pin_x = nullptr, *pin_c = nullptr, *stage_x = nullptr, *stage_c = nullptr;
+    size_t stage_x_bytes = 0, stage_c_bytes = 0;
+    void *stage_stream = nullptr;
+};
+
+namespace sptmm {
+
+// Tunables read once from the environment (SPTMM_TUNE="ctas_per_sm=1,threads=512,prefetch=8").
+struct Tune { int ctas_per_sm; int threads; int prefetch; int evict_first; };
+const Tune &tune();
+
+struct GemvArgs {
+    const sptmm_weights *w;
+    const void *const *arrays;        // device arrays of the chosen replica
+    const void *X; void *C;
+    uint32_t dtype, M, flags;
+    void *stream;
+};
+
+int launch_native_u16(const GemvArgs &a);
+int launch_native_delta(const GemvArgs &a);
+int launch_i2s(const GemvArgs &a);
+int launch_div(const void *X, const uint16_t *wp, const uint16_t *wn, void *C, uint32_t dtype,
+               uint32_t M, uint32_t K, uint32_t N, uint32_t S, uint32_t split, uint32_t flags,
+               void *stream);
+int launch_delta256(const void *X, const uint8_t *dp, const uint8_t *dn, void *C, uint32_t dtype,
+                    uint32_t M, uint32_t K, uint32_t N, uint32_t S, uint32_t flags, void *stream);
+int kernels_init();                   // opt in to >48 KB dynamic shared memory, once per process
+
+inline size_t dtype_size(uint32_t d) { return d == SPTMM_I8 ? 1 : d == SPTMM_F16 ? 2 : 4; }
+
+}  // namespace sptmm

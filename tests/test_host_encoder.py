@@ -1,0 +1,145 @@
+"""CPU tests of the library's host side through the C ABI: generators and encoder against the
+oracle byte for byte, error behaviour, and that libsptmm.so exports what include/sptmm.h declares.
+No compute call is made here (no GPU)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import sptmm_b200 as sp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "sptmm.h")).read()
+    declared = sorted(set(re.findall(r"\b(sptmm_[a-z0-9_]+)\s*\(", header)))
+    assert declared, "no declarations found"
+    raw = C.CDLL(sp.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), "libsptmm.so does not export %s" % name
+    assert sorted(sp.EXPORTS) == declared
+    assert sp.lib.sptmm_version() >= 100
+
+
+@pytest.mark.parametrize("K,N,S", [(256, 32, 128), (512, 48, 256), (6912, 64, 4096)])
+def test_fixed_generator_matches_oracle(K, N, S):
+    assert (sp.gen_ternary_fixed(K, N, S) == O.gen_fixed(K, N, S)).all()
+
+
+@pytest.mark.parametrize("p0,seed", [(1 / 3, 0), (0.5, 7), (0.75, 123456789)])
+def test_iid_generator_matches_oracle(p0, seed):
+    assert (sp.gen_ternary_iid(1000, 80, p0, seed) == O.gen_iid(1000, 80, p0, seed)).all()
+
+
+@pytest.mark.parametrize("split", [8, 16, 32])
+def test_u16_div_encoding_is_reference_layout(split):
+    K, N, S = 512, 64, 256
+    W = sp.gen_ternary_fixed(K, N, S)
+    w = sp.Weights(W, sp.FMT_U16_DIV, split=split, S=S)
+    pos, neg, _, _ = O.build_lists(W, S // 2, K)
+    name0, a0, _ = w.array(0)
+    name1, a1, _ = w.array(1)
+    assert name0 == "W_map_%d_div" % split and name1 == "W_map_negative_%d_div" % split
+    assert (a0.view(np.uint16) == O.encode_div(pos, split)).all()
+    assert (a1.view(np.uint16) == O.encode_div(neg, split)).all()
+    assert w.info.S == S and w.info.nnz == S * N and w.info.stream_bytes == 2 * S * N
+    assert w.info.max_count == S // 2
+
+
+@pytest.mark.parametrize("S", [512, 384])
+def test_delta_div256_encoding_is_reference_layout(S):
+    K, N = 1024, 32
+    W = sp.gen_ternary_fixed(K, N, S)
+    w = sp.Weights(W, sp.FMT_DELTA_DIV256, S=S)
+    pos, neg, _, _ = O.build_lists(W, S // 2, K)
+    gp, _ = O.delta_lists(pos)
+    gn, _ = O.delta_lists(neg)
+    assert (w.array(0)[1] == O.encode_delta_div256(gp)).all()
+    assert (w.array(1)[1] == O.encode_delta_div256(gn)).all()
+    assert w.info.lossy_entries == 0
+    assert w.info.stream_bytes == S * N          # the padded tail of the last block is never read
+
+
+def test_delta_div256_reports_lossy_entries():
+    K, N = 1024, 16
+    W = np.zeros((N, K), dtype=np.int8)
+    W[:, 300] = 1; W[:, 310] = 1
+    W[:, 5] = -1; W[:, 700] = -1
+    w = sp.Weights(W, sp.FMT_DELTA_DIV256)
+    assert w.info.lossy_entries == 2 * N         # first +1 index 300 and the -1 gap 695
+
+
+def _decode_v256(w: sp.Weights, K: int):
+    """Invert the native layout: position 8*lane+t of a block holds entry 32*t+lane."""
+    _, idx, _ = w.array(0)
+    _, off, _ = w.array(1)
+    idx = idx.view(np.uint16).reshape(-1, 32, 8)
+    off = off.view(np.uint32)
+    lists = []
+    for l in range(len(off) - 1):
+        blocks = idx[off[l]:off[l + 1]]                      # (nb, lane, t)
+        entries = blocks.transpose(0, 2, 1).reshape(-1)      # entry = b*256 + 32*t + lane
+        lists.append(entries[entries != K])
+    return lists
+
+
+@pytest.mark.parametrize("p0", [1 / 3, 0.75, 1.0])
+def test_v256_encoding_roundtrip(p0):
+    K, N = 700, 40
+    W = sp.gen_ternary_iid(K, N, p0, 11)
+    w = sp.Weights(W, sp.FMT_U16_V256)
+    lists = _decode_v256(w, K)
+    for c in range(N):
+        assert (lists[2 * c] == np.nonzero(W[c] == 1)[0]).all()
+        assert (lists[2 * c + 1] == np.nonzero(W[c] == -1)[0]).all()
+    _, off, _ = w.array(1)
+    total_blocks = int(off.view(np.uint32)[-1])
+    assert w.info.stream_bytes == total_blocks * 512 + (2 * N + 1) * 4
+    assert w.info.nnz == int((W != 0).sum())
+
+
+def test_i2s_encoding_matches_oracle_packing():
+    K, N = 64, 16
+    W = sp.gen_ternary_iid(K, N, 0.4, 3)
+    w = sp.Weights(W, sp.FMT_I2S)
+    words = w.array(0)[1].view(np.uint32).reshape(N, K // 16)
+    for c in (0, 7, 15):
+        for j in range(K // 16):
+            assert int(words[c, j]) == O.i2s_pack16(W[c, 16 * j:16 * j + 16])
+    assert w.info.stream_bytes == K * N // 4
+
+
+def test_encode_errors():
+    W = sp.gen_ternary_fixed(256, 32, 128)
+    with pytest.raises(sp.SptmmError) as e:
+        sp.Weights(W, sp.FMT_U16_DIV, split=12)
+    assert "Wrong split size" in e.value.message and e.value.code == -1     # main.cu:1039
+    with pytest.raises(sp.SptmmError):
+        sp.Weights(W, sp.FMT_U16_DIV, split=32, S=64)                       # a column has more than S/2
+    with pytest.raises(sp.SptmmError):
+        sp.Weights(W, sp.FMT_U16_DIV, split=32, S=129)                      # S odd (main.cu:90)
+    bad = W.copy(); bad[3, 5] = 2
+    with pytest.raises(sp.SptmmError):
+        sp.Weights(bad, sp.FMT_U16_V256)
+    with pytest.raises(sp.SptmmError):
+        sp.Weights(np.zeros((4, 65536), dtype=np.int8), sp.FMT_U16_V256)    # K < 65536 (main.cu:89)
+    iid = sp.gen_ternary_iid(256, 32, 0.5, 0)
+    with pytest.raises(sp.SptmmError) as e:
+        sp.Weights(iid, sp.FMT_DELTA_DIV256)                                # ragged lists: no padding value
+    assert e.value.code == -3
+    with pytest.raises(sp.SptmmError):
+        sp.Weights(W[:, :250], sp.FMT_I2S)                                  # K % 16
+
+
+def test_gemv_without_upload_fails_loudly():
+    W = sp.gen_ternary_fixed(256, 32, 128)
+    w = sp.Weights(W, sp.FMT_U16_V256)
+    x = np.zeros(256, dtype=np.int8)
+    out = np.zeros(32, dtype=np.int32)
+    with pytest.raises(sp.SptmmError) as e:
+        w.gemv(x, 1, out)
+    assert e.value.code == -6 and "not uploaded" in e.value.message
