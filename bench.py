@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the ternary GEMV hot path (6912 x 2560, M=1, int8 -> int32) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = `--calls` GEMV calls issued back to back on one stream, rotating over enough
+distinct copies of the encoded weights that their total exceeds L2 (cold-cache, HBM-bound).
+The step is captured once in a CUDA graph (programmatic-dependent-launch edges between the
+calls) and replayed; timing is by CUDA events on that stream, max over ranks.
+Prints ONE JSON line on rank 0.
+
+`--impl reference` times the CPU restatement of the reference's loop (the reference has no CPU
+path and its GPU kernels print only a time) on all host threads, same metric and unit.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+K, N, S, M = 6912, 2560, 4096, 1
+L2_BYTES = 126 * 1024 * 1024
+METRIC = "effective_hbm_GBps_ternary_gemv_6912x2560_M1"
+
+
+def algorithmic_bytes(stream_bytes: int, m: int, act_size: int) -> int:
+    """encoded weights + M*K activations + M*N int32/float32 outputs, per call."""
+    return stream_bytes + m * K * act_size + m * N * 4
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the benchmark runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.thread = [], None, None
+        self.cmd = ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "50"]
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append((time.time(), line.strip()))
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, n = [], None, set(), 0
+        for t, line in self.rows:
+            if t < t0 or t > t1 + 0.05:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx = float(f[1])
+            except ValueError:
+                continue
+            n += 1
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": n}
+
+
+def cpu_baseline(budget_s: float = 8.0):
+    """Scalar add/sub loop over the reference's chunk-interleaved u16 layout on the host cores."""
+    import oracle_lib as O
+    W = O.gen_fixed(K, N, S)
+    X = O.gen_x_i8(M * K, 1)
+    pos, neg, _, _ = O.build_lists(W, S // 2, K)
+    wp, wn = O.encode_div(pos, 32), O.encode_div(neg, 32)
+    cores = os.cpu_count() or 1
+    nbytes = algorithmic_bytes(2 * S * N, M, 1)
+    O.gemv_i8_div_mt(X, wp, wn, M, K, N, S, 32, cores)
+    calls, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < budget_s:
+        O.gemv_i8_div_mt(X, wp, wn, M, K, N, S, 32, cores)
+        calls += 1
+    dt = (time.perf_counter() - t0) / calls
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "us_per_call": dt * 1e6,
+            "sample": "%d calls of the same M=1 6912x2560 S=4096 GEMV over ~%.0f s, %d threads" % (calls, budget_s, cores)}, (X, wp, wn)
+
+
+def run_reference(args):
+    """CPU port of the reference loop, all host threads; step = 4 calls."""
+    import oracle_lib as O
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, (X, wp, wn) = cpu_baseline(budget_s=2.0)
+    cores = base["cores"]
+    per_step = 4
+    for _ in range(min(args.warmup, 20)):
+        O.gemv_i8_div_mt(X, wp, wn, M, K, N, S, 32, cores)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for _ in range(per_step):
+            O.gemv_i8_div_mt(X, wp, wn, M, K, N, S, 32, cores)
+    dt = time.perf_counter() - t0
+    nbytes = algorithmic_bytes(2 * S * N, M, 1)
+    value = nbytes * per_step * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "us_per_call": dt / (args.steps * per_step) * 1e6, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+        "config": {"workload": "C1 ternary GEMV M=1 K=6912 N=2560, reference generator -S=4096, u16 lists split 32",
+                   "calls_per_step": per_step},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": "%d steps x %d calls, scalar add/sub loop over W_map_32_div, %d threads" % (args.steps, per_step, cores)},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import sptmm_b200 as sp
+    import oracle_lib as O
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    # ---- workload: every rank owns an independent 2560-column shard (weak scaling over N)
+    W = sp.gen_ternary_fixed(K, N, S)
+    w = sp.Weights(W, sp.FMT_U16_V256)
+    per_copy = w.stream_bytes
+    replicas = max(2, -(-int(2.5 * L2_BYTES) // per_copy))
+    w.upload(replicas)
+    nbytes = algorithmic_bytes(per_copy, M, 1)
+    Xh = O.gen_x_i8(M * K, 1)
+    xd = torch.from_numpy(Xh).cuda()
+    out = torch.zeros(replicas, M * N, dtype=torch.int32, device="cuda")
+    calls = args.calls
+    st = torch.cuda.Stream()
+
+    def issue_step(stream):
+        for i in range(calls):
+            r = i % replicas
+            w.gemv(xd, M, out[r], sp.I8, sp.LAUNCH_PDL, replica=r, stream=stream.cuda_stream)
+
+    # parity first: a fast wrong kernel is not a result
+    with torch.cuda.stream(st):
+        issue_step(st)
+    st.synchronize()
+    want = O.gemv_i8_dense(Xh, W).reshape(-1)
+    for r in range(replicas):
+        if not np.array_equal(out[r].cpu().numpy(), want):
+            raise SystemExit("parity failure on replica %d" % r)
+
+    graph, mode = None, "direct launches"
+    if not args.no_graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st, capture_error_mode="thread_local"):
+                issue_step(st)
+            graph, mode = g, "CUDA graph replay"
+        except Exception as e:                      # keep going with plain launches
+            mode = "direct launches (graph capture failed: %s)" % str(e).splitlines()[0][:80]
+            torch.cuda.synchronize()
+
+    def one_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            issue_step(st)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(st):
+        if sampler:
+            sampler.start()
+        t_load0 = time.time()
+        for _ in range(max(3, args.warmup)):
+            one_step()
+        st.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev0.record(st)
+        for _ in range(args.steps):
+            one_step()
+        ev1.record(st)
+        st.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t_load1 = time.time()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop(t_load0, t_load1) if sampler else None
+
+    total_calls = args.steps * calls
+    us_per_call = ms * 1e3 / total_calls
+    per_gpu = nbytes / (us_per_call * 1e-6) / 1e9
+    value = per_gpu * world
+
+    # ---- end to end through the host-buffer entry point (H2D + kernel + D2H + wait per call)
+    e2e_calls = max(64, min(2000, total_calls // 8))
+    Ch = np.empty((M, N), dtype=np.int32)
+    for i in range(8):
+        w.gemv_host(Xh, sp.I8, replica=i % replicas, out=Ch)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_calls):
+        w.gemv_host(Xh, sp.I8, replica=i % replicas, out=Ch)
+    e2e_s = time.perf_counter() - t0
+    if not np.array_equal(Ch.reshape(-1), want):
+        raise SystemExit("parity failure in the host-buffer call")
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_us = e2e_s / e2e_calls * 1e6
+    e2e_value = nbytes / (e2e_us * 1e-6) / 1e9 * world
+
+    line = None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "us_per_call": us_per_call,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
+            "pct_of_8000GBps": per_gpu / 8000.0 * 100.0,
+            "config": {"workload": "C1 ternary GEMV M=1 K=6912 N=2560, reference generator -S=4096, native u16 lists",
+                       "calls_per_step": calls, "weight_copies": replicas,
+                       "l2": "cold: rotating %d weight copies (%.0f MB) > 126 MB L2" % (replicas, replicas * per_copy / 1e6),
+                       "launch": mode + ", programmatic dependent launch",
+                       "per_rank": "each GPU runs the same independent 2560-column shard",
+                       "tune": os.environ.get("SPTMM_TUNE", "")},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                         "peak_kind": peak_kind, "algorithmic_bytes_per_launch": nbytes, "traffic": NCU_TRAFFIC_BYTES},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "us_per_call": e2e_us,
+                    "h2d_bytes_per_step": M * K * calls, "d2h_bytes_per_step": M * N * 4 * calls,
+                    "calls_timed": e2e_calls, "how": "sptmm_gemv_host per call: pinned H2D, kernel, D2H, stream wait"},
+            "gpu_launches": total_calls,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"], _ = cpu_baseline()
+        if args.extra:
+            line["extra"] = extra_workloads(sp, O, torch, st)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of k_u16_v256 from the committed ncu
+# summary under profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES = None
+
+
+def extra_workloads(sp, O, torch, st):
+    """M=4 fp16 (same W), the reference layouts, the delta sweep and the comparators: us/call,
+    warm-cache (single weight copy), for context beside the headline."""
+    res = {}
+    W = sp.gen_ternary_fixed(K, N, S)
+    rng = np.random.default_rng(2)
+
+    def timeit(fn, n=400):
+        for _ in range(20):
+            fn()
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(n):
+            fn()
+        e1.record(st)
+        st.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / n
+
+    def cold_replicas(w):
+        r = max(2, -(-int(2.5 * L2_BYTES) // max(1, w.stream_bytes)))
+        return min(r, 160)
+
+    cases = [("u16_v256", sp.FMT_U16_V256, 32, 0), ("u16_div32", sp.FMT_U16_DIV, 32, S),
+             ("delta_div256", sp.FMT_DELTA_DIV256, 32, S), ("i2s", sp.FMT_I2S, 0, 0)]
+    for name, fmt, split, s_arg in cases:
+        w = sp.Weights(W, fmt, split=split, S=s_arg)
+        reps = cold_replicas(w)
+        w.upload(reps)
+        for m, dt in ((1, sp.I8), (4, sp.I8), (4, sp.F16), (16, sp.I8)):
+            if fmt == sp.FMT_I2S and dt != sp.I8:
+                continue
+            if dt == sp.I8:
+                x = torch.from_numpy(O.gen_x_i8(m * K, 1)).cuda()
+                o = torch.zeros(m * N, dtype=torch.int32, device="cuda")
+            else:
+                x = torch.from_numpy(rng.standard_normal((m, K)).astype(np.float16)).cuda()
+                o = torch.zeros(m * N, dtype=torch.float32, device="cuda")
+            ctr = [0]
+            def call():
+                w.gemv(x, m, o, dt, sp.LAUNCH_PDL, replica=ctr[0] % reps, stream=st.cuda_stream)
+                ctr[0] += 1
+            us = timeit(call)
+            nb = algorithmic_bytes(w.stream_bytes, m, 1 if dt == sp.I8 else 2)
+            res["%s_M%d_%s" % (name, m, "i8" if dt == sp.I8 else "f16")] = {
+                "us_per_call": us, "GBps": nb / us / 1e3, "bytes": nb, "copies": reps}
+        w.close()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--calls", type=int, default=1024, help="GEMV calls per step")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

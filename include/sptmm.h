@@ -117,7 +117,7 @@ int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M
 /* Same, but X and C are HOST buffers: copies X in, runs, copies C out, waits.  Uses pinned
  * staging owned by the handle (not re-entrant per handle). */
 int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
-                    uint32_t flags);
+                    uint32_t flags, uint32_t replica);
 
 /* Raw-pointer forms with the reference's kernel argument convention (X, W_pos, W_neg, C), for a
  * caller that built the reference layouts itself.

@@ -58,7 +58,7 @@ def _load() -> C.CDLL:
         "sptmm_weights_upload_replicas": (i32, [vp, u32]),
         "sptmm_weights_free": (i32, [vp]),
         "sptmm_gemv": (i32, [vp, vp, u32, u32, vp, u32, u32, vp]),
-        "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32]),
+        "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32, u32]),
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
@@ -163,14 +163,15 @@ class Weights:
         """C = X*W on the device; X and out are device tensors (or addresses)."""
         check(lib.sptmm_gemv(self._h, _ptr(X), dtype, M, _ptr(out), flags, replica, stream))
 
-    def gemv_host(self, X: np.ndarray, dtype: int = I8, flags: int = 0) -> np.ndarray:
+    def gemv_host(self, X: np.ndarray, dtype: int = I8, flags: int = 0, replica: int = 0, out: Optional[np.ndarray] = None) -> np.ndarray:
         """Host-buffer call: copies X to the device, runs, copies C back."""
         X = np.ascontiguousarray(X, dtype=_NP_DTYPE[dtype])
         M = X.shape[0] if X.ndim == 2 else 1
         if flags & X_COLMAJOR:
             M = X.shape[1]
-        out = np.empty((self.N, M) if flags & C_COLMAJOR else (M, self.N), dtype=_OUT_DTYPE[dtype])
-        check(lib.sptmm_gemv_host(self._h, X.ctypes.data, dtype, M, out.ctypes.data, flags))
+        if out is None:
+            out = np.empty((self.N, M) if flags & C_COLMAJOR else (M, self.N), dtype=_OUT_DTYPE[dtype])
+        check(lib.sptmm_gemv_host(self._h, X.ctypes.data, dtype, M, out.ctypes.data, flags, replica))
         return out
 
     def close(self) -> None:

@@ -164,7 +164,7 @@ extern "C" int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype,
 }
 
 extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
-                               uint32_t flags)
+                               uint32_t flags, uint32_t replica)
 {
     if (!w || !X_host || !C_host) return fail(SPTMM_ERR_INVALID, "gemv_host: null pointer");
     if (M == 0 || dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv_host: bad M or dtype");
@@ -194,7 +194,7 @@ extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dt
     cudaStream_t st = (cudaStream_t)w->stage_stream;
     memcpy(w->pin_x, X_host, xb);
     SPTMM_CUDA_TRY(cudaMemcpyAsync(w->stage_x, w->pin_x, xb, cudaMemcpyHostToDevice, st));
-    int rc = sptmm_gemv(w, w->stage_x, dtype, M, w->stage_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, 0, st);
+    int rc = sptmm_gemv(w, w->stage_x, dtype, M, w->stage_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, replica, st);
     if (rc != SPTMM_OK) return rc;
     SPTMM_CUDA_TRY(cudaMemcpyAsync(w->pin_c, w->stage_c, cb, cudaMemcpyDeviceToHost, st));
     SPTMM_CUDA_TRY(cudaStreamSynchronize(st));
