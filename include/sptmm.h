@@ -141,6 +141,13 @@ int sptmm_row_split_delta2(const int8_t *X, const uint8_t *W_pos_delta, const ui
 int sptmm_dense_cublas_gemm(const int8_t *X_colmajor, const int8_t *W_dense, int32_t *C_colmajor,
                             uint32_t M, uint32_t K, uint32_t N, void *stream);
 
+/* ---- diagnostics ---------------------------------------------------------------------------- */
+
+/* No counterpart in the reference.  While `dev_ptr` (64 x uint64 of device memory) is set, the
+ * native kernel's first 8 CTAs record %globaltimer at entry, after the wait on the previous
+ * kernel, after staging X, after the gather loop and at exit.  NULL switches it off. */
+int sptmm_set_trace_buffer(void *dev_ptr);
+
 /* ---- small device helpers so a C caller needs no CUDA headers ------------------------------ */
 int sptmm_device_count(int *count);
 int sptmm_set_device(int device);

@@ -43,7 +43,7 @@ class WeightsInfo(C.Structure):
 
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
-        raise ImportError("libsptmm.so is not built: run `python -m sptmm_b200.build` (needs nvcc)")
+        raise ImportError("libsptmm.so is not built: run `python sptmm_b200/build.py` (needs nvcc)")
     lib = C.CDLL(LIB_PATH)
     u32, u64, vp, i32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int
     sigs = {
@@ -62,6 +62,7 @@ def _load() -> C.CDLL:
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
+        "sptmm_set_trace_buffer": (i32, [vp]),
         "sptmm_device_count": (i32, [C.POINTER(C.c_int)]),
         "sptmm_set_device": (i32, [C.c_int]),
         "sptmm_dev_alloc": (i32, [C.POINTER(vp), u64]),
@@ -82,7 +83,7 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_host",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
-           "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
+           "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
 
 

@@ -1,6 +1,6 @@
 """Builds libsptmm.so (and the rcr / ccc command-line programs) in-tree with nvcc for sm_100a.
 
-    python -m sptmm_b200.build [--force] [--verbose]
+    python sptmm_b200/build.py [--force] [--verbose] [--ptxas]
 
 The shared library is the product: a C ABI (include/sptmm.h) over hand-written CUDA kernels.
 Objects are rebuilt only when their source, or a shared header, is newer.

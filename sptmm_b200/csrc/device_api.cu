@@ -11,7 +11,7 @@ namespace sptmm {
 const Tune &tune()
 {
     static Tune t = [] {
-        Tune v{1, 512, 8, 0};
+        Tune v{1, 512, 8, 0, 1, 100};
         const char *s = getenv("SPTMM_TUNE");
         if (s) {
             std::string str(s);
@@ -28,6 +28,8 @@ const Tune &tune()
                     else if (k == "threads" && val >= 32 && val <= 512 && val % 32 == 0) v.threads = val;
                     else if (k == "prefetch" && val >= 1 && val <= 16) v.prefetch = val;
                     else if (k == "evict_first") v.evict_first = val != 0;
+                    else if (k == "l2_prefetch") v.l2_prefetch = val != 0;
+                    else if (k == "smem_kb" && val >= 0 && val <= 220) v.smem_kb = val;
                 }
                 pos = end + 1;
             }
@@ -45,6 +47,7 @@ static void free_device_side(sptmm_weights *w)
         cudaSetDevice(w->device);
         for (auto &rep : w->dev) for (void *p : rep) if (p) cudaFree(p);
         if (w->plan.d_ctas) cudaFree(w->plan.d_ctas);
+        if (w->plan.d_status) cudaFree(w->plan.d_status);
         if (w->stage_x) cudaFree(w->stage_x);
         if (w->stage_c) cudaFree(w->stage_c);
         if (w->pin_x) cudaFreeHost(w->pin_x);
@@ -64,7 +67,8 @@ static void make_plan(sptmm_weights *w)
 {
     LaunchPlan &pl = w->plan;
     const Tune &t = tune();
-    pl.grid = w->sm_count * t.ctas_per_sm;
+    pl.grid = std::min<uint32_t>(w->sm_count * t.ctas_per_sm, 1024);
+    pl.cta_blk.clear(); pl.cta_col.clear();
     pl.threads = t.threads;
     const uint32_t *off = (const uint32_t *)w->arrays[1].data.data();
     const uint32_t N = w->N;
@@ -82,9 +86,14 @@ static void make_plan(sptmm_weights *w)
             if (c1 < N && (int64_t)off[2 * (size_t)(c1 + 1)] - (int64_t)target < (int64_t)target - (int64_t)off[2 * (size_t)c1]) c1++;
         }
         pl.ctas[i] = CtaPlan{c, c1, off[2 * (size_t)c], off[2 * (size_t)c1]};
+        pl.cta_blk.push_back(off[2 * (size_t)c]);
+        pl.cta_col.push_back(c);
         pl.max_cols = std::max(pl.max_cols, c1 - c);
+        pl.max_cta_blocks = std::max(pl.max_cta_blocks, off[2 * (size_t)c1] - off[2 * (size_t)c]);
         c = c1;
     }
+    pl.cta_blk.push_back(off[2 * (size_t)N]);
+    pl.cta_col.push_back(N);
 }
 
 }  // namespace sptmm
@@ -115,9 +124,11 @@ extern "C" int sptmm_weights_upload_replicas(sptmm_weights *w, uint32_t copies)
         }
     if (w->format == SPTMM_FMT_U16_V256 || w->format == SPTMM_FMT_DELTA_LANE) {
         make_plan(w);
-        const size_t bytes = w->plan.ctas.size() * sizeof(CtaPlan);
+        const size_t bytes = w->plan.cta_col.size() * sizeof(uint32_t);
         cudaError_t e = cudaMalloc(&w->plan.d_ctas, bytes);
-        if (e == cudaSuccess) e = cudaMemcpy(w->plan.d_ctas, w->plan.ctas.data(), bytes, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(w->plan.d_ctas, w->plan.cta_col.data(), bytes, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMalloc(&w->plan.d_status, 16);
+        if (e == cudaSuccess) e = cudaMemset(w->plan.d_status, 0, 16);
         if (e != cudaSuccess) {
             free_device_side(w);
             return fail(SPTMM_ERR_CUDA, "weights_upload: %s", cudaGetErrorString(e));
@@ -215,6 +226,12 @@ extern "C" int sptmm_row_split_delta2(const int8_t *X, const uint8_t *W_pos_delt
 {
     if (split != 32) return fail(SPTMM_ERR_INVALID, "Wrong split size");     // main.cu:1837-1839
     return launch_delta256(X, W_pos_delta, W_neg_delta, C, SPTMM_I8, M, K, N, S, 0, stream);
+}
+
+extern "C" int sptmm_set_trace_buffer(void *dev_ptr)
+{
+    set_trace_buffer((unsigned long long *)dev_ptr);
+    return SPTMM_OK;
 }
 
 extern "C" int sptmm_device_count(int *count)

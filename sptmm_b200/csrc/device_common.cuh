@@ -74,6 +74,10 @@ template <int DT, int MT>
 __device__ __forceinline__ void gather_add(typename ActTraits<DT>::acc (&acc)[MT], const unsigned char *xs, uint32_t row)
 {
     constexpr int RB = MT * ActTraits<DT>::size;
+    if constexpr (DT == SPTMM_I8 && MT == 1) {
+        acc[0] += *reinterpret_cast<const int8_t *>(xs + row);      // one sign-extending byte load
+        return;
+    }
     uint32_t r[RowWords<RB>::n];
     load_row<RB>(xs, row, r);
     if constexpr (DT == SPTMM_I8) {
@@ -119,6 +123,55 @@ __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint3
         const uint4 *src = reinterpret_cast<const uint4 *>(X + (size_t)m0 * K);
         for (uint32_t i = tid; i < vec; i += nt) reinterpret_cast<uint4 *>(xs)[i] = __ldg(src + i);
         for (uint32_t k = vec * (16 / ES) + tid; k < K; k += nt) dst[k] = X[(size_t)m0 * K + k];
+    } else if (MT > 1 && !x_colmajor && (K % (4 / ES)) == 0 && (reinterpret_cast<uintptr_t>(X) & 3) == 0) {
+        // One thread takes one 32-bit word (KP = 4/ES consecutive k) from each of the MT rows --
+        // coalesced along k -- transposes the MT x KP elements in registers and writes the KP
+        // finished tile rows (MT*4 contiguous bytes) with vector stores.
+        constexpr int KP = 4 / ES;
+        const uint32_t pieces = K / KP;
+        for (uint32_t pc = tid; pc < pieces; pc += nt) {
+            uint32_t w[MT];
+#pragma unroll
+            for (int m = 0; m < MT; m++)
+                w[m] = (uint32_t)m < mv ? __ldg(reinterpret_cast<const uint32_t *>(X + (size_t)(m0 + m) * K) + pc) : 0u;
+            uint32_t o[MT];                      // o[i*(MT/KP) + j]: word j of tile row k0+i
+            if constexpr (ES == 4) {
+#pragma unroll
+                for (int m = 0; m < MT; m++) o[m] = w[m];
+            } else if constexpr (ES == 2) {
+#pragma unroll
+                for (int j = 0; j < MT / 2; j++) {
+                    o[j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x5410);
+                    o[MT / 2 + j] = __byte_perm(w[2 * j], w[2 * j + 1], 0x7632);
+                }
+            } else {
+                if constexpr (MT == 2) {
+                    // rows k0..k0+3 hold two bytes each: (a_i, b_i)
+                    o[0] = __byte_perm(w[0], w[1], 0x5140);          // a0 b0 a1 b1
+                    o[1] = __byte_perm(w[0], w[1], 0x7362);          // a2 b2 a3 b3
+                } else {
+#pragma unroll
+                    for (int j = 0; j < MT / 4; j++) {
+                        const uint32_t t0 = __byte_perm(w[4 * j], w[4 * j + 1], 0x5140);      // a0 b0 a1 b1
+                        const uint32_t t1 = __byte_perm(w[4 * j + 2], w[4 * j + 3], 0x5140);  // c0 d0 c1 d1
+                        const uint32_t t2 = __byte_perm(w[4 * j], w[4 * j + 1], 0x7362);      // a2 b2 a3 b3
+                        const uint32_t t3 = __byte_perm(w[4 * j + 2], w[4 * j + 3], 0x7362);  // c2 d2 c3 d3
+                        o[0 * (MT / 4) + j] = __byte_perm(t0, t1, 0x5410);
+                        o[1 * (MT / 4) + j] = __byte_perm(t0, t1, 0x7632);
+                        o[2 * (MT / 4) + j] = __byte_perm(t2, t3, 0x5410);
+                        o[3 * (MT / 4) + j] = __byte_perm(t2, t3, 0x7632);
+                    }
+                }
+            }
+            uint32_t *out = reinterpret_cast<uint32_t *>(xs + (size_t)pc * KP * MT * ES);   // MT words
+            if constexpr (MT == 2) {
+                *reinterpret_cast<uint2 *>(out) = make_uint2(o[0], o[1]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < MT / 4; q++)
+                    reinterpret_cast<uint4 *>(out)[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+            }
+        }
     } else {
         for (uint32_t m = 0; m < (uint32_t)MT; m++) {
             if (m < mv) {

@@ -164,6 +164,9 @@ static void encode_u16_v256(const Lists &L, sptmm_weights &w)
     }
     w.total_blocks = off[2 * (size_t)N];
     w.entries_per_block = 256;
+    w.uniform_nbl = off[1] - off[0];
+    for (size_t l = 0; l < 2 * (size_t)N; l++)
+        if (off[l + 1] - off[l] != w.uniform_nbl) { w.uniform_nbl = 0; break; }
     w.arrays.push_back(make_array("idx_v256", (size_t)w.total_blocks * 512, true));
     uint16_t *out = (uint16_t *)w.arrays.back().data.data();
     parallel_columns(N, [&](uint32_t c0, uint32_t c1) {

@@ -26,7 +26,11 @@ struct LaunchPlan {                   // derived at upload time from the device'
     uint32_t threads = 0;             // threads per CTA
     uint32_t max_cols = 0;            // most columns any CTA owns
     std::vector<CtaPlan> ctas;
+    std::vector<uint32_t> cta_blk;    // grid+1 block boundaries (passed in kernel parameters)
+    std::vector<uint32_t> cta_col;    // grid+1 column boundaries (device copy in d_ctas)
     void *d_ctas = nullptr;
+    void *d_status = nullptr;         // device word set by a kernel whose bounded wait ran out
+    uint32_t max_cta_blocks = 0;      // most blocks any CTA owns
 };
 
 }  // namespace sptmm
@@ -36,6 +40,7 @@ struct sptmm_weights {
     uint64_t nnz = 0, stream_bytes = 0, lossy = 0;
     uint32_t total_blocks = 0;        // native formats
     uint32_t entries_per_block = 0;
+    uint32_t uniform_nbl = 0;         // blocks per list if every list has the same count, else 0
     std::vector<sptmm::HostArray> arrays;
 
     int device = -1;
@@ -52,7 +57,7 @@ struct sptmm_weights {
 namespace sptmm {
 
 // Tunables read once from the environment (SPTMM_TUNE="ctas_per_sm=1,threads=512,prefetch=8").
-struct Tune { int ctas_per_sm; int threads; int prefetch; int evict_first; };
+struct Tune { int ctas_per_sm; int threads; int prefetch; int evict_first; int l2_prefetch; int smem_kb; };
 const Tune &tune();
 
 struct GemvArgs {
@@ -71,6 +76,7 @@ int launch_div(const void *X, const uint16_t *wp, const uint16_t *wn, void *C, u
                void *stream);
 int launch_delta256(const void *X, const uint8_t *dp, const uint8_t *dn, void *C, uint32_t dtype,
                     uint32_t M, uint32_t K, uint32_t N, uint32_t S, uint32_t flags, void *stream);
+void set_trace_buffer(unsigned long long *dev_ptr);
 int kernels_init();                   // opt in to >48 KB dynamic shared memory, once per process
 
 inline size_t dtype_size(uint32_t d) { return d == SPTMM_I8 ? 1 : d == SPTMM_F16 ? 2 : 4; }

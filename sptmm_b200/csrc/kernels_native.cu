@@ -4,56 +4,141 @@
 // two-byte index loads and byte gathers through L1, re-streaming every index once per row of X.
 //
 // Design.  The encoded matrix is one contiguous run of 512-byte blocks (256 sorted row indices
-// of one column and one sign, see host_encode.cpp).  The grid is one CTA per SM; a plan made at
-// upload time gives CTA i a contiguous range of whole columns with an equal share of blocks,
-// and inside the CTA each warp takes an equal contiguous slice of those blocks, so every warp
-// streams one linear piece of memory with 16-byte loads per lane, P blocks in flight.
+// of one column and one sign, see host_encode.cpp).  A plan made at upload time gives CTA i a
+// contiguous range of whole columns with an equal share of blocks; the plan travels in the
+// kernel parameters, so no global load precedes the first weight load.  Inside the CTA each
+// warp takes an equal contiguous slice of those blocks.
+//
+// The kernel is a chain of latencies unless every byte is requested at once, so at entry each
+// warp requests its whole slice: the first P blocks with 16-byte loads into registers, the rest
+// with bulk copies (cp.async.bulk, completion on an mbarrier) into a warp-private, double-
+// buffered staging area in shared memory.  Only then does it wait for the previous kernel in
+// the stream (programmatic dependent launch); with two such CTAs resident per SM, DRAM streams
+// this matrix while the previous kernel is still gathering.
 // The activation tile sits transposed in shared memory, so one gather serves MT rows of X and
 // the index stream is read once for up to 16 rows.  Nothing is multiplied.
-// A warp's slice can start and end inside a column: sums for its first and last column go to
-// per-warp slots that are folded in warp order after a barrier, all other columns are owned by
-// one warp, so results do not depend on scheduling (integer and floating point alike).
-// With programmatic dependent launch the index prefetch is issued before the wait on the
-// previous kernel, which hides launch latency and the DRAM ramp behind that kernel's tail.
+//
+// A warp's slice can start and end inside a column.  Integer sums are order-free, so every
+// finished list is added to its column's slot with a shared-memory atomic.  Floating-point sums
+// for a warp's first and last column go to per-warp slots that are folded in warp order after a
+// barrier (all other columns are owned by one warp), so results do not depend on scheduling.
+// Every wait on an mbarrier is bounded; if one runs out the kernel raises a status word and
+// returns instead of hanging.
+#include <algorithm>
+
 #include "device_common.cuh"
 
 namespace sptmm {
 
+constexpr int kMaxGrid = 1024;
+constexpr int kMaxWarps = 16;
+
 struct NativeParams {
     const uint4 *idx;            // total_blocks * 32 vectors
     const uint32_t *blk_off;     // 2N+1
-    const CtaPlan *plan;         // grid entries
     const void *X;
     void *C;
+    unsigned long long *trace;   // optional: 8 timestamps per CTA for the first 8 CTAs
+    uint32_t *status;            // device word: set non-zero if a bounded wait ran out
     uint32_t K, N, M;
     uint32_t max_cols;
-    uint32_t x_colmajor, c_colmajor, evict_first;
+    uint32_t x_colmajor, c_colmajor;
+    uint32_t uniform_nbl;        // blocks per list when every list has the same count, else 0
+    uint32_t half_blocks;        // blocks per half of a warp's staging area
+    uint32_t stage_blocks;       // blocks of staging area per warp (one or two halves)
+    uint32_t stage_off;          // byte offset of the staging area in dynamic shared memory
+    uint32_t cta_blk[kMaxGrid + 1];   // block boundaries: CTA i owns blocks [cta_blk[i], cta_blk[i+1])
+    uint32_t cta_col[kMaxGrid + 1];   // column boundaries: CTA i owns columns [cta_col[i], cta_col[i+1])
 };
 
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ uint4 ld_weights16(const uint4 *p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// bulk copy global -> this CTA's shared memory, completion counted on `bar` (one elected lane)
+__device__ __forceinline__ void bulk_fetch(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// returns false if the barrier did not complete the phase within the iteration limit
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done = 0;
+    for (uint32_t spin = 0; spin < (1u << 22) && !done; spin++)
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+
 template <int DT, int MT, int P, int MINB>
-__global__ void __launch_bounds__(512, MINB) k_u16_v256(const NativeParams p)
+__global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ NativeParams p)
 {
     using acc_t = typename ActTraits<DT>::acc;
     constexpr int RB = MT * ActTraits<DT>::size;
+    constexpr bool kInt = DT == SPTMM_I8;
     extern __shared__ __align__(16) unsigned char smem[];
 
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const CtaPlan plan = p.plan[blockIdx.x];
-    const uint32_t ncols = plan.c1 - plan.c0, nlists = 2 * ncols;
-    const uint32_t nb = plan.b1 - plan.b0;
-    const uint32_t wb0 = plan.b0 + (uint32_t)(((uint64_t)nb * warp) / nwarps);
-    const uint32_t wb1 = plan.b0 + (uint32_t)(((uint64_t)nb * (warp + 1)) / nwarps);
-    const uint64_t ef = p.evict_first ? l2_evict_first_policy() : 0ull;
+    pdl_launch_dependents();     // the next kernel may start its own weight requests right away
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const uint32_t b0 = p.cta_blk[blockIdx.x], b1 = p.cta_blk[blockIdx.x + 1];
+    const uint32_t c0 = p.cta_col[blockIdx.x], c1 = p.cta_col[blockIdx.x + 1];
+    const uint32_t ncols = c1 - c0, nlists = 2 * ncols;
+    const uint32_t nb = b1 - b0;
+    const uint32_t wb0 = b0 + (uint32_t)(((uint64_t)nb * warp) / nwarps);
+    const uint32_t wb1 = b0 + (uint32_t)(((uint64_t)nb * (warp + 1)) / nwarps);
+    const uint32_t n = wb1 - wb0;
+    const uint32_t nbl = p.uniform_nbl;
+    const bool tracing = p.trace != nullptr && blockIdx.x < 8 && blockIdx.y == 0 && tid == 33;   // a lane that issues no fences or copies
+    if (tracing) p.trace[blockIdx.x * 8 + 0] = global_ns();
 
-    // ---- prefetch: weights do not depend on the previous kernel
-    const uint4 *src = p.idx + (size_t)wb0 * 32 + lane;
+    // ---- list boundaries (only needed when lists differ in length): ask for them first, so the
+    // answer is not queued behind the weight stream
+    uint32_t off_r0 = 0, off_r1 = 0;
+    if (nbl == 0) {
+        if (tid <= nlists) off_r0 = __ldg(p.blk_off + 2 * (size_t)c0 + tid);
+        if (tid + blockDim.x <= nlists) off_r1 = __ldg(p.blk_off + 2 * (size_t)c0 + tid + blockDim.x);
+    }
+
+    // ---- weights do not depend on the previous kernel: request the whole slice now
+    const uint32_t H = p.half_blocks;
+    const uint32_t nreg = min(n, (uint32_t)P);
+    const uint32_t nstaged = n - nreg;
+    const uint32_t nrounds = H ? (nstaged + H - 1) / H : 0;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + p.stage_off) + 2 * warp;
+    const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(bars);
+    const uint4 *wstage = reinterpret_cast<const uint4 *>(smem + p.stage_off + 256 + (size_t)warp * p.stage_blocks * 512);
+    const uint32_t wstage_a = (uint32_t)__cvta_generic_to_shared(wstage);
+    const uint4 *slice = p.idx + (size_t)wb0 * 32;
+    auto issue_round = [&](uint32_t r) {          // lane 0 only
+        const uint32_t cnt = min(H, nstaged - r * H);
+        bulk_fetch(wstage_a + (r & 1) * H * 512, slice + (size_t)(nreg + r * H) * 32, cnt * 512u, bar_a + 8 * (r & 1));
+    };
+    if (lane == 0 && nrounds) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a + 8) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue_round(0);
+        if (nrounds > 1) issue_round(1);
+    }
     uint4 buf[P];
 #pragma unroll
     for (int i = 0; i < P; i++)
-        if (wb0 + i < wb1) buf[i] = ld_stream16(src + (size_t)i * 32, ef);
-
-    pdl_launch_dependents();
-    pdl_wait_prior_grid();
+        if ((uint32_t)i < nreg) buf[i] = ld_weights16(slice + (size_t)i * 32 + lane);
 
     // ---- shared memory carve-up
     unsigned char *xs = smem;
@@ -64,92 +149,162 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const NativeParams p)
     uint32_t *hcol_s = reinterpret_cast<uint32_t *>(tail_s + (size_t)nwarps * MT);  // nwarps
     uint32_t *tcol_s = hcol_s + nwarps;
 
+    if (nbl == 0) {
+        if (tid <= nlists) off_s[tid] = off_r0;
+        if (tid + blockDim.x <= nlists) off_s[tid + blockDim.x] = off_r1;
+        for (uint32_t i = tid + 2 * blockDim.x; i <= nlists; i += blockDim.x) off_s[i] = p.blk_off[2 * (size_t)c0 + i];
+    }
+    for (uint32_t i = tid; i < ncols * MT; i += blockDim.x) c_s[i] = acc_t(0);
+    if (!kInt)
+        for (uint32_t i = tid; i < nwarps * MT; i += blockDim.x) { head_s[i] = acc_t(0); tail_s[i] = acc_t(0); }
+
+    pdl_wait_prior_grid();
+    if (tracing) p.trace[blockIdx.x * 8 + 1] = global_ns();
+
     const uint32_t m0 = blockIdx.y * MT;
     const uint32_t mv = min((uint32_t)MT, p.M - m0);
     stage_x<DT, MT>(xs, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
-    for (uint32_t i = threadIdx.x; i <= nlists; i += blockDim.x) off_s[i] = p.blk_off[2 * plan.c0 + i];
-    for (uint32_t i = threadIdx.x; i < ncols * MT; i += blockDim.x) c_s[i] = acc_t(0);
-    for (uint32_t i = threadIdx.x; i < nwarps * MT; i += blockDim.x) { head_s[i] = acc_t(0); tail_s[i] = acc_t(0); }
     __syncthreads();
+    if (tracing) p.trace[blockIdx.x * 8 + 2] = global_ns();
 
-    if (wb0 < wb1) {
-        // list that holds block wb0 / block wb1-1: count boundaries at or below the block
-        uint32_t li = 0, llast = 0;
-        for (uint32_t r = 1; r <= nlists; r += 32) {          // warp-uniform trip count
-            const uint32_t i = r + lane;
-            const uint32_t o = i <= nlists ? off_s[i] : 0xffffffffu;
-            li += __popc(__ballot_sync(0xffffffffu, o <= wb0));
-            llast += __popc(__ballot_sync(0xffffffffu, o <= wb1 - 1));
+    if (n) {
+        // local index (relative to list 2*c0) of the list that holds block wb0, and of wb1-1
+        uint32_t li, llast, bound;
+        if (nbl) {
+            li = wb0 / nbl - 2 * c0;
+            llast = (wb1 - 1) / nbl - 2 * c0;
+            bound = (wb0 / nbl + 1) * nbl;
+        } else {
+            li = 0; llast = 0;
+            for (uint32_t r = 1; r <= nlists; r += 32) {          // warp-uniform trip count
+                const uint32_t i = r + lane;
+                const uint32_t o = i <= nlists ? off_s[i] : 0xffffffffu;
+                li += __popc(__ballot_sync(0xffffffffu, o <= wb0));
+                llast += __popc(__ballot_sync(0xffffffffu, o <= wb1 - 1));
+            }
+            bound = off_s[li + 1];
         }
         const uint32_t first_col = li >> 1, last_col = llast >> 1;
-        if (lane == 0) { hcol_s[warp] = first_col; tcol_s[warp] = last_col; }
+        if (!kInt && lane == 0) { hcol_s[warp] = first_col; tcol_s[warp] = last_col; }
 
         acc_t acc[MT];
 #pragma unroll
         for (int m = 0; m < MT; m++) acc[m] = acc_t(0);
-        uint32_t bound = off_s[li + 1];
         bool dirty = false;
 
         auto flush = [&]() {
             const uint32_t col = li >> 1;
-            acc_t *dst = col == first_col ? head_s + warp * MT : (col == last_col ? tail_s + warp * MT : c_s + col * MT);
 #pragma unroll
             for (int m = 0; m < MT; m++) {
                 acc_t v = warp_sum(acc[m]);
-                if (lane == 0) dst[m] += (li & 1) ? -v : v;
+                v = (li & 1) ? -v : v;
+                if constexpr (kInt) {
+                    if (lane == 0) atomicAdd(reinterpret_cast<int *>(c_s) + col * MT + m, (int)v);
+                } else {
+                    acc_t *dst = col == first_col ? head_s + warp * MT : (col == last_col ? tail_s + warp * MT : c_s + col * MT);
+                    if (lane == 0) dst[m] += v;
+                }
                 acc[m] = acc_t(0);
             }
         };
+        auto consume = [&](const uint4 v, const uint32_t b) {
+            if (b >= bound) {                       // crossed into another list (rare)
+                do {
+                    if (dirty) { flush(); dirty = false; }
+                    li++;
+                    bound = nbl ? bound + nbl : off_s[li + 1];
+                } while (b >= bound);
+            }
+            dirty = true;
+            gather_add<DT, MT>(acc, xs, v.x & 0xffffu);
+            gather_add<DT, MT>(acc, xs, v.x >> 16);
+            gather_add<DT, MT>(acc, xs, v.y & 0xffffu);
+            gather_add<DT, MT>(acc, xs, v.y >> 16);
+            gather_add<DT, MT>(acc, xs, v.z & 0xffffu);
+            gather_add<DT, MT>(acc, xs, v.z >> 16);
+            gather_add<DT, MT>(acc, xs, v.w & 0xffffu);
+            gather_add<DT, MT>(acc, xs, v.w >> 16);
+        };
 
-        for (uint32_t base = wb0; base < wb1; base += P) {
+        // two blocks at once when both lie inside the current list: sixteen independent gathers
+        auto consume2 = [&](const uint4 v0, const uint4 v1, const uint32_t b) {
+            if (b + 1 < bound) {
+                dirty = true;
+                gather_add<DT, MT>(acc, xs, v0.x & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v1.x & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v0.x >> 16);
+                gather_add<DT, MT>(acc, xs, v1.x >> 16);
+                gather_add<DT, MT>(acc, xs, v0.y & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v1.y & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v0.y >> 16);
+                gather_add<DT, MT>(acc, xs, v1.y >> 16);
+                gather_add<DT, MT>(acc, xs, v0.z & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v1.z & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v0.z >> 16);
+                gather_add<DT, MT>(acc, xs, v1.z >> 16);
+                gather_add<DT, MT>(acc, xs, v0.w & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v1.w & 0xffffu);
+                gather_add<DT, MT>(acc, xs, v0.w >> 16);
+                gather_add<DT, MT>(acc, xs, v1.w >> 16);
+            } else {
+                consume(v0, b);
+                consume(v1, b + 1);
+            }
+        };
+
+        // the blocks that came straight into registers
 #pragma unroll
-            for (int i = 0; i < P; i++) {
-                const uint32_t b = base + i;
-                if (b < wb1) {
-                    const uint4 v = buf[i];
-                    if (b + P < wb1) buf[i] = ld_stream16(src + (size_t)(b + P - wb0) * 32, ef);
-                    while (b >= bound) {
-                        if (dirty) { flush(); dirty = false; }
-                        li++;
-                        bound = off_s[li + 1];
-                    }
-                    dirty = true;
-                    gather_add<DT, MT>(acc, xs, v.x & 0xffffu);
-                    gather_add<DT, MT>(acc, xs, v.x >> 16);
-                    gather_add<DT, MT>(acc, xs, v.y & 0xffffu);
-                    gather_add<DT, MT>(acc, xs, v.y >> 16);
-                    gather_add<DT, MT>(acc, xs, v.z & 0xffffu);
-                    gather_add<DT, MT>(acc, xs, v.z >> 16);
-                    gather_add<DT, MT>(acc, xs, v.w & 0xffffu);
-                    gather_add<DT, MT>(acc, xs, v.w >> 16);
+        for (int i = 0; i + 1 < P; i += 2) {
+            if ((uint32_t)i + 1 < nreg) consume2(buf[i], buf[i + 1], wb0 + i);
+            else if ((uint32_t)i < nreg) consume(buf[i], wb0 + i);
+        }
+
+        // the staged blocks, round by round; a finished half is refilled two rounds ahead
+        bool ok = true;
+        for (uint32_t r = 0; r < nrounds; r++) {
+            ok = bounded_wait(bar_a + 8 * (r & 1), (r >> 1) & 1);
+            if (!ok) break;
+            const uint32_t cnt = min(H, nstaged - r * H);
+            const uint4 *half = wstage + (size_t)(r & 1) * H * 32 + lane;
+            const uint32_t bfirst = wb0 + nreg + r * H;
+            uint32_t j = 0;
+            for (; j + 1 < cnt; j += 2) consume2(half[(size_t)j * 32], half[(size_t)(j + 1) * 32], bfirst + j);
+            if (j < cnt) consume(half[(size_t)j * 32], bfirst + j);
+            if (r + 2 < nrounds) {
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    issue_round(r + 2);
                 }
             }
         }
+        if (!ok && lane == 0 && p.status) atomicOr(p.status, 1u);    // report, do not hang
         if (dirty) flush();
-    } else if (lane == 0) {
+    } else if (!kInt && lane == 0) {
         hcol_s[warp] = 0xffffffffu; tcol_s[warp] = 0xffffffffu;
     }
     __syncthreads();
+    if (tracing) p.trace[blockIdx.x * 8 + 3] = global_ns();
 
-    // ---- fold the per-warp edge sums in warp order (one thread per row of the tile)
-    if (threadIdx.x < (uint32_t)MT) {
-        const uint32_t m = threadIdx.x;
-        for (uint32_t w = 0; w < nwarps; w++) {
-            const uint32_t hc = hcol_s[w], tc = tcol_s[w];
-            if (hc != 0xffffffffu) {
-                c_s[hc * MT + m] += head_s[w * MT + m];
-                if (tc != hc) c_s[tc * MT + m] += tail_s[w * MT + m];
+    // ---- write the CTA's columns; floats first fold the per-warp edge sums in warp order
+    acc_t *C = reinterpret_cast<acc_t *>(p.C);
+    for (uint32_t i = tid; i < ncols * mv; i += blockDim.x) {
+        const uint32_t m = i / ncols, col = i - m * ncols;
+        acc_t v = c_s[col * MT + m];
+        if constexpr (!kInt) {
+#pragma unroll
+            for (uint32_t w = 0; w < (uint32_t)kMaxWarps; w++) {
+                if (w < nwarps) {
+                    const uint32_t hc = hcol_s[w], tc = tcol_s[w];
+                    const acc_t hv = head_s[w * MT + m], tv = tail_s[w * MT + m];
+                    v += hc == col ? hv : (tc == col ? tv : acc_t(0));
+                }
             }
         }
+        const size_t o = p.c_colmajor ? (size_t)(c0 + col) * p.M + m0 + m : (size_t)(m0 + m) * p.N + c0 + col;
+        C[o] = v;
     }
-    __syncthreads();
-
-    acc_t *C = reinterpret_cast<acc_t *>(p.C);
-    for (uint32_t i = threadIdx.x; i < ncols * mv; i += blockDim.x) {
-        const uint32_t m = i / ncols, col = i - m * ncols;
-        const size_t o = p.c_colmajor ? (size_t)(plan.c0 + col) * p.M + m0 + m : (size_t)(m0 + m) * p.N + plan.c0 + col;
-        C[o] = c_s[col * MT + m];
-    }
+    if (tracing) p.trace[blockIdx.x * 8 + 4] = global_ns();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -163,7 +318,7 @@ static size_t native_smem(uint32_t K, int rb, int mt, uint32_t max_cols, uint32_
     s += (size_t)max_cols * mt * 4;
     s += 2 * (size_t)nwarps * mt * 4;
     s += 2 * (size_t)nwarps * 4;
-    return s;
+    return (s + 127) & ~(size_t)127;       // the staging area (barriers, then blocks) starts here
 }
 
 template <int DT, int MT, int P, int MINB>
@@ -174,6 +329,8 @@ static int launch_one(const NativeParams &prm, dim3 grid, uint32_t threads, size
     SPTMM_CUDA_TRY(cudaGetDevice(&dev));
     if (configured_device != dev) {
         SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_u16_v256<DT, MT, P, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_u16_v256<DT, MT, P, MINB>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                            cudaSharedmemCarveoutMaxShared));
         configured_device = dev;
     }
     cudaLaunchConfig_t cfg = {};
@@ -186,54 +343,87 @@ static int launch_one(const NativeParams &prm, dim3 grid, uint32_t threads, size
     return SPTMM_OK;
 }
 
-template <int DT>
-static int launch_dtype(const NativeParams &prm, int mt, dim3 grid, uint32_t threads, size_t smem, bool pdl,
-                        cudaStream_t st, int prefetch)
+static int prefetch_depth(int mt)
 {
+    const int t = tune().prefetch;
+    if (mt == 1) return t >= 16 ? 16 : (t <= 4 ? 4 : 8);
+    if (mt == 4) return t <= 4 ? 4 : 8;
+    return mt == 2 ? 8 : 4;
+}
+
+template <int DT>
+static int launch_dtype(const NativeParams &prm, int mt, dim3 grid, uint32_t threads, size_t smem, bool pdl, cudaStream_t st)
+{
+    const int pd = prefetch_depth(mt);
     switch (mt) {
         case 1:
-            if (prefetch >= 16) return launch_one<DT, 1, 16, 1>(prm, grid, threads, smem, pdl, st);
-            if (prefetch <= 4) return launch_one<DT, 1, 4, 2>(prm, grid, threads, smem, pdl, st);
+            if (pd == 16) return launch_one<DT, 1, 16, 1>(prm, grid, threads, smem, pdl, st);
+            if (pd == 4) return launch_one<DT, 1, 4, 2>(prm, grid, threads, smem, pdl, st);
             return launch_one<DT, 1, 8, 2>(prm, grid, threads, smem, pdl, st);
         case 2: return launch_one<DT, 2, 8, 2>(prm, grid, threads, smem, pdl, st);
-        case 4: return launch_one<DT, 4, 8, 2>(prm, grid, threads, smem, pdl, st);
+        case 4:
+            if (pd == 4) return launch_one<DT, 4, 4, 2>(prm, grid, threads, smem, pdl, st);
+            return launch_one<DT, 4, 8, 2>(prm, grid, threads, smem, pdl, st);
         case 8: return launch_one<DT, 8, 4, 1>(prm, grid, threads, smem, pdl, st);
         case 16: return launch_one<DT, 16, 4, 1>(prm, grid, threads, smem, pdl, st);
     }
     return fail(SPTMM_ERR_INVALID, "internal: row tile %d", mt);
 }
 
+static unsigned long long *g_trace = nullptr;
+void set_trace_buffer(unsigned long long *dev_ptr) { g_trace = dev_ptr; }
+
 int launch_native_u16(const GemvArgs &a)
 {
     const sptmm_weights &w = *a.w;
     const int es = (int)dtype_size(a.dtype);
     const uint32_t threads = w.plan.threads, nwarps = threads / 32;
+    if (w.plan.grid > (uint32_t)kMaxGrid || nwarps > (uint32_t)kMaxWarps)
+        return fail(SPTMM_ERR_INVALID, "internal: launch plan %u x %u out of range", w.plan.grid, threads);
     // widest row tile (<= 16 rows, power of two) whose transposed copy of X fits shared memory
+    // beside a minimal staging area (two blocks per warp)
+    const size_t min_stage = 256 + (size_t)nwarps * 2 * 512;
     int mt = 1;
     while (mt < 16 && (uint32_t)mt < a.M) mt *= 2;
-    const size_t cap = 200 * 1024;
-    while (mt > 1 && native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps) > cap) mt /= 2;
-    const size_t smem = native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps);
-    if (smem > 227 * 1024)
+    while (mt > 1 && native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps) + min_stage > 200 * 1024) mt /= 2;
+    const size_t base_smem = native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps);
+    if (base_smem + min_stage > 227 * 1024)
         return fail(SPTMM_ERR_UNSUPPORTED, "gemv: K=%u rows of %d-byte activations do not fit shared memory", w.K, es);
+
+    // staging area: what a warp's slice holds beyond the registers, in one round if the budget
+    // allows (a budget of about half an SM leaves room for the next kernel's CTA), else in
+    // double-buffered rounds of half the room each
+    const uint32_t pd = (uint32_t)prefetch_depth(mt);
+    const uint32_t per_warp = (w.plan.max_cta_blocks + nwarps - 1) / nwarps + 1;
+    const uint32_t need = per_warp > pd ? per_warp - pd : 0;
+    const size_t budget = std::min(std::max((size_t)tune().smem_kb * 1024, base_smem + min_stage), (size_t)227 * 1024);
+    const uint32_t room = (uint32_t)((budget - base_smem - 256) / ((size_t)nwarps * 512));   // blocks per warp
+    const uint32_t half = need == 0 ? 0 : (need <= room ? need : std::max(1u, room / 2));
+    const uint32_t halves = need <= room ? 1 : 2;
+    const size_t smem = base_smem + 256 + (size_t)nwarps * halves * half * 512;
 
     NativeParams prm;
     prm.idx = (const uint4 *)a.arrays[0];
     prm.blk_off = (const uint32_t *)a.arrays[1];
-    prm.plan = (const CtaPlan *)w.plan.d_ctas;
     prm.X = a.X; prm.C = a.C;
+    prm.trace = g_trace;
+    prm.status = (uint32_t *)w.plan.d_status;
     prm.K = w.K; prm.N = w.N; prm.M = a.M;
     prm.max_cols = w.plan.max_cols;
     prm.x_colmajor = (a.flags & SPTMM_X_COLMAJOR) ? 1 : 0;
     prm.c_colmajor = (a.flags & SPTMM_C_COLMAJOR) ? 1 : 0;
-    prm.evict_first = tune().evict_first;
+    prm.uniform_nbl = w.uniform_nbl;
+    prm.half_blocks = half;
+    prm.stage_blocks = halves * half;
+    prm.stage_off = (uint32_t)base_smem;
+    for (uint32_t i = 0; i <= w.plan.grid; i++) { prm.cta_blk[i] = w.plan.cta_blk[i]; prm.cta_col[i] = w.plan.cta_col[i]; }
     const dim3 grid(w.plan.grid, (a.M + mt - 1) / mt, 1);
     const bool pdl = (a.flags & SPTMM_LAUNCH_PDL) != 0;
     cudaStream_t st = (cudaStream_t)a.stream;
     switch (a.dtype) {
-        case SPTMM_I8:  return launch_dtype<SPTMM_I8>(prm, mt, grid, threads, smem, pdl, st, tune().prefetch);
-        case SPTMM_F16: return launch_dtype<SPTMM_F16>(prm, mt, grid, threads, smem, pdl, st, tune().prefetch);
-        case SPTMM_F32: return launch_dtype<SPTMM_F32>(prm, mt, grid, threads, smem, pdl, st, tune().prefetch);
+        case SPTMM_I8:  return launch_dtype<SPTMM_I8>(prm, mt, grid, threads, smem, pdl, st);
+        case SPTMM_F16: return launch_dtype<SPTMM_F16>(prm, mt, grid, threads, smem, pdl, st);
+        case SPTMM_F32: return launch_dtype<SPTMM_F32>(prm, mt, grid, threads, smem, pdl, st);
     }
     return fail(SPTMM_ERR_INVALID, "gemv: unknown dtype %u", a.dtype);
 }

@@ -19,8 +19,7 @@ def _built():
     if not os.path.exists(os.path.join(ROOT, "oracle", "liboracle.so")):
         subprocess.run(["make", "-C", os.path.join(ROOT, "oracle")], check=True, capture_output=True)
     if not os.path.exists(os.path.join(ROOT, "sptmm_b200", "libsptmm.so")):
-        from sptmm_b200 import build as b
-        b.build()
+        subprocess.run([sys.executable, os.path.join(ROOT, "sptmm_b200", "build.py")], check=True)
 
 
 def has_gpu() -> bool:
