@@ -141,6 +141,42 @@ int sptmm_row_split_delta2(const int8_t *X, const uint8_t *W_pos_delta, const ui
 int sptmm_dense_cublas_gemm(const int8_t *X_colmajor, const int8_t *W_dense, int32_t *C_colmajor,
                             uint32_t M, uint32_t K, uint32_t N, void *stream);
 
+/* ---- sequences of matmuls in one launch ----------------------------------------------------- */
+
+/* No counterpart in the reference, which launches one kernel per matmul and synchronises the host
+ * after each (main.cu:994-1458).  A sequence is a fixed list of steps C = X*W (native u16 format,
+ * int8 activations, int32 results, M <= 16) that one persistent kernel runs back to back, with
+ * the next step's weights streaming from HBM while the current one is gathered. */
+typedef struct sptmm_seq sptmm_seq;
+
+typedef struct sptmm_seq_step {
+    const sptmm_weights *w;  /* uploaded to the current device                                   */
+    uint32_t replica;        /* which uploaded copy of w                                          */
+    uint32_t x_kind;         /* 0: X is int8.  1: X (and X2, if set) are int32 results of earlier
+                                steps; their sum is quantised per row to int8 with
+                                q = clamp(rint(v * (127/absmax)), -127, 127) before the matmul    */
+    const void *X;           /* device, M rows of K elements, row stride ldx (0 = K)              */
+    const void *X2;          /* optional second int32 source, row stride ldx2 (0 = K)             */
+    void *C;                 /* device int32, M rows of N, row stride ldc (0 = N)                 */
+    float *scale_out;        /* optional device float[M]: absmax/127 of the quantised rows        */
+    uint32_t ldx, ldx2, ldc;
+    int32_t dep;             /* index of the earlier step whose output this step reads, or -1.
+                                A step starts reading X only after step `dep` has finished on the
+                                whole device.  Buffers are the caller's: a step must not overwrite
+                                memory that a step it does not (transitively) depend on may still
+                                be reading.                                                       */
+} sptmm_seq_step;
+
+int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, sptmm_seq **out);
+/* One cooperative launch on `stream`; asynchronous.  Runs of one sequence must not overlap. */
+int sptmm_seq_run(sptmm_seq *seq, void *stream);
+/* status (if not NULL): waits for the device, then reads the error word a run raises when one of
+ * its bounded waits ran out (0 = all good).  stream_bytes (if not NULL): encoded bytes per run. */
+int sptmm_seq_status(sptmm_seq *seq, uint32_t *status, uint64_t *stream_bytes);
+/* Diagnostics: 4 x uint64 timestamps per step (first 256 steps) from CTA 0; NULL = off. */
+int sptmm_seq_set_trace(sptmm_seq *seq, void *dev_ptr);
+int sptmm_seq_free(sptmm_seq *seq);
+
 /* ---- diagnostics ---------------------------------------------------------------------------- */
 
 /* No counterpart in the reference.  While `dev_ptr` (64 x uint64 of device memory) is set, the

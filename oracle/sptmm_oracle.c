@@ -381,3 +381,32 @@ uint64_t oracle_fnv1a64(const void *p, uint64_t n)
     for (uint64_t i = 0; i < n; i++) { h ^= b[i]; h *= 0x100000001b3ull; }
     return h;
 }
+
+/* Not in the reference (it has no activation quantiser; its X is drawn as int8 directly,
+ * main.cu:787-797).  Defines the quantiser a layer stack needs between matmuls: per row,
+ * amax = max |a+b|, q = clamp(rint((float)(a+b) * (127.0f/(float)amax)), -127, 127) with
+ * single-precision arithmetic and round-to-nearest-even; amax == 0 gives zeros.
+ * scale[m] = amax/127.  B may be NULL. */
+#include <math.h>
+void oracle_quant_absmax_i8(const int32_t *A, uint32_t lda, const int32_t *B, uint32_t ldb,
+                            uint32_t M, uint32_t K, int8_t *out, float *scale)
+{
+    for (uint32_t m = 0; m < M; m++) {
+        int amax = 0;
+        for (uint32_t k = 0; k < K; k++) {
+            int v = A[(uint64_t)m * lda + k] + (B ? B[(uint64_t)m * ldb + k] : 0);
+            int a = v < 0 ? -v : v;
+            if (a > amax) amax = a;
+        }
+        volatile float s = amax ? 127.0f / (float)amax : 0.0f;
+        for (uint32_t k = 0; k < K; k++) {
+            int v = A[(uint64_t)m * lda + k] + (B ? B[(uint64_t)m * ldb + k] : 0);
+            volatile float prod = (float)v * s;
+            int q = (int)rintf(prod);
+            if (q > 127) q = 127;
+            if (q < -127) q = -127;
+            out[(uint64_t)m * K + k] = (int8_t)q;
+        }
+        if (scale) scale[m] = (float)amax / 127.0f;
+    }
+}

@@ -62,6 +62,11 @@ def _load() -> C.CDLL:
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
+        "sptmm_seq_create": (i32, [vp, u32, u32, C.POINTER(vp)]),
+        "sptmm_seq_run": (i32, [vp, vp]),
+        "sptmm_seq_status": (i32, [vp, C.POINTER(u32), C.POINTER(u64)]),
+        "sptmm_seq_set_trace": (i32, [vp, vp]),
+        "sptmm_seq_free": (i32, [vp]),
         "sptmm_set_trace_buffer": (i32, [vp]),
         "sptmm_device_count": (i32, [C.POINTER(C.c_int)]),
         "sptmm_set_device": (i32, [C.c_int]),
@@ -83,6 +88,7 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_host",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
+           "sptmm_seq_create", "sptmm_seq_run", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
 
@@ -178,6 +184,64 @@ class Weights:
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:
             lib.sptmm_weights_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class SeqStep(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("replica", C.c_uint32), ("x_kind", C.c_uint32), ("X", C.c_void_p),
+                ("X2", C.c_void_p), ("C", C.c_void_p), ("scale_out", C.c_void_p),
+                ("ldx", C.c_uint32), ("ldx2", C.c_uint32), ("ldc", C.c_uint32), ("dep", C.c_int32)]
+
+
+class Sequence:
+    """A fixed list of matmul steps run by one persistent kernel (sptmm_seq_* in the C ABI).
+
+    steps: dicts with keys w (Weights), X, C and optionally replica, x_kind, X2, scale_out, ldx,
+    ldx2, ldc, dep (index of the step whose output this one reads; default -1 = none)."""
+
+    def __init__(self, steps, M: int = 1):
+        arr = (SeqStep * len(steps))()
+        self._keep = list(steps)                     # keep tensors and handles alive
+        for a, s in zip(arr, steps):
+            a.w = s["w"]._h
+            a.replica = s.get("replica", 0)
+            a.x_kind = s.get("x_kind", 0)
+            a.X = _ptr(s["X"])
+            a.X2 = _ptr(s["X2"]) if s.get("X2") is not None else None
+            a.C = _ptr(s["C"])
+            a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
+            a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
+            a.dep = s.get("dep", -1)
+        h = C.c_void_p()
+        check(lib.sptmm_seq_create(C.cast(arr, C.c_void_p), len(steps), M, C.byref(h)))
+        self._h = h
+
+    def run(self, stream: int = 0) -> None:
+        check(lib.sptmm_seq_run(self._h, stream))
+
+    def status(self) -> int:
+        st = C.c_uint32(0)
+        check(lib.sptmm_seq_status(self._h, C.byref(st), None))
+        return st.value
+
+    @property
+    def stream_bytes(self) -> int:
+        nb = C.c_uint64(0)
+        check(lib.sptmm_seq_status(self._h, None, C.byref(nb)))
+        return nb.value
+
+    def set_trace(self, dev_tensor) -> None:
+        check(lib.sptmm_seq_set_trace(self._h, _ptr(dev_tensor) if dev_tensor is not None else None))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            lib.sptmm_seq_free(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):

@@ -21,9 +21,10 @@ BIN = os.path.join(PKG, "bin")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"] + ARCH
+NVCC_FLAGS += os.environ.get("SPTMM_NVCC_EXTRA", "").split()      # e.g. -DSPTMM_SEQ_PROFILE for loop timers
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-pthread"]
 
-LIB_SOURCES = ["host_encode.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "cublas_cmp.cu"]
+LIB_SOURCES = ["host_encode.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "kernels_seq.cu", "cublas_cmp.cu"]
 HEADERS = ["internal.h", "device_common.cuh", os.path.join(ROOT, "include", "sptmm.h")]
 
 

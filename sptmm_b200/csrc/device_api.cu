@@ -63,37 +63,40 @@ static void free_device_side(sptmm_weights *w)
 }
 
 // Give each of `grid` CTAs a contiguous run of whole columns holding about total/grid blocks.
-static void make_plan(sptmm_weights *w)
+// off = the 2N+1 list boundaries of a native-format matrix.
+void plan_columns(const uint32_t *off, uint32_t N, uint32_t grid, std::vector<uint32_t> &cta_blk,
+                  std::vector<uint32_t> &cta_col, uint32_t &max_cols, uint32_t &max_cta_blocks)
 {
-    LaunchPlan &pl = w->plan;
-    const Tune &t = tune();
-    pl.grid = std::min<uint32_t>(w->sm_count * t.ctas_per_sm, 1024);
-    pl.cta_blk.clear(); pl.cta_col.clear();
-    pl.threads = t.threads;
-    const uint32_t *off = (const uint32_t *)w->arrays[1].data.data();
-    const uint32_t N = w->N;
-    const uint64_t total = w->total_blocks;
-    pl.ctas.resize(pl.grid);
+    const uint64_t total = off[2 * (size_t)N];
+    cta_blk.clear(); cta_col.clear();
+    max_cols = 1; max_cta_blocks = 0;
     uint32_t c = 0;
-    pl.max_cols = 1;
-    for (uint32_t i = 0; i < pl.grid; i++) {
-        const uint64_t target = total * (i + 1) / pl.grid;
+    for (uint32_t i = 0; i < grid; i++) {
+        const uint64_t target = total * (i + 1) / grid;
         uint32_t c1 = c;
-        if (i + 1 == pl.grid) c1 = N;
+        if (i + 1 == grid) c1 = N;
         else {
             while (c1 < N && off[2 * (size_t)(c1 + 1)] <= target) c1++;
             // take one more column if that lands closer to the target
             if (c1 < N && (int64_t)off[2 * (size_t)(c1 + 1)] - (int64_t)target < (int64_t)target - (int64_t)off[2 * (size_t)c1]) c1++;
         }
-        pl.ctas[i] = CtaPlan{c, c1, off[2 * (size_t)c], off[2 * (size_t)c1]};
-        pl.cta_blk.push_back(off[2 * (size_t)c]);
-        pl.cta_col.push_back(c);
-        pl.max_cols = std::max(pl.max_cols, c1 - c);
-        pl.max_cta_blocks = std::max(pl.max_cta_blocks, off[2 * (size_t)c1] - off[2 * (size_t)c]);
+        cta_blk.push_back(off[2 * (size_t)c]);
+        cta_col.push_back(c);
+        max_cols = std::max(max_cols, c1 - c);
+        max_cta_blocks = std::max(max_cta_blocks, off[2 * (size_t)c1] - off[2 * (size_t)c]);
         c = c1;
     }
-    pl.cta_blk.push_back(off[2 * (size_t)N]);
-    pl.cta_col.push_back(N);
+    cta_blk.push_back(off[2 * (size_t)N]);
+    cta_col.push_back(N);
+}
+
+static void make_plan(sptmm_weights *w)
+{
+    LaunchPlan &pl = w->plan;
+    const Tune &t = tune();
+    pl.grid = std::min<uint32_t>(w->sm_count * t.ctas_per_sm, 1024);
+    pl.threads = t.threads;
+    plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, pl.grid, pl.cta_blk, pl.cta_col, pl.max_cols, pl.max_cta_blocks);
 }
 
 }  // namespace sptmm

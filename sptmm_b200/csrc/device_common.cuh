@@ -53,34 +53,42 @@ __device__ __forceinline__ uint4 ld_stream16(const uint4 *p, uint64_t policy)
 // MT accumulators.  Row K is an all-zero row: padded list entries carry index K.
 template <int RB> struct RowWords { static constexpr int n = RB < 4 ? 1 : RB / 4; };
 
-template <int RB>
-__device__ __forceinline__ void load_row(const unsigned char *xs, uint32_t row, uint32_t (&r)[RowWords<RB>::n])
+// The tile always starts at this absolute address of the CTA's shared window (dynamic shared
+// memory starts at 1024 plus the kernel's static shared memory; kernels skip the gap).  With
+// the base a compile-time constant, a gather is one shared load whose address is row*RB plus an
+// immediate -- no add per gather.
+constexpr uint32_t kXsAbs = 2048;
+
+__device__ __forceinline__ unsigned char *tile_base(unsigned char *dyn_smem)
 {
-    const unsigned char *p = xs + (size_t)row * RB;
-    if constexpr (RB == 1) r[0] = *p;
-    else if constexpr (RB == 2) r[0] = *reinterpret_cast<const uint16_t *>(p);
-    else if constexpr (RB == 4) r[0] = *reinterpret_cast<const uint32_t *>(p);
-    else if constexpr (RB == 8) { uint2 v = *reinterpret_cast<const uint2 *>(p); r[0] = v.x; r[1] = v.y; }
+    return dyn_smem + (kXsAbs - (uint32_t)__cvta_generic_to_shared(dyn_smem));
+}
+
+template <int RB>
+__device__ __forceinline__ void load_row(uint32_t row, uint32_t (&r)[RowWords<RB>::n])
+{
+    const uint32_t a = row * RB;
+    if constexpr (RB == 1) asm volatile("ld.shared.s8 %0, [%1+2048];" : "=r"(r[0]) : "r"(a));
+    else if constexpr (RB == 2) asm volatile("ld.shared.u16 %0, [%1+2048];" : "=r"(r[0]) : "r"(a));
+    else if constexpr (RB == 4) asm volatile("ld.shared.u32 %0, [%1+2048];" : "=r"(r[0]) : "r"(a));
+    else if constexpr (RB == 8) asm volatile("ld.shared.v2.u32 {%0,%1}, [%2+2048];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
     else {
 #pragma unroll
-        for (int i = 0; i < RB / 16; i++) {
-            uint4 v = reinterpret_cast<const uint4 *>(p)[i];
-            r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
-        }
+        for (int i = 0; i < RB / 16; i++)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+2048];"
+                         : "=r"(r[4 * i]), "=r"(r[4 * i + 1]), "=r"(r[4 * i + 2]), "=r"(r[4 * i + 3]) : "r"(a + 16 * i));
     }
 }
 
 template <int DT, int MT>
-__device__ __forceinline__ void gather_add(typename ActTraits<DT>::acc (&acc)[MT], const unsigned char *xs, uint32_t row)
+__device__ __forceinline__ void gather_add(typename ActTraits<DT>::acc (&acc)[MT], uint32_t row)
 {
     constexpr int RB = MT * ActTraits<DT>::size;
-    if constexpr (DT == SPTMM_I8 && MT == 1) {
-        acc[0] += *reinterpret_cast<const int8_t *>(xs + row);      // one sign-extending byte load
-        return;
-    }
     uint32_t r[RowWords<RB>::n];
-    load_row<RB>(xs, row, r);
-    if constexpr (DT == SPTMM_I8) {
+    load_row<RB>(row, r);
+    if constexpr (DT == SPTMM_I8 && MT == 1) {
+        acc[0] += (int32_t)r[0];                                     // the load sign-extends
+    } else if constexpr (DT == SPTMM_I8) {
 #pragma unroll
         for (int m = 0; m < MT; m++) acc[m] += (int32_t)(int8_t)(r[m >> 2] >> (8 * (m & 3)));
     } else if constexpr (DT == SPTMM_F16) {

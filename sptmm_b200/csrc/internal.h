@@ -25,7 +25,6 @@ struct LaunchPlan {                   // derived at upload time from the device'
     uint32_t grid = 0;                // CTAs along x
     uint32_t threads = 0;             // threads per CTA
     uint32_t max_cols = 0;            // most columns any CTA owns
-    std::vector<CtaPlan> ctas;
     std::vector<uint32_t> cta_blk;    // grid+1 block boundaries (passed in kernel parameters)
     std::vector<uint32_t> cta_col;    // grid+1 column boundaries (device copy in d_ctas)
     void *d_ctas = nullptr;
@@ -77,6 +76,8 @@ int launch_div(const void *X, const uint16_t *wp, const uint16_t *wn, void *C, u
 int launch_delta256(const void *X, const uint8_t *dp, const uint8_t *dn, void *C, uint32_t dtype,
                     uint32_t M, uint32_t K, uint32_t N, uint32_t S, uint32_t flags, void *stream);
 void set_trace_buffer(unsigned long long *dev_ptr);
+void plan_columns(const uint32_t *off, uint32_t N, uint32_t grid, std::vector<uint32_t> &cta_blk,
+                  std::vector<uint32_t> &cta_col, uint32_t &max_cols, uint32_t &max_cta_blocks);
 int kernels_init();                   // opt in to >48 KB dynamic shared memory, once per process
 
 inline size_t dtype_size(uint32_t d) { return d == SPTMM_I8 ? 1 : d == SPTMM_F16 ? 2 : 4; }

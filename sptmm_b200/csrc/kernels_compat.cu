@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) k_div(const DivParams p)
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     const uint32_t m0 = blockIdx.y * MT, mv = min((uint32_t)MT, p.M - m0);
-    stage_x<DT, MT>(smem, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
+    stage_x<DT, MT>(tile_base(smem), p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
     __syncthreads();
 
     const uint32_t ngroups = p.N / CPW;
@@ -51,11 +51,11 @@ __global__ void __launch_bounds__(256) k_div(const DivParams p)
 #pragma unroll
             for (int u = 0; u < U; u++) { ip[u] = __ldg(bp + (j + u) * stride); in[u] = __ldg(bn + (j + u) * stride); }
 #pragma unroll
-            for (int u = 0; u < U; u++) { gather_add<DT, MT>(ap, smem, ip[u]); gather_add<DT, MT>(an, smem, in[u]); }
+            for (int u = 0; u < U; u++) { gather_add<DT, MT>(ap, ip[u]); gather_add<DT, MT>(an, in[u]); }
         }
         for (; j < p.chunks; j++) {
-            gather_add<DT, MT>(ap, smem, __ldg(bp + j * stride));
-            gather_add<DT, MT>(an, smem, __ldg(bn + j * stride));
+            gather_add<DT, MT>(ap, __ldg(bp + j * stride));
+            gather_add<DT, MT>(an, __ldg(bn + j * stride));
         }
         const uint32_t col = g * CPW + lane / SPLIT;
 #pragma unroll
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(256) k_delta256(const DeltaParams p)
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     const uint32_t m0 = blockIdx.y * MT, mv = min((uint32_t)MT, p.M - m0);
-    stage_x<DT, MT>(smem, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
+    stage_x<DT, MT>(tile_base(smem), p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
     __syncthreads();
 
     const uint32_t nblk = (p.half + 255) / 256;
@@ -140,8 +140,8 @@ __global__ void __launch_bounds__(256) k_delta256(const DeltaParams p)
             for (int i = 0; i < 8; i++) {
                 const bool valid = e0 + i < p.half;
                 const uint32_t ip = (base_p + sp[i]) & 0xffffu, in = (base_n + sn[i]) & 0xffffu;
-                gather_add<DT, MT>(ap, smem, (valid && ip < p.K) ? ip : p.K);
-                gather_add<DT, MT>(an, smem, (valid && in < p.K) ? in : p.K);
+                gather_add<DT, MT>(ap, (valid && ip < p.K) ? ip : p.K);
+                gather_add<DT, MT>(an, (valid && in < p.K) ? in : p.K);
             }
             const uint32_t tot = __shfl_sync(0xffffffffu, incl, 31);
             carry_p = (carry_p + (tot & 0xffffu)) & 0xffffu;
@@ -284,7 +284,7 @@ int launch_div(const void *X, const uint16_t *wp, const uint16_t *wn, void *C, u
     if ((S & 1) || (S / 2) % split) return fail(SPTMM_ERR_INVALID, "row_split3_small: S/2=%u must be a multiple of split=%u", S / 2, split);
     if (N % (32 / split)) return fail(SPTMM_ERR_INVALID, "row_split3_small: N=%u must be a multiple of %u", N, 32 / split);
     const int es = (int)dtype_size(dtype), mt = pick_row_tile(M, K, es, 8);
-    const size_t smem = xs_bytes(K, mt * es);
+    const size_t smem = xs_bytes(K, mt * es) + 1024;      // room to start the tile at its fixed address
     if (smem > 227 * 1024) return fail(SPTMM_ERR_UNSUPPORTED, "row_split3_small: K=%u does not fit shared memory", K);
     DivParams prm{wp, wn, X, C, K, N, M, (S / 2) / split, (flags & SPTMM_X_COLMAJOR) ? 1u : 0u, (flags & SPTMM_C_COLMAJOR) ? 1u : 0u};
     const uint32_t ngroups = N / (32 / split);
@@ -319,7 +319,7 @@ int launch_delta256(const void *X, const uint8_t *dp, const uint8_t *dn, void *C
     if ((reinterpret_cast<uintptr_t>(dp) | reinterpret_cast<uintptr_t>(dn)) & 7)
         return fail(SPTMM_ERR_INVALID, "row_split_delta2: gap arrays must be 8-byte aligned");
     const int es = (int)dtype_size(dtype), mt = pick_row_tile(M, K, es, 8);
-    const size_t smem = xs_bytes(K, mt * es);
+    const size_t smem = xs_bytes(K, mt * es) + 1024;      // room to start the tile at its fixed address
     if (smem > 227 * 1024) return fail(SPTMM_ERR_UNSUPPORTED, "row_split_delta2: K=%u does not fit shared memory", K);
     DeltaParams prm{dp, dn, X, C, K, N, M, S / 2, (flags & SPTMM_X_COLMAJOR) ? 1u : 0u, (flags & SPTMM_C_COLMAJOR) ? 1u : 0u};
     const dim3 grid((N + 7) / 8, (M + mt - 1) / mt, 1);

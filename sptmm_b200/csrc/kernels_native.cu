@@ -90,9 +90,10 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     using acc_t = typename ActTraits<DT>::acc;
     constexpr int RB = MT * ActTraits<DT>::size;
     constexpr bool kInt = DT == SPTMM_I8;
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(16) unsigned char dyn_smem[];
 
     pdl_launch_dependents();     // the next kernel may start its own weight requests right away
+    unsigned char *smem = tile_base(dyn_smem);     // everything below is laid out from the tile's fixed address
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const uint32_t b0 = p.cta_blk[blockIdx.x], b1 = p.cta_blk[blockIdx.x + 1];
     const uint32_t c0 = p.cta_col[blockIdx.x], c1 = p.cta_col[blockIdx.x + 1];
@@ -216,36 +217,36 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
                 } while (b >= bound);
             }
             dirty = true;
-            gather_add<DT, MT>(acc, xs, v.x & 0xffffu);
-            gather_add<DT, MT>(acc, xs, v.x >> 16);
-            gather_add<DT, MT>(acc, xs, v.y & 0xffffu);
-            gather_add<DT, MT>(acc, xs, v.y >> 16);
-            gather_add<DT, MT>(acc, xs, v.z & 0xffffu);
-            gather_add<DT, MT>(acc, xs, v.z >> 16);
-            gather_add<DT, MT>(acc, xs, v.w & 0xffffu);
-            gather_add<DT, MT>(acc, xs, v.w >> 16);
+            gather_add<DT, MT>(acc, v.x & 0xffffu);
+            gather_add<DT, MT>(acc, v.x >> 16);
+            gather_add<DT, MT>(acc, v.y & 0xffffu);
+            gather_add<DT, MT>(acc, v.y >> 16);
+            gather_add<DT, MT>(acc, v.z & 0xffffu);
+            gather_add<DT, MT>(acc, v.z >> 16);
+            gather_add<DT, MT>(acc, v.w & 0xffffu);
+            gather_add<DT, MT>(acc, v.w >> 16);
         };
 
         // two blocks at once when both lie inside the current list: sixteen independent gathers
         auto consume2 = [&](const uint4 v0, const uint4 v1, const uint32_t b) {
             if (b + 1 < bound) {
                 dirty = true;
-                gather_add<DT, MT>(acc, xs, v0.x & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v1.x & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v0.x >> 16);
-                gather_add<DT, MT>(acc, xs, v1.x >> 16);
-                gather_add<DT, MT>(acc, xs, v0.y & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v1.y & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v0.y >> 16);
-                gather_add<DT, MT>(acc, xs, v1.y >> 16);
-                gather_add<DT, MT>(acc, xs, v0.z & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v1.z & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v0.z >> 16);
-                gather_add<DT, MT>(acc, xs, v1.z >> 16);
-                gather_add<DT, MT>(acc, xs, v0.w & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v1.w & 0xffffu);
-                gather_add<DT, MT>(acc, xs, v0.w >> 16);
-                gather_add<DT, MT>(acc, xs, v1.w >> 16);
+                gather_add<DT, MT>(acc, v0.x & 0xffffu);
+                gather_add<DT, MT>(acc, v1.x & 0xffffu);
+                gather_add<DT, MT>(acc, v0.x >> 16);
+                gather_add<DT, MT>(acc, v1.x >> 16);
+                gather_add<DT, MT>(acc, v0.y & 0xffffu);
+                gather_add<DT, MT>(acc, v1.y & 0xffffu);
+                gather_add<DT, MT>(acc, v0.y >> 16);
+                gather_add<DT, MT>(acc, v1.y >> 16);
+                gather_add<DT, MT>(acc, v0.z & 0xffffu);
+                gather_add<DT, MT>(acc, v1.z & 0xffffu);
+                gather_add<DT, MT>(acc, v0.z >> 16);
+                gather_add<DT, MT>(acc, v1.z >> 16);
+                gather_add<DT, MT>(acc, v0.w & 0xffffu);
+                gather_add<DT, MT>(acc, v1.w & 0xffffu);
+                gather_add<DT, MT>(acc, v0.w >> 16);
+                gather_add<DT, MT>(acc, v1.w >> 16);
             } else {
                 consume(v0, b);
                 consume(v1, b + 1);
@@ -387,7 +388,8 @@ int launch_native_u16(const GemvArgs &a)
     while (mt < 16 && (uint32_t)mt < a.M) mt *= 2;
     while (mt > 1 && native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps) + min_stage > 200 * 1024) mt /= 2;
     const size_t base_smem = native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps);
-    if (base_smem + min_stage > 227 * 1024)
+    const size_t gap = 1024;                  // dynamic shared memory before the tile's fixed address
+    if (gap + base_smem + min_stage > 227 * 1024)
         return fail(SPTMM_ERR_UNSUPPORTED, "gemv: K=%u rows of %d-byte activations do not fit shared memory", w.K, es);
 
     // staging area: what a warp's slice holds beyond the registers, in one round if the budget
@@ -396,11 +398,11 @@ int launch_native_u16(const GemvArgs &a)
     const uint32_t pd = (uint32_t)prefetch_depth(mt);
     const uint32_t per_warp = (w.plan.max_cta_blocks + nwarps - 1) / nwarps + 1;
     const uint32_t need = per_warp > pd ? per_warp - pd : 0;
-    const size_t budget = std::min(std::max((size_t)tune().smem_kb * 1024, base_smem + min_stage), (size_t)227 * 1024);
+    const size_t budget = std::min(std::max((size_t)tune().smem_kb * 1024, base_smem + min_stage), (size_t)226 * 1024);
     const uint32_t room = (uint32_t)((budget - base_smem - 256) / ((size_t)nwarps * 512));   // blocks per warp
     const uint32_t half = need == 0 ? 0 : (need <= room ? need : std::max(1u, room / 2));
     const uint32_t halves = need <= room ? 1 : 2;
-    const size_t smem = base_smem + 256 + (size_t)nwarps * halves * half * 512;
+    const size_t smem = gap + base_smem + 256 + (size_t)nwarps * halves * half * 512;
 
     NativeParams prm;
     prm.idx = (const uint4 *)a.arrays[0];

@@ -1,0 +1,563 @@
+// kernels_seq.cu -- one persistent kernel that runs a whole sequence of ternary matmuls.
+//
+// No counterpart in the reference, which launches one kernel per matmul and synchronises the
+// host after each (main.cu:994-1458).  A kernel boundary costs more than the 3 us a 21 MB
+// matrix needs to stream from HBM, so here a single cooperative launch (one CTA per SM) walks
+// a list of steps; each step is C = X*W for one encoded matrix (native u16 format).
+//
+//  - Weights: every warp owns, for every step, the same contiguous slice of blocks the
+//    per-call kernel gives it, and runs a private ring of 4 KB slots in shared memory filled by
+//    bulk copies (cp.async.bulk + mbarrier).  The ring is refilled as slots are consumed and
+//    runs ahead across step boundaries, so the next matrix streams from HBM while this one is
+//    still being gathered and while the CTAs synchronise.
+//  - Dependencies: a step may wait for an earlier step to have finished on all CTAs (its input
+//    is that step's output).  Each CTA adds 1 to the step's counter after its results are
+//    visible; waiters poll the counter with acquire loads.  Every wait is bounded: if one runs
+//    out, the kernel raises a status word, stops waiting and runs to the end.
+//  - Activations: int8 rows are staged transposed in shared memory as in the per-call kernel.
+//    A step can instead take int32 outputs of earlier steps (optionally the sum of two) and
+//    quantise them on the fly to int8 with a per-row absmax scale, which fuses the activation
+//    quantiser between the layers of a stack into the matmul.
+#include <algorithm>
+#include <cstdlib>
+
+#include "device_common.cuh"
+
+namespace sptmm {
+
+#ifndef SPTMM_SEQ_SLOT_BLOCKS
+#define SPTMM_SEQ_SLOT_BLOCKS 8
+#endif
+constexpr uint32_t kSlotBlocks = SPTMM_SEQ_SLOT_BLOCKS;      // 512-byte blocks per ring slot
+constexpr uint32_t kSlotBytes = kSlotBlocks * 512;
+
+struct SeqDesc {
+    const uint4 *idx;            // encoded blocks of this step's matrix
+    const uint32_t *blk_off;     // its 2N+1 list boundaries
+    const void *X;               // activations: int8 (x_kind 0) or int32 (x_kind 1), row stride ldx
+    const void *X2;              // optional second int32 source added to X (x_kind 1)
+    int32_t *C;                  // output, row stride ldc
+    float *scale_out;            // optional: absmax/127 per row of the quantised input
+    uint32_t K, N, ldx, ldx2, ldc, uniform_nbl, x_kind;
+    int32_t dep;                 // step that must be complete before this one reads X, or -1
+};
+
+struct SeqParams {
+    const SeqDesc *desc;
+    const uint32_t *cta_blk;     // [nsteps][G+1]
+    const uint32_t *cta_col;     // [nsteps][G+1]
+    unsigned long long *counters;
+    uint32_t *status;
+    unsigned long long *trace;   // optional, 4 timestamps per step (first 256 steps) from CTA 0
+    unsigned long long target;   // counters[s] >= target  <=>  step s finished in this run
+    uint32_t nsteps, M, max_cols, ring_slots, xs_bytes, G;
+};
+
+__device__ __forceinline__ unsigned long long seq_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void seq_bulk_fetch(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Non-blocking variant for the producer warp, whose lanes poll different barriers: a blocking
+// try_wait in one lane would stall the copies of all the others.
+__device__ __forceinline__ bool seq_bounded_poll(uint32_t bar, uint32_t parity)
+{
+    uint32_t done = 0;
+    for (uint32_t spin = 0; spin < (1u << 26) && !done; spin++)
+        asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+
+__device__ __forceinline__ bool seq_bounded_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done = 0;
+    for (uint32_t spin = 0; spin < (1u << 22) && !done; spin++)
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+
+// int32 rows (optionally the sum of two sources) -> int8 with a per-row absmax scale:
+// q = clamp(rint(v * (127 / amax)), -127, 127), all in fp32; amax == 0 gives zeros.
+template <int MT>
+__device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &d, uint32_t M, int *red, bool write_scale)
+{
+    const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
+    const int32_t *B = reinterpret_cast<const int32_t *>(d.X2);
+    int8_t *dst = reinterpret_cast<int8_t *>(xs);
+    const uint32_t tid = threadIdx.x, nt = 512, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;   // consumer threads only
+    for (uint32_t m = 0; m < (uint32_t)MT; m++) {
+        if (m >= M) {
+            for (uint32_t k = tid; k < d.K; k += nt) dst[(size_t)k * MT + m] = 0;
+            continue;
+        }
+        int amax = 0;
+        for (uint32_t k = tid; k < d.K; k += nt) {
+            int v = __ldcg(A + (size_t)m * d.ldx + k);
+            if (B) v += __ldcg(B + (size_t)m * d.ldx2 + k);
+            amax = max(amax, abs(v));
+        }
+        amax = __reduce_max_sync(0xffffffffu, amax);
+        asm volatile("bar.sync 1, 512;" ::: "memory");       // red[] free to overwrite (consumer warps only)
+        if (lane == 0) red[warp] = amax;
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        amax = 0;
+        for (uint32_t w = 0; w < nwarps; w++) amax = max(amax, red[w]);
+        const float scale = amax ? 127.0f / (float)amax : 0.0f;
+        for (uint32_t k = tid; k < d.K; k += nt) {
+            int v = __ldcg(A + (size_t)m * d.ldx + k);
+            if (B) v += __ldcg(B + (size_t)m * d.ldx2 + k);
+            int q = __float2int_rn((float)v * scale);
+            q = max(-127, min(127, q));
+            dst[(size_t)k * MT + m] = (int8_t)q;
+        }
+        if (write_scale && d.scale_out && tid == 0) d.scale_out[m] = (float)amax / 127.0f;
+    }
+    if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = 0;          // the zero row
+}
+
+// int8 rows with a row stride, read around L1 (the buffer may have been written by other CTAs)
+template <int MT>
+__device__ __forceinline__ void stage_x_i8(unsigned char *xs, const SeqDesc &d, uint32_t M)
+{
+    const int8_t *X = reinterpret_cast<const int8_t *>(d.X);
+    int8_t *dst = reinterpret_cast<int8_t *>(xs);
+    const uint32_t tid = threadIdx.x, nt = 512;          // consumer threads only
+    if (MT == 1 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) {
+        // every CTA starts at a different place: CTAs released together by a step barrier would
+        // otherwise all ask the same few L2 lines at the same moment
+        const uint32_t vec = d.K / 16, rot = (blockIdx.x * 37u) % max(vec, 1u);
+        for (uint32_t i = tid; i < vec; i += nt) {
+            const uint32_t j = i + rot < vec ? i + rot : i + rot - vec;
+            reinterpret_cast<uint4 *>(xs)[j] = __ldcg(reinterpret_cast<const uint4 *>(X) + j);
+        }
+        for (uint32_t k = vec * 16 + tid; k < d.K; k += nt) dst[k] = __ldcg(X + k);
+    } else {
+        for (uint32_t m = 0; m < (uint32_t)MT; m++)
+            for (uint32_t k = tid; k < d.K; k += nt)
+                dst[(size_t)k * MT + m] = m < M ? __ldcg(X + (size_t)m * d.ldx + k) : (int8_t)0;
+    }
+    if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = 0;
+}
+
+constexpr uint32_t kConsumers = 16;          // consumer warps; warp 16 is the producer
+constexpr uint32_t kConsumerThreads = kConsumers * 32;
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+
+template <int MT>
+__global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_constant__ SeqParams p)
+{
+    extern __shared__ __align__(128) unsigned char dyn_smem[];
+    unsigned char *smem = tile_base(dyn_smem);     // the tile's fixed address; all offsets count from it
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t cta = blockIdx.x, R = p.ring_slots;
+    const bool producer = warp == kConsumers;
+
+    // ---- shared memory: X tile | column sums (two buffers) | scratch | barriers | rings
+    unsigned char *xs = smem;
+    int *c_base = reinterpret_cast<int *>(smem + p.xs_bytes);
+    int *red = c_base + 2 * (size_t)p.max_cols * MT;
+    size_t o = p.xs_bytes + (2 * (size_t)p.max_cols * MT + 32) * 4;
+    o = (o + 7) & ~(size_t)7;
+    const uint32_t bars_a = (uint32_t)__cvta_generic_to_shared(smem + o);     // [warp][full R | empty R]
+    o += (size_t)kConsumers * 2 * R * 8;
+    o = (o + 127) & ~(size_t)127;
+    unsigned char *rings = smem + o;                                           // [warp][R][kSlotBytes]
+    __shared__ uint32_t failed;              // a bounded wait ran out somewhere in this CTA
+    __shared__ __align__(16) uint32_t desc_s[2][(sizeof(SeqDesc) + 15) / 16 * 4];   // this and the next step's descriptor
+    __shared__ uint32_t meta_s[2][4];        // their plan entries: b0, b1, c0, c1
+    if (tid == 0) failed = 0;
+    if (!producer && lane == 0) {
+        for (uint32_t i = 0; i < 2 * R; i++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars_a + (warp * 2 * R + i) * 8) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // ================= producer warp: lane w keeps consumer warp w's ring full =================
+    if (producer) {
+        if (lane >= kConsumers) return;
+        const uint32_t w = lane;
+        const uint32_t full_a = bars_a + w * 2 * R * 8, empty_a = full_a + R * 8;
+        const uint32_t ring_a = (uint32_t)__cvta_generic_to_shared(rings + (size_t)w * R * kSlotBytes);
+        // Lock-step state machine: the 16 lanes poll and issue together, so one instruction of
+        // this warp moves up to 16 rings forward (diverged lanes would serialise ~50 copies a step).
+        uint32_t slot = 0, par = 1;          // parity 1 on a fresh barrier passes: all slots start empty
+        uint32_t s = 0xffffffffu, pb = 0, pend = 0, spins = 0;
+        const uint4 *idx = nullptr;
+        bool done = false;
+        while (true) {
+            if (!done && pb >= pend) {       // move to the next step (one per iteration; empty slices just pass)
+                if (++s >= p.nsteps) done = true;
+                else {
+                    const uint32_t b0 = __ldg(p.cta_blk + (size_t)s * (p.G + 1) + cta);
+                    const uint32_t b1 = __ldg(p.cta_blk + (size_t)s * (p.G + 1) + cta + 1);
+                    idx = p.desc[s].idx;
+                    const uint32_t nb = b1 - b0;
+                    pb = b0 + (uint32_t)(((uint64_t)nb * w) / kConsumers);
+                    pend = b0 + (uint32_t)(((uint64_t)nb * (w + 1)) / kConsumers);
+                }
+            }
+            if (!done && pb < pend) {
+                uint32_t ready;
+                asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                             : "=r"(ready) : "r"(empty_a + slot * 8), "r"(par) : "memory");
+                if (ready) {
+                    const uint32_t cnt = min(kSlotBlocks, pend - pb);
+                    seq_bulk_fetch(ring_a + slot * kSlotBytes, idx + (size_t)pb * 32, cnt * 512u, full_a + slot * 8);
+                    pb += cnt;
+                    if (++slot == R) { slot = 0; par ^= 1; }
+                    spins = 0;
+                } else if (++spins > (1u << 26)) {      // the consumer never freed the slot: report, stop
+                    atomicOr(p.status, 4u);
+                    done = true;
+                }
+            }
+            if (__all_sync(0x0000ffffu, done)) break;
+        }
+        return;
+    }
+
+    // ================= consumer warps =================
+    // threads 0..19 carry one word each of a step's descriptor, threads 32..35 its plan entries
+    auto load_step_word = [&](uint32_t st) -> uint32_t {
+        if (tid < sizeof(SeqDesc) / 4) return __ldg(reinterpret_cast<const uint32_t *>(p.desc + st) + tid);
+        if (tid >= 32 && tid < 36) {
+            const uint32_t *row = (tid < 34 ? p.cta_blk : p.cta_col) + (size_t)st * (p.G + 1) + cta;
+            return __ldg(row + (tid & 1));
+        }
+        return 0;
+    };
+    auto store_step_word = [&](uint32_t st, uint32_t v) {
+        if (tid < sizeof(SeqDesc) / 4) desc_s[st & 1][tid] = v;
+        if (tid >= 32 && tid < 36) meta_s[st & 1][tid - 32] = v;
+    };
+    store_step_word(0, load_step_word(0));
+    consumer_sync();
+    const uint32_t full_a = bars_a + warp * 2 * R * 8, empty_a = full_a + R * 8;
+    const uint4 *ring = reinterpret_cast<const uint4 *>(rings + (size_t)warp * R * kSlotBytes);
+    uint32_t cslot = 0, cpar = 0;            // consumer cursor: slot and phase parity
+    bool ring_ok = true;
+
+    for (uint32_t s = 0; s < p.nsteps; s++) {
+        // descriptor and plan entries of this step: put in shared memory during the previous step
+        const SeqDesc d = *reinterpret_cast<const SeqDesc *>(desc_s[s & 1]);
+        const uint32_t b0 = meta_s[s & 1][0], b1 = meta_s[s & 1][1], c0 = meta_s[s & 1][2], c1 = meta_s[s & 1][3];
+        int *c_s = c_base + (s & 1) * (size_t)p.max_cols * MT;
+        const bool tracing = p.trace != nullptr && cta == 0 && tid == 33 && s < 256;
+        // ---- wait until the step this one depends on has finished everywhere
+        if (d.dep >= 0) {
+            if (tid == 0 && !failed) {
+                const unsigned long long *ctr = p.counters + d.dep;
+                unsigned long long v = 0;
+                for (uint32_t it = 0; it < (1u << 21); it++) {
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
+                    if (v >= p.target) break;
+                    __nanosleep(64);
+                }
+                if (v < p.target) { failed = 1; atomicOr(p.status, 2u); }
+            }
+            consumer_sync();
+        }
+        if (tracing) p.trace[s * 4 + 0] = seq_ns();
+
+        // ---- activations and column sums
+        const uint32_t ncols = c1 - c0;
+        // ask for the next step's descriptor and plan entries now; they are stored after the loop,
+        // so their latency (long right after a step barrier, when every CTA asks the same few
+        // L2 lines) hides behind the gathers
+        uint32_t nxt = 0;
+        if (s + 1 < p.nsteps) nxt = load_step_word(s + 1);
+#ifdef SPTMM_SEQ_PROFILE
+        if (tracing) p.trace[1024 + s * 4 + 0] = seq_ns() + (b0 + c0 == 0xffffffffu);
+#endif
+        if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
+        else stage_x_quant<MT>(xs, d, p.M, red, cta == 0);
+#ifdef SPTMM_SEQ_PROFILE
+        if (tracing) p.trace[1024 + s * 4 + 1] = seq_ns() + (xs[tid] == 77 && xs[tid + 1] == 78 && xs[tid+2] == 99);
+#endif
+        for (uint32_t i = tid; i < ncols * MT; i += kConsumerThreads) c_s[i] = 0;
+        consumer_sync();
+        if (tracing) p.trace[s * 4 + 1] = seq_ns();
+
+        // ---- gather this warp's blocks out of its ring
+        const uint32_t nb = b1 - b0;
+        const uint32_t wb0 = b0 + (uint32_t)(((uint64_t)nb * warp) / kConsumers);
+        const uint32_t wb1 = b0 + (uint32_t)(((uint64_t)nb * (warp + 1)) / kConsumers);
+        if (wb0 < wb1) {
+            const uint32_t nbl = d.uniform_nbl;
+            uint32_t li, bound;
+            if (nbl) {
+                li = wb0 / nbl - 2 * c0;
+                bound = (wb0 / nbl + 1) * nbl;
+            } else {
+                // lists are few per CTA: count boundaries at or below wb0 straight from global
+                li = 0;
+                const uint32_t nlists = 2 * ncols;
+                for (uint32_t r = 1; r <= nlists; r += 32) {
+                    const uint32_t i = r + lane;
+                    const uint32_t ov = i <= nlists ? __ldg(d.blk_off + 2 * (size_t)c0 + i) : 0xffffffffu;
+                    li += __popc(__ballot_sync(0xffffffffu, ov <= wb0));
+                }
+                bound = __ldg(d.blk_off + 2 * (size_t)c0 + li + 1);
+            }
+            int acc[MT];
+#pragma unroll
+            for (int m = 0; m < MT; m++) acc[m] = 0;
+            bool dirty = false;
+            auto flush = [&]() {
+                const uint32_t col = li >> 1;
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    int v = __reduce_add_sync(0xffffffffu, acc[m]);
+                    if (lane == 0) atomicAdd(c_s + col * MT + m, (li & 1) ? -v : v);
+                    acc[m] = 0;
+                }
+            };
+            auto gather8 = [&](const uint4 v) {
+                gather_add<SPTMM_I8, MT>(acc, v.x & 0xffffu);
+                gather_add<SPTMM_I8, MT>(acc, v.x >> 16);
+                gather_add<SPTMM_I8, MT>(acc, v.y & 0xffffu);
+                gather_add<SPTMM_I8, MT>(acc, v.y >> 16);
+                gather_add<SPTMM_I8, MT>(acc, v.z & 0xffffu);
+                gather_add<SPTMM_I8, MT>(acc, v.z >> 16);
+                gather_add<SPTMM_I8, MT>(acc, v.w & 0xffffu);
+                gather_add<SPTMM_I8, MT>(acc, v.w >> 16);
+            };
+            for (uint32_t b = wb0; b < wb1;) {
+                const uint32_t cnt = min(kSlotBlocks, wb1 - b);
+                if (ring_ok) ring_ok = seq_bounded_wait(full_a + cslot * 8, cpar);
+                if (!ring_ok) break;
+                const uint4 *slot = ring + (size_t)cslot * (kSlotBytes / 16) + lane;
+                // runs of blocks that stay inside one list go through a loop with no checks in it
+                for (uint32_t i = 0; i < cnt;) {
+                    if (b + i >= bound) {
+                        do {
+                            if (dirty) { flush(); dirty = false; }
+                            li++;
+                            bound = nbl ? bound + nbl : __ldg(d.blk_off + 2 * (size_t)c0 + li + 1);
+                        } while (b + i >= bound);
+                    }
+                    const uint32_t run = min(cnt - i, bound - (b + i));
+#pragma unroll 2
+                    for (uint32_t j = 0; j < run; j++) gather8(slot[(i + j) * 32]);
+                    dirty = true;
+                    i += run;
+                }
+                b += cnt;
+                __syncwarp();                  // every lane has the slot's data in registers
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_a + cslot * 8) : "memory");
+                if (++cslot == R) { cslot = 0; cpar ^= 1; }
+            }
+            if (!ring_ok && lane == 0) { failed = 1; atomicOr(p.status, 1u); }
+            if (dirty) flush();
+        }
+        if (s + 1 < p.nsteps) store_step_word(s + 1, nxt);
+        consumer_sync();
+        if (tracing) p.trace[s * 4 + 2] = seq_ns();
+
+        // ---- results out, then tell the other CTAs this step is done here.  Warp 0 does it alone
+        // while the others move on (the next step accumulates into the other buffer).
+        if (warp == 0) {
+            for (uint32_t i = lane; i < ncols * p.M; i += 32) {
+                const uint32_t m = i / ncols, col = i - m * ncols;
+                d.C[(size_t)m * d.ldc + c0 + col] = c_s[col * MT + m];
+            }
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence();
+                asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
+            }
+        }
+        if (tracing) p.trace[s * 4 + 3] = seq_ns();
+    }
+}
+
+}  // namespace sptmm
+
+// ---------------------------------------------------------------------------------------------
+using namespace sptmm;
+
+struct sptmm_seq {
+    int device = -1;
+    uint32_t nsteps = 0, M = 0, mt = 0, G = 0, threads = 544, max_cols = 1, ring_slots = 0, xs_bytes = 0;
+    size_t smem = 0;
+    uint64_t stream_bytes = 0;       // encoded bytes one run reads
+    uint64_t epoch = 0;
+    void *d_desc = nullptr, *d_blk = nullptr, *d_col = nullptr, *d_counters = nullptr, *d_status = nullptr;
+    void *d_trace = nullptr;
+};
+
+// Shallow rings stream best: three 4 KB slots per warp reach the HBM rate, deeper ones lose it.
+static size_t seq_ring_cap()
+{
+    const char *e = getenv("SPTMM_SEQ_RING");
+    const int v = e ? atoi(e) : 3;
+    return (size_t)std::max(2, std::min(v, 24));
+}
+
+static void seq_release(sptmm_seq *q)
+{
+    if (!q) return;
+    if (q->device >= 0) {
+        int cur = 0;
+        cudaGetDevice(&cur);
+        cudaSetDevice(q->device);
+        for (void *p : {q->d_desc, q->d_blk, q->d_col, q->d_counters, q->d_status}) if (p) cudaFree(p);
+        cudaSetDevice(cur);
+    }
+    delete q;
+}
+
+extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_t M, sptmm_seq **out)
+{
+    if (!steps || !out || n == 0) return fail(SPTMM_ERR_INVALID, "seq_create: null pointer or empty sequence");
+    *out = nullptr;
+    if (M == 0 || M > 16) return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: M=%u, the sequence kernel blocks 1..16 rows", M);
+    int dev = 0, sms = 0, coop = 0;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    SPTMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    SPTMM_CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+    if (!coop) return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: device cannot launch cooperatively");
+
+    sptmm_seq *q = new (std::nothrow) sptmm_seq();
+    if (!q) return fail(SPTMM_ERR_NOMEM, "seq_create: out of host memory");
+    q->device = dev; q->nsteps = n; q->M = M; q->G = (uint32_t)sms;
+    q->mt = M == 1 ? 1 : (M <= 4 ? 4 : 16);
+    std::vector<SeqDesc> desc(n);
+    std::vector<uint32_t> blk, col, tb, tc;
+    uint32_t kmax = 0;
+    for (uint32_t s = 0; s < n; s++) {
+        const sptmm_seq_step &st = steps[s];
+        const sptmm_weights *w = st.w;
+        int rc = SPTMM_OK;
+        if (!w || !st.X || !st.C) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u has a null pointer", s);
+        else if (w->format != SPTMM_FMT_U16_V256) rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u is not in the native u16 format", s);
+        else if (w->device != dev || st.replica >= w->dev.size()) rc = fail(SPTMM_ERR_STATE, "seq_create: step %u weights are not uploaded to device %d (replica %u)", s, dev, st.replica);
+        else if (st.x_kind > 1) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
+        else if (st.dep >= (int32_t)s) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u depends on step %d, which does not precede it", s, st.dep);
+        if (rc != SPTMM_OK) { seq_release(q); return rc; }
+        SeqDesc &d = desc[s];
+        d.idx = (const uint4 *)w->dev[st.replica][0];
+        d.blk_off = (const uint32_t *)w->dev[st.replica][1];
+        d.X = st.X; d.X2 = st.X2; d.C = (int32_t *)st.C; d.scale_out = st.scale_out;
+        d.K = w->K; d.N = w->N;
+        d.ldx = st.ldx ? st.ldx : w->K; d.ldx2 = st.ldx2 ? st.ldx2 : w->K; d.ldc = st.ldc ? st.ldc : w->N;
+        d.uniform_nbl = w->uniform_nbl; d.x_kind = st.x_kind; d.dep = st.dep < 0 ? -1 : st.dep;
+        uint32_t mc = 1, mb = 0;
+        plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q->G, tb, tc, mc, mb);
+        blk.insert(blk.end(), tb.begin(), tb.end());
+        col.insert(col.end(), tc.begin(), tc.end());
+        q->max_cols = std::max(q->max_cols, mc);
+        kmax = std::max(kmax, w->K);
+        q->stream_bytes += w->stream_bytes;
+    }
+    // shared memory: X tile, column sums + scratch, then as many 1 KB ring slots per warp as fit
+    const uint32_t nwarps = 16;               // consumer warps (one more warp produces)
+    q->xs_bytes = (uint32_t)xs_bytes(kmax, (int)q->mt);
+    size_t fixed = q->xs_bytes + (2 * (size_t)q->max_cols * q->mt + 32) * 4;
+    fixed = (fixed + 7) & ~(size_t)7;
+    const size_t avail = 223 * 1024;      // minus static shared memory and the gap before the tile
+    if (fixed + 128 + (size_t)nwarps * 2 * (kSlotBytes + 16) > avail) {
+        seq_release(q);
+        return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: K=%u with %u-row blocking leaves no room for the weight rings", kmax, q->mt);
+    }
+    q->ring_slots = (uint32_t)std::min<size_t>(seq_ring_cap(), (avail - fixed - 128) / ((size_t)nwarps * (kSlotBytes + 16)));
+    size_t o = fixed + (size_t)nwarps * 2 * q->ring_slots * 8;
+    o = (o + 127) & ~(size_t)127;
+    q->smem = 1024 + o + (size_t)nwarps * q->ring_slots * kSlotBytes;
+
+    cudaError_t e = cudaMalloc(&q->d_desc, n * sizeof(SeqDesc));
+    if (e == cudaSuccess) e = cudaMemcpy(q->d_desc, desc.data(), n * sizeof(SeqDesc), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&q->d_blk, blk.size() * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(q->d_blk, blk.data(), blk.size() * 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&q->d_col, col.size() * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(q->d_col, col.data(), col.size() * 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&q->d_counters, (size_t)n * 8);
+    if (e == cudaSuccess) e = cudaMemset(q->d_counters, 0, (size_t)n * 8);
+    if (e == cudaSuccess) e = cudaMalloc(&q->d_status, 16);
+    if (e == cudaSuccess) e = cudaMemset(q->d_status, 0, 16);
+    if (e != cudaSuccess) { seq_release(q); return fail(SPTMM_ERR_CUDA, "seq_create: %s", cudaGetErrorString(e)); }
+    *out = q;
+    return SPTMM_OK;
+}
+
+template <int MT>
+static int seq_launch(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
+{
+    static int configured_device = -1;
+    if (configured_device != q->device) {
+        SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_seq<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        configured_device = q->device;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(q->G); cfg.blockDim = dim3(q->threads); cfg.dynamicSmemBytes = q->smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;      // all CTAs resident at once, or the launch fails
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    SPTMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, k_seq<MT>, prm));
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
+{
+    if (!q) return fail(SPTMM_ERR_INVALID, "seq_run: null handle");
+    int dev = -1;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != q->device) return fail(SPTMM_ERR_STATE, "seq_run: sequence lives on device %d, current device is %d", q->device, dev);
+    q->epoch++;
+    SeqParams prm;
+    prm.desc = (const SeqDesc *)q->d_desc;
+    prm.cta_blk = (const uint32_t *)q->d_blk;
+    prm.cta_col = (const uint32_t *)q->d_col;
+    prm.counters = (unsigned long long *)q->d_counters;
+    prm.status = (uint32_t *)q->d_status;
+    prm.trace = (unsigned long long *)q->d_trace;
+    prm.target = (unsigned long long)q->G * q->epoch;
+    prm.nsteps = q->nsteps; prm.M = q->M; prm.max_cols = q->max_cols; prm.ring_slots = q->ring_slots;
+    prm.xs_bytes = q->xs_bytes; prm.G = q->G;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (q->mt) {
+        case 1: return seq_launch<1>(q, prm, st);
+        case 4: return seq_launch<4>(q, prm, st);
+        case 16: return seq_launch<16>(q, prm, st);
+    }
+    return fail(SPTMM_ERR_INVALID, "internal: row tile %u", q->mt);
+}
+
+extern "C" int sptmm_seq_status(sptmm_seq *q, uint32_t *status, uint64_t *stream_bytes)
+{
+    if (!q) return fail(SPTMM_ERR_INVALID, "seq_status: null handle");
+    if (status) {
+        SPTMM_CUDA_TRY(cudaDeviceSynchronize());
+        SPTMM_CUDA_TRY(cudaMemcpy(status, q->d_status, 4, cudaMemcpyDeviceToHost));
+    }
+    if (stream_bytes) *stream_bytes = q->stream_bytes;
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_seq_set_trace(sptmm_seq *q, void *dev_ptr)
+{
+    if (!q) return fail(SPTMM_ERR_INVALID, "seq_set_trace: null handle");
+    q->d_trace = dev_ptr;
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_seq_free(sptmm_seq *q)
+{
+    seq_release(q);
+    return SPTMM_OK;
+}

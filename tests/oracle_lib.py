@@ -141,6 +141,7 @@ def i2s_unpack16(word: int) -> np.ndarray:
     return out
 
 
+_lib.oracle_quant_absmax_i8.argtypes = [vp, u32, vp, u32, u32, u32, vp, vp]
 _lib.oracle_fnv1a64.argtypes = [vp, u64]
 _lib.oracle_fnv1a64.restype = u64
 
@@ -148,3 +149,14 @@ _lib.oracle_fnv1a64.restype = u64
 def fnv1a64(a) -> str:
     a = np.ascontiguousarray(a)
     return "%016x" % _lib.oracle_fnv1a64(_p(a), a.nbytes)
+
+
+def quant_absmax_i8(A: np.ndarray, B=None):
+    """A (and optional B): int32 (M, K) possibly strided views; returns (int8 (M,K), float32 scale (M,))."""
+    M, K = A.shape
+    lda = A.strides[0] // 4
+    ldb = B.strides[0] // 4 if B is not None else 0
+    out = np.empty((M, K), dtype=np.int8)
+    scale = np.empty(M, dtype=np.float32)
+    _lib.oracle_quant_absmax_i8(A.ctypes.data, lda, B.ctypes.data if B is not None else None, ldb, M, K, _p(out), _p(scale))
+    return out, scale

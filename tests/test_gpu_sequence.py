@@ -1,0 +1,107 @@
+"""GPU parity tests of the persistent sequence kernel (sptmm_seq_*): independent steps against
+the per-call results and the oracle, dependent chains with the fused int32 -> int8 quantiser
+against an oracle chain, repeated runs, and the fused-shape layer of a BitNet-like stack."""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import sptmm_b200 as sp
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    torch.cuda.set_device(0)
+    yield
+    torch.cuda.synchronize()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("M", [1, 3, 4, 16])
+def test_independent_steps_match_oracle(M):
+    shapes = [(512, 384, 1 / 3), (384, 700, 0.5), (1037, 333, 0.75), (64, 1, 0.2), (700, 40, 1.0)]
+    Ws = [sp.gen_ternary_iid(K, N, p0, 10 + i) for i, (K, N, p0) in enumerate(shapes)]
+    ws = [sp.Weights(W, sp.FMT_U16_V256).upload() for W in Ws]
+    Xs = [O.gen_x_i8(M * K, 20 + i) for i, (K, N, _) in enumerate(shapes)]
+    xd = [dev(x) for x in Xs]
+    outs = [torch.full((M * N,), -5, dtype=torch.int32, device="cuda") for (K, N, _) in shapes]
+    seq = sp.Sequence([{"w": w, "X": x, "C": o} for w, x, o in zip(ws, xd, outs)], M=M)
+    for _ in range(3):                                  # repeated runs reuse the counters
+        for o in outs:
+            o.fill_(-5)
+        seq.run()
+        assert seq.status() == 0
+        for W, X, o in zip(Ws, Xs, outs):
+            assert (o.cpu().numpy().reshape(M, -1) == O.gemv_i8_dense(X, W)).all()
+
+
+def test_full_size_rotating_replicas():
+    K, N, S, M = 6912, 2560, 4096, 1
+    W = sp.gen_ternary_fixed(K, N, S)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload(replicas=4)
+    X = O.gen_x_i8(K, 1)
+    xd = dev(X)
+    outs = [torch.zeros(N, dtype=torch.int32, device="cuda") for _ in range(12)]
+    steps = [{"w": w, "replica": i % 4, "X": xd, "C": o, "dep": i - 1} for i, o in enumerate(outs)]
+    seq = sp.Sequence(steps, M=M)
+    seq.run()
+    assert seq.status() == 0
+    want = O.gemv_i8_dense(X, W).reshape(-1)
+    for o in outs:
+        assert (o.cpu().numpy() == want).all()
+    assert seq.stream_bytes == 12 * w.stream_bytes
+
+
+@pytest.mark.parametrize("M", [1, 4, 9])
+def test_dependent_chain_with_fused_quantiser(M):
+    """x -> W1 -> quant -> W2 (fused two-halves output) -> quant(sum of halves) -> W3."""
+    K1, N1, H, N3 = 512, 384, 320, 200
+    W1 = sp.gen_ternary_iid(K1, N1, 0.4, 1)
+    W2 = sp.gen_ternary_iid(N1, 2 * H, 0.5, 2)          # "gate|up" fused along N
+    W3 = sp.gen_ternary_iid(H, N3, 1 / 3, 3)
+    w1, w2, w3 = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (W1, W2, W3))
+    X = O.gen_x_i8(M * K1, 4)
+    c1 = torch.zeros((M, N1), dtype=torch.int32, device="cuda")
+    c2 = torch.zeros((M, 2 * H), dtype=torch.int32, device="cuda")
+    c3 = torch.zeros((M, N3), dtype=torch.int32, device="cuda")
+    s2 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    s3 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    seq = sp.Sequence([
+        {"w": w1, "X": dev(X), "C": c1},
+        {"w": w2, "X": c1, "C": c2, "x_kind": 1, "dep": 0, "scale_out": s2},
+        {"w": w3, "X": c2, "X2": c2[:, H:], "ldx": 2 * H, "ldx2": 2 * H, "C": c3, "x_kind": 1, "dep": 1, "scale_out": s3},
+    ], M=M)
+    for _ in range(2):
+        seq.run()
+        assert seq.status() == 0
+        r1 = O.gemv_i8_dense(X, W1)
+        q1, sc1 = O.quant_absmax_i8(r1)
+        r2 = O.gemv_i8_dense(q1.reshape(-1), W2)
+        q2, sc2 = O.quant_absmax_i8(r2[:, :H], r2[:, H:])
+        r3 = O.gemv_i8_dense(q2.reshape(-1), W3)
+        assert (c1.cpu().numpy() == r1).all()
+        assert (c2.cpu().numpy() == r2).all()
+        assert (c3.cpu().numpy() == r3).all()
+        assert (s2.cpu().numpy() == sc1).all() and (s3.cpu().numpy() == sc2).all()
+
+
+def test_sequence_errors():
+    W = sp.gen_ternary_iid(256, 64, 0.5, 0)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload()
+    wd = sp.Weights(sp.gen_ternary_fixed(256, 64, 128), sp.FMT_U16_DIV, split=32).upload()
+    x = dev(O.gen_x_i8(256, 1))
+    c = torch.zeros(64, dtype=torch.int32, device="cuda")
+    with pytest.raises(sp.SptmmError):
+        sp.Sequence([{"w": wd, "X": x, "C": c}])                     # not the native format
+    with pytest.raises(sp.SptmmError):
+        sp.Sequence([{"w": w, "X": x, "C": c, "dep": 0}])            # depends on itself
+    with pytest.raises(sp.SptmmError):
+        sp.Sequence([{"w": w, "X": x, "C": c}], M=17)
+    with pytest.raises(sp.SptmmError):
+        sp.Sequence([{"w": sp.Weights(W, sp.FMT_U16_V256), "X": x, "C": c}])   # not uploaded
