@@ -257,6 +257,35 @@ def run_ours(args):
     e2e_us = e2e_s / e2e_calls * 1e6
     e2e_value = nbytes / (e2e_us * 1e-6) / 1e9 * world
 
+    # ---- the same GEMVs as one persistent-kernel sequence (sptmm_seq_*): `chain` makes every
+    # step wait for the previous one device-wide (a layer stack), `independent` does not
+    seq_info = {}
+    if not args.no_seq:
+        nseq = min(calls, 512)
+        for name, dep in (("chain", True), ("independent", False)):
+            steps = [{"w": w, "replica": i % replicas, "X": xd, "C": out[i % replicas], "dep": (i - 1 if dep else -1)}
+                     for i in range(nseq)]
+            seq = sp.Sequence(steps, M=M)
+            with torch.cuda.stream(st):
+                out.zero_()
+                seq.run(st.cuda_stream)
+                st.synchronize()
+                if seq.status() != 0 or not all(np.array_equal(out[r].cpu().numpy(), want) for r in range(replicas)):
+                    raise SystemExit("parity failure in the sequence kernel (%s)" % name)
+                for _ in range(3):
+                    seq.run(st.cuda_stream)
+                st.synchronize()
+                reps = max(4, args.steps // 8)
+                s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s0.record(st)
+                for _ in range(reps):
+                    seq.run(st.cuda_stream)
+                s1.record(st)
+                st.synchronize()
+            sus = s0.elapsed_time(s1) * 1e3 / (reps * nseq)
+            seq_info[name] = {"us_per_gemv": sus, "GBps": nbytes / sus / 1e3, "steps_per_launch": nseq, "launches_timed": reps}
+            seq.close()
+
     line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -276,6 +305,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "GB/s", "us_per_call": e2e_us,
                     "h2d_bytes_per_step": M * K * calls, "d2h_bytes_per_step": M * N * 4 * calls,
                     "calls_timed": e2e_calls, "how": "sptmm_gemv_host per call: pinned H2D, kernel, D2H, stream wait"},
+            "sequence": seq_info,
             "gpu_launches": total_calls,
             "clocks": clocks,
         }
@@ -353,6 +383,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-seq", action="store_true", help="skip the persistent-sequence measurement")
     ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -168,6 +168,21 @@ typedef struct sptmm_seq_step {
 } sptmm_seq_step;
 
 int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, sptmm_seq **out);
+
+/* The same over several GPUs of one node, one process per GPU, each holding a column shard of
+ * every matrix (the reference is single-GPU; no counterpart).  Instead of an all-gather after a
+ * step, every rank's kernel stores its output columns directly into each peer's copy of the
+ * output buffer over NVLink and adds to each peer's step counter; a dependent step waits until
+ * all ranks have reported.  No collective call and no NCCL kernel sits on the data path.
+ *  - C_peers[s*n_peers + p]: where step s's shard starts in rank p's buffer (peer-mapped device
+ *    pointer valid in THIS process, e.g. from CUDA IPC / symmetric memory; p = own rank too).
+ *    Each points at column 0 of this rank's shard inside the full-width row (stride ldc).
+ *  - counter_peers[p]: rank p's array of n_steps uint64 counters, zeroed once before first use,
+ *    peer-mapped likewise.  All ranks must create the same sequence and run it equally often.
+ * steps[].C is ignored when n_peers > 0. */
+int sptmm_seq_create_shared(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M,
+                            void *const *C_peers, void *const *counter_peers, uint32_t n_peers,
+                            uint32_t my_rank, sptmm_seq **out);
 /* One cooperative launch on `stream`; asynchronous.  Runs of one sequence must not overlap. */
 int sptmm_seq_run(sptmm_seq *seq, void *stream);
 /* status (if not NULL): waits for the device, then reads the error word a run raises when one of

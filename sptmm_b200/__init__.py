@@ -63,6 +63,7 @@ def _load() -> C.CDLL:
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
         "sptmm_seq_create": (i32, [vp, u32, u32, C.POINTER(vp)]),
+        "sptmm_seq_create_shared": (i32, [vp, u32, u32, vp, vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_run": (i32, [vp, vp]),
         "sptmm_seq_status": (i32, [vp, C.POINTER(u32), C.POINTER(u64)]),
         "sptmm_seq_set_trace": (i32, [vp, vp]),
@@ -88,7 +89,7 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_host",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
-           "sptmm_seq_create", "sptmm_seq_run", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
+           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_run", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
 
@@ -205,7 +206,9 @@ class Sequence:
     steps: dicts with keys w (Weights), X, C and optionally replica, x_kind, X2, scale_out, ldx,
     ldx2, ldc, dep (index of the step whose output this one reads; default -1 = none)."""
 
-    def __init__(self, steps, M: int = 1):
+    def __init__(self, steps, M: int = 1, counter_peers=None, rank: int = 0):
+        """counter_peers: for a multi-GPU sequence, the peer-mapped addresses of every rank's
+        counter array (len = ranks); each step then carries "C_peers", one address per rank."""
         arr = (SeqStep * len(steps))()
         self._keep = list(steps)                     # keep tensors and handles alive
         for a, s in zip(arr, steps):
@@ -214,12 +217,19 @@ class Sequence:
             a.x_kind = s.get("x_kind", 0)
             a.X = _ptr(s["X"])
             a.X2 = _ptr(s["X2"]) if s.get("X2") is not None else None
-            a.C = _ptr(s["C"])
+            a.C = _ptr(s["C"]) if s.get("C") is not None else None
             a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
             a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
             a.dep = s.get("dep", -1)
         h = C.c_void_p()
-        check(lib.sptmm_seq_create(C.cast(arr, C.c_void_p), len(steps), M, C.byref(h)))
+        if counter_peers is None:
+            check(lib.sptmm_seq_create(C.cast(arr, C.c_void_p), len(steps), M, C.byref(h)))
+        else:
+            n = len(counter_peers)
+            cp = (C.c_void_p * (len(steps) * n))(*[int(a) for s in steps for a in s["C_peers"]])
+            kp = (C.c_void_p * n)(*[int(a) for a in counter_peers])
+            check(lib.sptmm_seq_create_shared(C.cast(arr, C.c_void_p), len(steps), M, C.cast(cp, C.c_void_p),
+                                              C.cast(kp, C.c_void_p), n, rank, C.byref(h)))
         self._h = h
 
     def run(self, stream: int = 0) -> None:

@@ -30,6 +30,7 @@ namespace sptmm {
 #endif
 constexpr uint32_t kSlotBlocks = SPTMM_SEQ_SLOT_BLOCKS;      // 512-byte blocks per ring slot
 constexpr uint32_t kSlotBytes = kSlotBlocks * 512;
+constexpr uint32_t kMaxPeers = 8;                            // GPUs of one node
 
 struct SeqDesc {
     const uint4 *idx;            // encoded blocks of this step's matrix
@@ -40,13 +41,16 @@ struct SeqDesc {
     float *scale_out;            // optional: absmax/127 per row of the quantised input
     uint32_t K, N, ldx, ldx2, ldc, uniform_nbl, x_kind;
     int32_t dep;                 // step that must be complete before this one reads X, or -1
+    int32_t *Cp[kMaxPeers];      // multi-GPU: this shard's place in every rank's output buffer
 };
 
 struct SeqParams {
     const SeqDesc *desc;
     const uint32_t *cta_blk;     // [nsteps][G+1]
     const uint32_t *cta_col;     // [nsteps][G+1]
-    unsigned long long *counters;
+    unsigned long long *counters;           // this rank's step counters
+    unsigned long long *counter_peers[kMaxPeers];   // every rank's (peer-mapped); used when n_peers > 0
+    uint32_t n_peers;            // 0: single GPU
     uint32_t *status;
     unsigned long long *trace;   // optional, 4 timestamps per step (first 256 steps) from CTA 0
     unsigned long long target;   // counters[s] >= target  <=>  step s finished in this run
@@ -231,24 +235,25 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     }
 
     // ================= consumer warps =================
-    // threads 0..19 carry one word each of a step's descriptor, threads 32..35 its plan entries
+    // the first threads carry one word each of a step's descriptor, threads 64..67 its plan entries
     auto load_step_word = [&](uint32_t st) -> uint32_t {
         if (tid < sizeof(SeqDesc) / 4) return __ldg(reinterpret_cast<const uint32_t *>(p.desc + st) + tid);
-        if (tid >= 32 && tid < 36) {
-            const uint32_t *row = (tid < 34 ? p.cta_blk : p.cta_col) + (size_t)st * (p.G + 1) + cta;
+        if (tid >= 64 && tid < 68) {
+            const uint32_t *row = (tid < 66 ? p.cta_blk : p.cta_col) + (size_t)st * (p.G + 1) + cta;
             return __ldg(row + (tid & 1));
         }
         return 0;
     };
     auto store_step_word = [&](uint32_t st, uint32_t v) {
         if (tid < sizeof(SeqDesc) / 4) desc_s[st & 1][tid] = v;
-        if (tid >= 32 && tid < 36) meta_s[st & 1][tid - 32] = v;
+        if (tid >= 64 && tid < 68) meta_s[st & 1][tid - 64] = v;
     };
     store_step_word(0, load_step_word(0));
     consumer_sync();
     const uint32_t full_a = bars_a + warp * 2 * R * 8, empty_a = full_a + R * 8;
     const uint4 *ring = reinterpret_cast<const uint4 *>(rings + (size_t)warp * R * kSlotBytes);
     uint32_t cslot = 0, cpar = 0;            // consumer cursor: slot and phase parity
+    int held_slot = -1;                      // a consumed slot whose release is deferred (see below)
     bool ring_ok = true;
 
     for (uint32_t s = 0; s < p.nsteps; s++) {
@@ -263,15 +268,19 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 const unsigned long long *ctr = p.counters + d.dep;
                 unsigned long long v = 0;
                 for (uint32_t it = 0; it < (1u << 21); it++) {
-                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
+                    if (p.n_peers) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
+                    else asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
                     if (v >= p.target) break;
-                    __nanosleep(64);
                 }
                 if (v < p.target) { failed = 1; atomicOr(p.status, 2u); }
             }
             consumer_sync();
         }
         if (tracing) p.trace[s * 4 + 0] = seq_ns();
+#ifdef SPTMM_SEQ_PROFILE
+        if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
+            p.trace[1024 + 64 + (s - 100) * 16 + warp] = seq_ns();
+#endif
 
         // ---- activations and column sums
         const uint32_t ncols = c1 - c0;
@@ -280,16 +289,18 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         // L2 lines) hides behind the gathers
         uint32_t nxt = 0;
         if (s + 1 < p.nsteps) nxt = load_step_word(s + 1);
-#ifdef SPTMM_SEQ_PROFILE
-        if (tracing) p.trace[1024 + s * 4 + 0] = seq_ns() + (b0 + c0 == 0xffffffffu);
-#endif
         if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
         else stage_x_quant<MT>(xs, d, p.M, red, cta == 0);
 #ifdef SPTMM_SEQ_PROFILE
-        if (tracing) p.trace[1024 + s * 4 + 1] = seq_ns() + (xs[tid] == 77 && xs[tid + 1] == 78 && xs[tid+2] == 99);
+        if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
+            p.trace[1024 + (s - 100) * 16 + warp] = seq_ns() + (xs[tid] == 77 && xs[tid + 1] == 78 && xs[tid + 2] == 99);
 #endif
         for (uint32_t i = tid; i < ncols * MT; i += kConsumerThreads) c_s[i] = 0;
         consumer_sync();
+        if (held_slot >= 0) {                  // X is in: now the previous step's last slot may refill
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_a + held_slot * 8) : "memory");
+            held_slot = -1;
+        }
         if (tracing) p.trace[s * 4 + 1] = seq_ns();
 
         // ---- gather this warp's blocks out of its ring
@@ -358,7 +369,14 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 }
                 b += cnt;
                 __syncwarp();                  // every lane has the slot's data in registers
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_a + cslot * 8) : "memory");
+                // Free the slot for refilling -- except the step's last one, which is handed back only
+                // after the next step's X is staged: its refill would otherwise be in flight to
+                // this SM exactly when the latency-critical X loads are.
+                if (b < wb1) {
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_a + cslot * 8) : "memory");
+                } else {
+                    held_slot = (int)cslot;
+                }
                 if (++cslot == R) { cslot = 0; cpar ^= 1; }
             }
             if (!ring_ok && lane == 0) { failed = 1; atomicOr(p.status, 1u); }
@@ -371,14 +389,25 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         // ---- results out, then tell the other CTAs this step is done here.  Warp 0 does it alone
         // while the others move on (the next step accumulates into the other buffer).
         if (warp == 0) {
-            for (uint32_t i = lane; i < ncols * p.M; i += 32) {
-                const uint32_t m = i / ncols, col = i - m * ncols;
-                d.C[(size_t)m * d.ldc + c0 + col] = c_s[col * MT + m];
-            }
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence();
-                asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
+            if (p.n_peers == 0) {
+                for (uint32_t i = lane; i < ncols * p.M; i += 32) {
+                    const uint32_t m = i / ncols, col = i - m * ncols;
+                    d.C[(size_t)m * d.ldc + c0 + col] = c_s[col * MT + m];
+                }
+                __syncwarp();
+                // the release orders this warp's stores (seen by lane 0 through __syncwarp) before the count
+                if (lane == 0) asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
+            } else {
+                // the exchange: this CTA's columns go straight into every rank's buffer over NVLink
+                // (plain peer stores), then every rank's counter for the step is bumped
+                for (uint32_t i = lane; i < ncols * p.M; i += 32) {
+                    const uint32_t m = i / ncols, col = i - m * ncols;
+                    const int v = c_s[col * MT + m];
+                    for (uint32_t r = 0; r < p.n_peers; r++) d.Cp[r][(size_t)m * d.ldc + c0 + col] = v;
+                }
+                __syncwarp();
+                if (lane < p.n_peers)
+                    asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p.counter_peers[lane] + s) : "memory");
             }
         }
         if (tracing) p.trace[s * 4 + 3] = seq_ns();
@@ -398,6 +427,8 @@ struct sptmm_seq {
     uint64_t epoch = 0;
     void *d_desc = nullptr, *d_blk = nullptr, *d_col = nullptr, *d_counters = nullptr, *d_status = nullptr;
     void *d_trace = nullptr;
+    uint32_t n_peers = 0, my_rank = 0;
+    void *counter_peers[kMaxPeers] = {};
 };
 
 // Shallow rings stream best: three 4 KB slots per warp reach the HBM rate, deeper ones lose it.
@@ -421,10 +452,13 @@ static void seq_release(sptmm_seq *q)
     delete q;
 }
 
-extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_t M, sptmm_seq **out)
+static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, void *const *C_peers,
+                           void *const *counter_peers, uint32_t n_peers, uint32_t my_rank, sptmm_seq **out)
 {
     if (!steps || !out || n == 0) return fail(SPTMM_ERR_INVALID, "seq_create: null pointer or empty sequence");
     *out = nullptr;
+    if (n_peers > kMaxPeers || (n_peers && (!C_peers || !counter_peers || my_rank >= n_peers)))
+        return fail(SPTMM_ERR_INVALID, "seq_create: bad peer arguments (n_peers=%u, rank=%u)", n_peers, my_rank);
     if (M == 0 || M > 16) return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: M=%u, the sequence kernel blocks 1..16 rows", M);
     int dev = 0, sms = 0, coop = 0;
     SPTMM_CUDA_TRY(cudaGetDevice(&dev));
@@ -443,7 +477,7 @@ extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_
         const sptmm_seq_step &st = steps[s];
         const sptmm_weights *w = st.w;
         int rc = SPTMM_OK;
-        if (!w || !st.X || !st.C) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u has a null pointer", s);
+        if (!w || !st.X || (!st.C && !n_peers)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u has a null pointer", s);
         else if (w->format != SPTMM_FMT_U16_V256) rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u is not in the native u16 format", s);
         else if (w->device != dev || st.replica >= w->dev.size()) rc = fail(SPTMM_ERR_STATE, "seq_create: step %u weights are not uploaded to device %d (replica %u)", s, dev, st.replica);
         else if (st.x_kind > 1) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
@@ -456,6 +490,12 @@ extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_
         d.K = w->K; d.N = w->N;
         d.ldx = st.ldx ? st.ldx : w->K; d.ldx2 = st.ldx2 ? st.ldx2 : w->K; d.ldc = st.ldc ? st.ldc : w->N;
         d.uniform_nbl = w->uniform_nbl; d.x_kind = st.x_kind; d.dep = st.dep < 0 ? -1 : st.dep;
+        for (uint32_t r = 0; r < kMaxPeers; r++) d.Cp[r] = r < n_peers ? (int32_t *)C_peers[(size_t)s * n_peers + r] : nullptr;
+        if (n_peers) {
+            for (uint32_t r = 0; r < n_peers; r++)
+                if (!d.Cp[r]) { seq_release(q); return fail(SPTMM_ERR_INVALID, "seq_create: step %u has no output pointer for rank %u", s, r); }
+            d.C = d.Cp[my_rank];
+        }
         uint32_t mc = 1, mb = 0;
         plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q->G, tb, tc, mc, mb);
         blk.insert(blk.end(), tb.begin(), tb.end());
@@ -485,13 +525,33 @@ extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_
     if (e == cudaSuccess) e = cudaMemcpy(q->d_blk, blk.data(), blk.size() * 4, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMalloc(&q->d_col, col.size() * 4);
     if (e == cudaSuccess) e = cudaMemcpy(q->d_col, col.data(), col.size() * 4, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMalloc(&q->d_counters, (size_t)n * 8);
-    if (e == cudaSuccess) e = cudaMemset(q->d_counters, 0, (size_t)n * 8);
+    q->n_peers = n_peers; q->my_rank = my_rank;
+    if (n_peers) {                    // counters live in peer-mapped memory the caller owns and zeroed
+        for (uint32_t r = 0; r < n_peers; r++) {
+            if (!counter_peers[r]) { seq_release(q); return fail(SPTMM_ERR_INVALID, "seq_create: no counters for rank %u", r); }
+            q->counter_peers[r] = counter_peers[r];
+        }
+    } else {
+        if (e == cudaSuccess) e = cudaMalloc(&q->d_counters, (size_t)n * 8);
+        if (e == cudaSuccess) e = cudaMemset(q->d_counters, 0, (size_t)n * 8);
+    }
     if (e == cudaSuccess) e = cudaMalloc(&q->d_status, 16);
     if (e == cudaSuccess) e = cudaMemset(q->d_status, 0, 16);
     if (e != cudaSuccess) { seq_release(q); return fail(SPTMM_ERR_CUDA, "seq_create: %s", cudaGetErrorString(e)); }
     *out = q;
     return SPTMM_OK;
+}
+
+extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_t M, sptmm_seq **out)
+{
+    return seq_create_impl(steps, n, M, nullptr, nullptr, 0, 0, out);
+}
+
+extern "C" int sptmm_seq_create_shared(const sptmm_seq_step *steps, uint32_t n, uint32_t M, void *const *C_peers,
+                                       void *const *counter_peers, uint32_t n_peers, uint32_t my_rank, sptmm_seq **out)
+{
+    if (n_peers == 0) return fail(SPTMM_ERR_INVALID, "seq_create_shared: n_peers must be at least 1");
+    return seq_create_impl(steps, n, M, C_peers, counter_peers, n_peers, my_rank, out);
 }
 
 template <int MT>
@@ -526,7 +586,11 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     prm.counters = (unsigned long long *)q->d_counters;
     prm.status = (uint32_t *)q->d_status;
     prm.trace = (unsigned long long *)q->d_trace;
-    prm.target = (unsigned long long)q->G * q->epoch;
+    prm.n_peers = q->n_peers;
+    for (uint32_t r = 0; r < kMaxPeers; r++) prm.counter_peers[r] = (unsigned long long *)q->counter_peers[r];
+    if (q->n_peers) prm.counters = prm.counter_peers[q->my_rank];
+    // a step is complete once every CTA of every rank has reported
+    prm.target = (unsigned long long)q->G * q->epoch * (q->n_peers ? q->n_peers : 1);
     prm.nsteps = q->nsteps; prm.M = q->M; prm.max_cols = q->max_cols; prm.ring_slots = q->ring_slots;
     prm.xs_bytes = q->xs_bytes; prm.G = q->G;
     cudaStream_t st = (cudaStream_t)stream;

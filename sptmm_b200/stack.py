@@ -1,0 +1,155 @@
+"""A BitNet-b1.58-shaped stack of ternary layers run as one persistent sequence per forward pass.
+
+Plumbing only: this module generates seeded weights, encodes and uploads this rank's column
+shard of every matrix, lays out the activation buffers and builds the step list; all compute is
+the C ABI's sequence kernel (sptmm_seq_*).  The reference has no layer stack, no quantiser and no
+multi-GPU path; the shapes are the ones its dispatch ladders hard-code (main.cu:1107-1190: fused
+qkv N=3840 and gate|up N=13824 at K=2560, down 6912x2560).
+
+Per layer, four dependent steps (int8 activations, int32 results, per-row absmax re-quantisation
+fused into the next step's input stage):
+    qkv  = Wqkv(x)          hidden -> hidden + 2*kv       x: previous layer's `down` output
+    o    = Wo(qkv[:, :hidden])                            (stand-in for attention: the q part)
+    gu   = Wgu(o)           hidden -> 2*ffn               (gate | up fused along N)
+    down = Wdown(gu[:, :ffn] + gu[:, ffn:])               ffn -> hidden
+
+Multi-GPU: every matrix is sharded by contiguous column ranges over the ranks of one node; each
+rank's kernel stores its output columns into every rank's buffers over NVLink and the step
+counters live in the same peer-mapped arena (torch symmetric memory), so a forward pass is still
+one kernel launch per rank with no collective call inside.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+import sptmm_b200 as sp
+
+
+def shard_range(n_cols: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous column range of `rank`; sizes differ by at most one."""
+    return n_cols * rank // world, n_cols * (rank + 1) // world
+
+
+def layer_shapes(hidden: int, ffn: int, kv: int):
+    """(name, K, N) of the four fused matrices of one layer, in execution order."""
+    return [("qkv", hidden, hidden + 2 * kv), ("o", hidden, hidden), ("gu", hidden, 2 * ffn), ("down", ffn, hidden)]
+
+
+def matrix_seed(seed: int, layer: int, which: int) -> int:
+    return (seed * 1000003 + layer * 16 + which) & 0xFFFFFFFFFFFFFFFF
+
+
+def stack_weights(layers: int, hidden: int, ffn: int, kv: int, p_zero: float, seed: int):
+    """Yields (layer, name, W) with W the full (N, K) int8 matrix -- identical on every rank."""
+    for l in range(layers):
+        for i, (name, K, N) in enumerate(layer_shapes(hidden, ffn, kv)):
+            yield l, name, sp.gen_ternary_iid(K, N, p_zero, matrix_seed(seed, l, i))
+
+
+class TernaryStack:
+    def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, M=1, p_zero=1 / 3, seed=0,
+                 rank=0, world=1, group=None, keep_dense=False):
+        import torch
+        self.torch = torch
+        self.layers, self.hidden, self.ffn, self.kv, self.M = layers, hidden, ffn, kv, M
+        self.rank, self.world = rank, world
+        self.dense = [] if keep_dense else None
+        shapes = layer_shapes(hidden, ffn, kv)
+        widths = {name: N for name, _, N in shapes}
+
+        # ---- weights: this rank's columns of every matrix
+        self.weights, self.stream_bytes, self.params = [], 0, 0
+        for l, name, W in stack_weights(layers, hidden, ffn, kv, p_zero, seed):
+            if keep_dense:
+                self.dense.append(W)
+            c0, c1 = shard_range(W.shape[0], rank, world)
+            w = sp.Weights(W[c0:c1], sp.FMT_U16_V256).upload()
+            self.weights.append(w)
+            self.stream_bytes += w.stream_bytes
+            self.params += W.shape[0] * W.shape[1]
+
+        # ---- activation buffers (full width on every rank) and step counters in one arena
+        n_steps = 4 * layers
+        off, cur = {}, 0
+        off["counters"] = cur; cur += n_steps * 8
+        for name in ("qkv", "o", "gu", "down"):
+            cur = (cur + 255) & ~255
+            off[name] = cur; cur += M * widths[name] * 4
+        cur = (cur + 255) & ~255
+        if world > 1:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm
+            self.arena = symm.empty(cur, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+            self.arena.zero_()
+            self.handle = symm.rendezvous(self.arena, group=group if group is not None else dist.group.WORLD)
+            bases = [int(p) for p in self.handle.buffer_ptrs]
+            dist.barrier()
+        else:
+            self.arena = torch.zeros(cur, dtype=torch.uint8, device="cuda")
+            bases = [self.arena.data_ptr()]
+        self.bases, self.off = bases, off
+        mine = bases[rank]
+        self.x_in = torch.zeros(M, hidden, dtype=torch.int8, device="cuda")
+        self.scales = torch.zeros(n_steps, M, dtype=torch.float32, device="cuda")
+
+        # ---- the step list
+        steps = []
+        for l in range(layers):
+            for i, (name, K, N) in enumerate(shapes):
+                s = 4 * l + i
+                c0, _ = shard_range(N, rank, world)
+                st = {"w": self.weights[s], "dep": s - 1, "ldc": N, "scale_out": self.scales[s]}
+                if name == "qkv":
+                    if l == 0:
+                        st.update(X=self.x_in, x_kind=0)
+                    else:
+                        st.update(X=mine + off["down"], x_kind=1, ldx=hidden)
+                elif name == "o":
+                    st.update(X=mine + off["qkv"], x_kind=1, ldx=widths["qkv"])
+                elif name == "gu":
+                    st.update(X=mine + off["o"], x_kind=1, ldx=hidden)
+                else:
+                    st.update(X=mine + off["gu"], X2=mine + off["gu"] + ffn * 4, x_kind=1, ldx=2 * ffn, ldx2=2 * ffn)
+                if world > 1:
+                    st["C_peers"] = [b + off[name] + c0 * 4 for b in bases]
+                else:
+                    st["C"] = mine + off[name] + c0 * 4
+                steps.append(st)
+        counter_peers = [b + off["counters"] for b in bases] if world > 1 else None
+        self.seq = sp.Sequence(steps, M=M, counter_peers=counter_peers, rank=rank)
+        self.n_steps = n_steps
+
+    def set_input(self, x_i8: np.ndarray) -> None:
+        self.x_in.copy_(self.torch.from_numpy(np.ascontiguousarray(x_i8, dtype=np.int8).reshape(self.M, self.hidden)))
+
+    def forward(self, stream: int = 0) -> None:
+        self.seq.run(stream)
+
+    def buffer(self, name: str) -> np.ndarray:
+        """This rank's copy of an activation buffer (int32, M x width), after a synchronise."""
+        width = dict((n, N) for n, _, N in layer_shapes(self.hidden, self.ffn, self.kv))[name]
+        t = self.arena[self.off[name]: self.off[name] + self.M * width * 4].view(self.torch.int32)
+        return t.cpu().numpy().reshape(self.M, width)
+
+    def status(self) -> int:
+        return self.seq.status()
+
+
+def reference_forward(dense, layers, hidden, ffn, kv, x_i8, gemv_dense, quant):
+    """The same chain on the host, given the oracle's dense matmul and quantiser; returns the
+    int32 outputs of the last layer's four steps (for parity tests on small stacks)."""
+    M = x_i8.shape[0]
+    x = np.ascontiguousarray(x_i8, dtype=np.int8)
+    out = {}
+    for l in range(layers):
+        Wqkv, Wo, Wgu, Wd = dense[4 * l: 4 * l + 4]
+        if l > 0:
+            x, _ = quant(out["down"])
+        out["qkv"] = gemv_dense(x.reshape(-1), Wqkv).reshape(M, -1)
+        xq, _ = quant(np.ascontiguousarray(out["qkv"][:, :hidden]))
+        out["o"] = gemv_dense(xq.reshape(-1), Wo).reshape(M, -1)
+        xo, _ = quant(out["o"])
+        out["gu"] = gemv_dense(xo.reshape(-1), Wgu).reshape(M, -1)
+        xg, _ = quant(np.ascontiguousarray(out["gu"][:, :ffn]), np.ascontiguousarray(out["gu"][:, ffn:]))
+        out["down"] = gemv_dense(xg.reshape(-1), Wd).reshape(M, -1)
+    return out
