@@ -286,6 +286,48 @@ def run_ours(args):
             seq_info[name] = {"us_per_gemv": sus, "GBps": nbytes / sus / 1e3, "steps_per_launch": nseq, "launches_timed": reps}
             seq.close()
 
+    # ---- BitNet-2B-shaped layer stack (30 x {qkv, o, gate|up, down}), one persistent kernel per
+    # pass, column-sharded over all ranks with the fused peer-store exchange when world > 1
+    stack_info = {}
+    if not args.no_stack:
+        from sptmm_b200 import stack as stack_mod
+        w.close()                                   # free the GEMV replicas first
+        del out
+        torch.cuda.empty_cache()
+        for m_rows in (1, 4, 16):
+            stk = stack_mod.TernaryStack(args.stack_layers, 2560, 6912, 640, M=m_rows, p_zero=1 / 3, seed=0, rank=rank, world=world)
+            stk.set_input(O.gen_x_i8(m_rows * 2560, 5).reshape(m_rows, 2560))
+            with torch.cuda.stream(st):
+                for _ in range(3):
+                    if world > 1:
+                        dist.barrier()
+                    stk.forward(st.cuda_stream)
+                    st.synchronize()
+                ok = stk.status() == 0
+                if world > 1:
+                    dist.barrier()
+                passes = 20
+                s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s0.record(st)
+                for _ in range(passes):
+                    stk.forward(st.cuda_stream)
+                s1.record(st)
+                st.synchronize()
+            sms = s0.elapsed_time(s1) / passes
+            total_bytes = float(stk.stream_bytes)
+            if world > 1:
+                t = torch.tensor([sms, -total_bytes, 0.0 if ok else 1.0], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                sms = float(t[0].item()); ok = ok and float(t[2].item()) == 0.0
+                tb = torch.tensor([total_bytes], dtype=torch.float64, device="cuda")
+                dist.all_reduce(tb)
+                total_bytes = float(tb.item())
+            stack_info["M%d" % m_rows] = {"us_per_pass": sms * 1e3, "tokens_per_s": m_rows / (sms * 1e-3),
+                                          "encoded_GB": total_bytes / 1e9, "GBps_all_gpus": total_bytes / (sms * 1e-3) / 1e9,
+                                          "status_ok": ok, "layers": args.stack_layers, "steps_per_pass": stk.n_steps}
+            del stk
+            torch.cuda.empty_cache()
+
     line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -306,6 +348,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": M * K * calls, "d2h_bytes_per_step": M * N * 4 * calls,
                     "calls_timed": e2e_calls, "how": "sptmm_gemv_host per call: pinned H2D, kernel, D2H, stream wait"},
             "sequence": seq_info,
+            "stack": stack_info,
             "gpu_launches": total_calls,
             "clocks": clocks,
         }
@@ -384,6 +427,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-seq", action="store_true", help="skip the persistent-sequence measurement")
+    ap.add_argument("--no-stack", action="store_true", help="skip the layer-stack measurement")
+    ap.add_argument("--stack-layers", type=int, default=30)
     ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -28,8 +28,8 @@ namespace sptmm {
 #ifndef SPTMM_SEQ_SLOT_BLOCKS
 #define SPTMM_SEQ_SLOT_BLOCKS 8
 #endif
-constexpr uint32_t kSlotBlocks = SPTMM_SEQ_SLOT_BLOCKS;      // 512-byte blocks per ring slot
-constexpr uint32_t kSlotBytes = kSlotBlocks * 512;
+constexpr uint32_t kMaxSlotBlocks = SPTMM_SEQ_SLOT_BLOCKS;   // 512-byte blocks per ring slot (4 KB streams best;
+                                                             // smaller only when the X tile leaves less room)
 constexpr uint32_t kMaxPeers = 8;                            // GPUs of one node
 
 struct SeqDesc {
@@ -55,12 +55,18 @@ struct SeqParams {
     unsigned long long *trace;   // optional, 4 timestamps per step (first 256 steps) from CTA 0
     unsigned long long target;   // counters[s] >= target  <=>  step s finished in this run
     uint32_t nsteps, M, max_cols, ring_slots, xs_bytes, G;
+    uint32_t slot_blocks;        // 512-byte blocks per ring slot
 };
 
-__device__ __forceinline__ unsigned long long seq_ns()
+// Timestamp for the optional trace.  A bare read of %globaltimer is hoisted by the assembler
+// (it was seen moving above barriers); guarding it with a predicate computed from a volatile
+// shared-memory load pins it behind whatever that load is ordered after.
+__device__ __forceinline__ unsigned long long seq_ns(const volatile uint32_t *anchor)
 {
+    const uint32_t v = *anchor;
     unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    asm volatile("{ .reg .pred p; setp.ne.u32 p, %1, 0xdeadbeef; @p mov.u64 %0, %globaltimer; @!p mov.u64 %0, 0; }"
+                 : "=l"(t) : "r"(v) : "memory");
     return t;
 }
 
@@ -100,6 +106,52 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
     const int32_t *B = reinterpret_cast<const int32_t *>(d.X2);
     int8_t *dst = reinterpret_cast<int8_t *>(xs);
     const uint32_t tid = threadIdx.x, nt = 512, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;   // consumer threads only
+    constexpr int V = 28;                      // values a thread keeps per row: covers K <= 14336
+    if (d.K <= (uint32_t)V * nt) {
+        // One pass: the row's values stay in registers between the absmax and the rounding, so
+        // the input is read once and a row costs one load latency and one barrier.
+        for (uint32_t m = 0; m < (uint32_t)MT; m++) {
+            if (m >= M) {
+                for (uint32_t k = tid; k < d.K; k += nt) dst[(size_t)k * MT + m] = 0;
+                continue;
+            }
+            int v[V];
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+                const uint32_t k = tid + j * nt;
+                v[j] = k < d.K ? __ldcg(A + (size_t)m * d.ldx + k) : 0;
+            }
+            if (B) {
+#pragma unroll
+                for (int j = 0; j < V; j++) {
+                    const uint32_t k = tid + j * nt;
+                    if (k < d.K) v[j] += __ldcg(B + (size_t)m * d.ldx2 + k);
+                }
+            }
+            int amax = 0;
+#pragma unroll
+            for (int j = 0; j < V; j++) amax = max(amax, abs(v[j]));
+            amax = __reduce_max_sync(0xffffffffu, amax);
+            int *slot = red + (m & 1) * 16;                       // alternate halves: one barrier per row
+            if (lane == 0) slot[warp] = amax;
+            asm volatile("bar.sync 1, 512;" ::: "memory");
+            amax = 0;
+            for (uint32_t w = 0; w < nwarps; w++) amax = max(amax, slot[w]);
+            const float scale = amax ? 127.0f / (float)amax : 0.0f;
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+                const uint32_t k = tid + j * nt;
+                if (k < d.K) {
+                    int q = __float2int_rn((float)v[j] * scale);
+                    q = max(-127, min(127, q));
+                    dst[(size_t)k * MT + m] = (int8_t)q;
+                }
+            }
+            if (write_scale && d.scale_out && tid == 0) d.scale_out[m] = (float)amax / 127.0f;
+        }
+        if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = 0;      // the zero row
+        return;
+    }
     for (uint32_t m = 0; m < (uint32_t)MT; m++) {
         if (m >= M) {
             for (uint32_t k = tid; k < d.K; k += nt) dst[(size_t)k * MT + m] = 0;
@@ -166,6 +218,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     unsigned char *smem = tile_base(dyn_smem);     // the tile's fixed address; all offsets count from it
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t cta = blockIdx.x, R = p.ring_slots;
+    const uint32_t slot_blocks = p.slot_blocks, slot_bytes = slot_blocks * 512;
     const bool producer = warp == kConsumers;
 
     // ---- shared memory: X tile | column sums (two buffers) | scratch | barriers | rings
@@ -177,7 +230,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     const uint32_t bars_a = (uint32_t)__cvta_generic_to_shared(smem + o);     // [warp][full R | empty R]
     o += (size_t)kConsumers * 2 * R * 8;
     o = (o + 127) & ~(size_t)127;
-    unsigned char *rings = smem + o;                                           // [warp][R][kSlotBytes]
+    unsigned char *rings = smem + o;                                           // [warp][R][slot_bytes]
     __shared__ uint32_t failed;              // a bounded wait ran out somewhere in this CTA
     __shared__ __align__(16) uint32_t desc_s[2][(sizeof(SeqDesc) + 15) / 16 * 4];   // this and the next step's descriptor
     __shared__ uint32_t meta_s[2][4];        // their plan entries: b0, b1, c0, c1
@@ -195,7 +248,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         if (lane >= kConsumers) return;
         const uint32_t w = lane;
         const uint32_t full_a = bars_a + w * 2 * R * 8, empty_a = full_a + R * 8;
-        const uint32_t ring_a = (uint32_t)__cvta_generic_to_shared(rings + (size_t)w * R * kSlotBytes);
+        const uint32_t ring_a = (uint32_t)__cvta_generic_to_shared(rings + (size_t)w * R * slot_bytes);
         // Lock-step state machine: the 16 lanes poll and issue together, so one instruction of
         // this warp moves up to 16 rings forward (diverged lanes would serialise ~50 copies a step).
         uint32_t slot = 0, par = 1;          // parity 1 on a fresh barrier passes: all slots start empty
@@ -219,8 +272,8 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                              : "=r"(ready) : "r"(empty_a + slot * 8), "r"(par) : "memory");
                 if (ready) {
-                    const uint32_t cnt = min(kSlotBlocks, pend - pb);
-                    seq_bulk_fetch(ring_a + slot * kSlotBytes, idx + (size_t)pb * 32, cnt * 512u, full_a + slot * 8);
+                    const uint32_t cnt = min(slot_blocks, pend - pb);
+                    seq_bulk_fetch(ring_a + slot * slot_bytes, idx + (size_t)pb * 32, cnt * 512u, full_a + slot * 8);
                     pb += cnt;
                     if (++slot == R) { slot = 0; par ^= 1; }
                     spins = 0;
@@ -251,7 +304,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     store_step_word(0, load_step_word(0));
     consumer_sync();
     const uint32_t full_a = bars_a + warp * 2 * R * 8, empty_a = full_a + R * 8;
-    const uint4 *ring = reinterpret_cast<const uint4 *>(rings + (size_t)warp * R * kSlotBytes);
+    const uint4 *ring = reinterpret_cast<const uint4 *>(rings + (size_t)warp * R * slot_bytes);
     uint32_t cslot = 0, cpar = 0;            // consumer cursor: slot and phase parity
     int held_slot = -1;                      // a consumed slot whose release is deferred (see below)
     bool ring_ok = true;
@@ -276,10 +329,10 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             }
             consumer_sync();
         }
-        if (tracing) p.trace[s * 4 + 0] = seq_ns();
+        if (tracing) p.trace[s * 4 + 0] = seq_ns(&failed);
 #ifdef SPTMM_SEQ_PROFILE
         if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
-            p.trace[1024 + 64 + (s - 100) * 16 + warp] = seq_ns();
+            p.trace[1024 + 64 + (s - 100) * 16 + warp] = seq_ns(&failed);
 #endif
 
         // ---- activations and column sums
@@ -293,7 +346,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         else stage_x_quant<MT>(xs, d, p.M, red, cta == 0);
 #ifdef SPTMM_SEQ_PROFILE
         if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
-            p.trace[1024 + (s - 100) * 16 + warp] = seq_ns() + (xs[tid] == 77 && xs[tid + 1] == 78 && xs[tid + 2] == 99);
+            p.trace[1024 + (s - 100) * 16 + warp] = seq_ns(&failed) + (xs[tid] == 77 && xs[tid + 1] == 78 && xs[tid + 2] == 99);
 #endif
         for (uint32_t i = tid; i < ncols * MT; i += kConsumerThreads) c_s[i] = 0;
         consumer_sync();
@@ -301,7 +354,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_a + held_slot * 8) : "memory");
             held_slot = -1;
         }
-        if (tracing) p.trace[s * 4 + 1] = seq_ns();
+        if (tracing) p.trace[s * 4 + 1] = seq_ns(&failed);
 
         // ---- gather this warp's blocks out of its ring
         const uint32_t nb = b1 - b0;
@@ -348,10 +401,10 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 gather_add<SPTMM_I8, MT>(acc, v.w >> 16);
             };
             for (uint32_t b = wb0; b < wb1;) {
-                const uint32_t cnt = min(kSlotBlocks, wb1 - b);
+                const uint32_t cnt = min(slot_blocks, wb1 - b);
                 if (ring_ok) ring_ok = seq_bounded_wait(full_a + cslot * 8, cpar);
                 if (!ring_ok) break;
-                const uint4 *slot = ring + (size_t)cslot * (kSlotBytes / 16) + lane;
+                const uint4 *slot = ring + (size_t)cslot * (slot_bytes / 16) + lane;
                 // runs of blocks that stay inside one list go through a loop with no checks in it
                 for (uint32_t i = 0; i < cnt;) {
                     if (b + i >= bound) {
@@ -384,7 +437,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         }
         if (s + 1 < p.nsteps) store_step_word(s + 1, nxt);
         consumer_sync();
-        if (tracing) p.trace[s * 4 + 2] = seq_ns();
+        if (tracing) p.trace[s * 4 + 2] = seq_ns(&failed);
 
         // ---- results out, then tell the other CTAs this step is done here.  Warp 0 does it alone
         // while the others move on (the next step accumulates into the other buffer).
@@ -410,7 +463,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                     asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p.counter_peers[lane] + s) : "memory");
             }
         }
-        if (tracing) p.trace[s * 4 + 3] = seq_ns();
+        if (tracing) p.trace[s * 4 + 3] = seq_ns(&failed);
     }
 }
 
@@ -421,7 +474,7 @@ using namespace sptmm;
 
 struct sptmm_seq {
     int device = -1;
-    uint32_t nsteps = 0, M = 0, mt = 0, G = 0, threads = 544, max_cols = 1, ring_slots = 0, xs_bytes = 0;
+    uint32_t nsteps = 0, M = 0, mt = 0, G = 0, threads = 544, max_cols = 1, ring_slots = 0, xs_bytes = 0, slot_blocks = 8;
     size_t smem = 0;
     uint64_t stream_bytes = 0;       // encoded bytes one run reads
     uint64_t epoch = 0;
@@ -510,14 +563,20 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
     size_t fixed = q->xs_bytes + (2 * (size_t)q->max_cols * q->mt + 32) * 4;
     fixed = (fixed + 7) & ~(size_t)7;
     const size_t avail = 223 * 1024;      // minus static shared memory and the gap before the tile
-    if (fixed + 128 + (size_t)nwarps * 2 * (kSlotBytes + 16) > avail) {
+    // 4 KB slots stream best; halve them while three of them per warp do not fit beside the X tile
+    uint32_t slot_blocks = kMaxSlotBlocks;
+    while (slot_blocks > 1 && fixed + 128 + (size_t)nwarps * 3 * (slot_blocks * 512 + 16) > avail) slot_blocks /= 2;
+    const size_t slot_bytes = (size_t)slot_blocks * 512;
+    q->slot_blocks = slot_blocks;
+    if (fixed + 128 + (size_t)nwarps * 2 * (slot_bytes + 16) > avail) {
+        const uint32_t mt = q->mt;
         seq_release(q);
-        return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: K=%u with %u-row blocking leaves no room for the weight rings", kmax, q->mt);
+        return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: K=%u with %u-row blocking leaves no room for the weight rings", kmax, mt);
     }
-    q->ring_slots = (uint32_t)std::min<size_t>(seq_ring_cap(), (avail - fixed - 128) / ((size_t)nwarps * (kSlotBytes + 16)));
+    q->ring_slots = (uint32_t)std::min<size_t>(seq_ring_cap(), (avail - fixed - 128) / ((size_t)nwarps * (slot_bytes + 16)));
     size_t o = fixed + (size_t)nwarps * 2 * q->ring_slots * 8;
     o = (o + 127) & ~(size_t)127;
-    q->smem = 1024 + o + (size_t)nwarps * q->ring_slots * kSlotBytes;
+    q->smem = 1024 + o + (size_t)nwarps * q->ring_slots * slot_bytes;
 
     cudaError_t e = cudaMalloc(&q->d_desc, n * sizeof(SeqDesc));
     if (e == cudaSuccess) e = cudaMemcpy(q->d_desc, desc.data(), n * sizeof(SeqDesc), cudaMemcpyHostToDevice);
@@ -592,7 +651,7 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     // a step is complete once every CTA of every rank has reported
     prm.target = (unsigned long long)q->G * q->epoch * (q->n_peers ? q->n_peers : 1);
     prm.nsteps = q->nsteps; prm.M = q->M; prm.max_cols = q->max_cols; prm.ring_slots = q->ring_slots;
-    prm.xs_bytes = q->xs_bytes; prm.G = q->G;
+    prm.xs_bytes = q->xs_bytes; prm.G = q->G; prm.slot_blocks = q->slot_blocks;
     cudaStream_t st = (cudaStream_t)stream;
     switch (q->mt) {
         case 1: return seq_launch<1>(q, prm, st);
