@@ -188,6 +188,25 @@ int sptmm_seq_run(sptmm_seq *seq, void *stream);
 /* status (if not NULL): waits for the device, then reads the error word a run raises when one of
  * its bounded waits ran out (0 = all good).  stream_bytes (if not NULL): encoded bytes per run. */
 int sptmm_seq_status(sptmm_seq *seq, uint32_t *status, uint64_t *stream_bytes);
+/* No counterpart in the reference.  Runs a sequence of at most 16 steps WITHOUT allocating any
+ * device memory: for callers that cannot call cudaMalloc when they need the result -- code inside
+ * a closed, pre-sized memory pool, a real-time loop that may not block on the allocator, a host
+ * framework that owns the whole device.  The sequence kernel's scratch (step descriptors, per-CTA
+ * plan, step counters, status word; about 36 KB) lives in a fixed array inside the library image
+ * instead, which every GPU that loads the library holds until the process exits.
+ *  - steps / M / stream as for sptmm_seq_create + sptmm_seq_run; weights must already be uploaded
+ *    (that upload allocates; this call does not).  More than 16 steps, or a device with more than
+ *    256 SMs, is refused with SPTMM_ERR_INVALID / SPTMM_ERR_UNSUPPORTED.
+ *  - The first call on a device looks the array's device address up and sets kernel attributes;
+ *    make that first call outside any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents (the counters and the
+ *    status word are cleared at every call): two calls whose kernels overlap on the GPU race.
+ *    Serialise them on one stream.
+ *  - status_out == NULL: asynchronous.  Otherwise the call waits for the stream, stores the error
+ *    word there (0 = all bounded waits were met) and returns SPTMM_ERR_STATE if it is not 0. */
+int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, void *stream,
+                         uint32_t *status_out);
+
 /* Diagnostics: 4 x uint64 timestamps per step (first 256 steps) from CTA 0; NULL = off. */
 int sptmm_seq_set_trace(sptmm_seq *seq, void *dev_ptr);
 int sptmm_seq_free(sptmm_seq *seq);

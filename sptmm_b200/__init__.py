@@ -65,6 +65,7 @@ def _load() -> C.CDLL:
         "sptmm_seq_create": (i32, [vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_create_shared": (i32, [vp, u32, u32, vp, vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_run": (i32, [vp, vp]),
+        "sptmm_seq_run_static": (i32, [vp, u32, u32, vp, C.POINTER(u32)]),
         "sptmm_seq_status": (i32, [vp, C.POINTER(u32), C.POINTER(u64)]),
         "sptmm_seq_set_trace": (i32, [vp, vp]),
         "sptmm_seq_free": (i32, [vp]),
@@ -89,7 +90,7 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_host",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
-           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_run", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
+           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
 
@@ -269,6 +270,26 @@ def row_split3_small(X, W_pos_div, W_neg_div, out, M: int, K: int, N: int, S: in
 def row_split_delta2(X, W_pos_delta, W_neg_delta, out, M: int, K: int, N: int, S: int, split: int = 32, stream: int = 0) -> None:
     """Raw-pointer form of the reference's -row_split_delta2 launch (main.cu:599-764)."""
     check(lib.sptmm_row_split_delta2(_ptr(X), _ptr(W_pos_delta), _ptr(W_neg_delta), _ptr(out), M, K, N, S, split, stream))
+
+
+def run_sequence_static(steps, M: int = 1, stream: int = 0, wait: bool = True) -> int:
+    """sptmm_seq_run_static: run up to 16 steps (dicts as for Sequence) without allocating device
+    memory -- for callers that may not call cudaMalloc at that point; the kernel's scratch is a
+    fixed array inside the library.  With wait=True the call waits and returns the status word."""
+    arr = (SeqStep * len(steps))()
+    for a, s in zip(arr, steps):
+        a.w = s["w"]._h
+        a.replica = s.get("replica", 0)
+        a.x_kind = s.get("x_kind", 0)
+        a.X = _ptr(s["X"])
+        a.X2 = _ptr(s["X2"]) if s.get("X2") is not None else None
+        a.C = _ptr(s["C"])
+        a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
+        a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
+        a.dep = s.get("dep", -1)
+    st = C.c_uint32(0)
+    check(lib.sptmm_seq_run_static(C.cast(arr, C.c_void_p), len(steps), M, stream, C.byref(st) if wait else None))
+    return st.value
 
 
 def dense_cublas_gemm(X_colmajor, W_dense, out_colmajor, M: int, K: int, N: int, stream: int = 0) -> None:

@@ -684,3 +684,131 @@ extern "C" int sptmm_seq_free(sptmm_seq *q)
     seq_release(q);
     return SPTMM_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// A sequence run that allocates nothing.
+//
+// Some callers may not allocate device memory at the moment they need a matmul: code running
+// inside a memory pool that was sized up front and closed, a real-time loop that forbids calls
+// which can block on the allocator, or a host framework that owns every byte of the device and
+// hands out only the buffers it was asked for.  For them the sequence kernel's scratch -- the
+// step descriptors, the per-CTA plan, the step counters and the status word -- lives in the
+// fixed array below instead of in memory obtained from cudaMalloc.  The array is part of the
+// library image: every GPU that loads the library carries it until the process exits.
+constexpr uint32_t kStaticMaxSteps = 16;      // steps per call
+constexpr uint32_t kStaticMaxCtas = 256;      // SMs of the device
+constexpr size_t kStaticDescOff = 0;
+constexpr size_t kStaticBlkOff = (kStaticMaxSteps * sizeof(SeqDesc) + 255) & ~(size_t)255;
+constexpr size_t kStaticColOff = kStaticBlkOff + (size_t)kStaticMaxSteps * (kStaticMaxCtas + 1) * 4;
+constexpr size_t kStaticCtrOff = (kStaticColOff + (size_t)kStaticMaxSteps * (kStaticMaxCtas + 1) * 4 + 255) & ~(size_t)255;
+constexpr size_t kStaticStatusOff = kStaticCtrOff + 256;
+constexpr size_t kStaticBytes = kStaticStatusOff + 256;          // about 36 KB
+static __device__ __align__(256) unsigned char g_seq_static_scratch[kStaticBytes];
+
+extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uint32_t M, void *stream,
+                                    uint32_t *status_out)
+{
+    if (!steps || n == 0) return fail(SPTMM_ERR_INVALID, "seq_run_static: null pointer or empty sequence");
+    if (n > kStaticMaxSteps)
+        return fail(SPTMM_ERR_INVALID, "seq_run_static: %u steps, the fixed scratch holds at most %u", n, kStaticMaxSteps);
+    if (M == 0 || M > 16) return fail(SPTMM_ERR_UNSUPPORTED, "seq_run_static: M=%u, the sequence kernel blocks 1..16 rows", M);
+    int dev = 0, sms = 0;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(SPTMM_ERR_UNSUPPORTED, "seq_run_static: device ordinal %d", dev);
+
+    // Once per device, with that device current: the array's name is only a stand-in on the host;
+    // the address a kernel can use has to be asked for.
+    static unsigned char *scratch_of[64] = {};
+    static int sms_of[64] = {};
+    if (!scratch_of[dev]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_seq_static_scratch);
+        if (e != cudaSuccess || !p) return fail(SPTMM_ERR_CUDA, "seq_run_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        SPTMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        sms_of[dev] = sms;
+        scratch_of[dev] = (unsigned char *)p;
+    }
+    sms = sms_of[dev];
+    unsigned char *scratch = scratch_of[dev];
+    if ((uint32_t)sms > kStaticMaxCtas)
+        return fail(SPTMM_ERR_UNSUPPORTED, "seq_run_static: %d SMs, the fixed scratch plans for at most %u", sms, kStaticMaxCtas);
+
+    // host-side tables (host heap only), laid out exactly as the kernel reads them
+    sptmm_seq q;                                   // a plain host object, nothing on the device
+    q.device = dev; q.nsteps = n; q.M = M; q.G = (uint32_t)sms;
+    q.mt = M == 1 ? 1 : (M <= 4 ? 4 : 16);
+    std::vector<SeqDesc> desc(n);
+    std::vector<uint32_t> blk, col, tb, tc;
+    uint32_t kmax = 0;
+    for (uint32_t s = 0; s < n; s++) {
+        const sptmm_seq_step &st = steps[s];
+        const sptmm_weights *w = st.w;
+        if (!w || !st.X || !st.C) return fail(SPTMM_ERR_INVALID, "seq_run_static: step %u has a null pointer", s);
+        if (w->format != SPTMM_FMT_U16_V256) return fail(SPTMM_ERR_UNSUPPORTED, "seq_run_static: step %u is not in the native u16 format", s);
+        if (w->device != dev || st.replica >= w->dev.size()) return fail(SPTMM_ERR_STATE, "seq_run_static: step %u weights are not uploaded to device %d", s, dev);
+        if (st.x_kind > 1 || st.dep >= (int32_t)s) return fail(SPTMM_ERR_INVALID, "seq_run_static: step %u has a bad x_kind or dep", s);
+        SeqDesc &d = desc[s];
+        d.idx = (const uint4 *)w->dev[st.replica][0];
+        d.blk_off = (const uint32_t *)w->dev[st.replica][1];
+        d.X = st.X; d.X2 = st.X2; d.C = (int32_t *)st.C; d.scale_out = st.scale_out;
+        d.K = w->K; d.N = w->N;
+        d.ldx = st.ldx ? st.ldx : w->K; d.ldx2 = st.ldx2 ? st.ldx2 : w->K; d.ldc = st.ldc ? st.ldc : w->N;
+        d.uniform_nbl = w->uniform_nbl; d.x_kind = st.x_kind; d.dep = st.dep < 0 ? -1 : st.dep;
+        for (uint32_t r = 0; r < kMaxPeers; r++) d.Cp[r] = nullptr;
+        uint32_t mc = 1, mb = 0;
+        plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q.G, tb, tc, mc, mb);
+        blk.insert(blk.end(), tb.begin(), tb.end());
+        col.insert(col.end(), tc.begin(), tc.end());
+        q.max_cols = std::max(q.max_cols, mc);
+        kmax = std::max(kmax, w->K);
+    }
+    const uint32_t nwarps = 16;
+    q.xs_bytes = (uint32_t)xs_bytes(kmax, (int)q.mt);
+    size_t fixed = q.xs_bytes + (2 * (size_t)q.max_cols * q.mt + 32) * 4;
+    fixed = (fixed + 7) & ~(size_t)7;
+    const size_t avail = 223 * 1024;
+    uint32_t slot_blocks = kMaxSlotBlocks;
+    while (slot_blocks > 1 && fixed + 128 + (size_t)nwarps * 3 * (slot_blocks * 512 + 16) > avail) slot_blocks /= 2;
+    const size_t slot_bytes = (size_t)slot_blocks * 512;
+    q.slot_blocks = slot_blocks;
+    if (fixed + 128 + (size_t)nwarps * 2 * (slot_bytes + 16) > avail)
+        return fail(SPTMM_ERR_UNSUPPORTED, "seq_run_static: K=%u with %u-row blocking leaves no room for the weight rings", kmax, q.mt);
+    q.ring_slots = (uint32_t)std::min<size_t>(seq_ring_cap(), (avail - fixed - 128) / ((size_t)nwarps * (slot_bytes + 16)));
+    size_t o = fixed + (size_t)nwarps * 2 * q.ring_slots * 8;
+    o = (o + 127) & ~(size_t)127;
+    q.smem = 1024 + o + (size_t)nwarps * q.ring_slots * slot_bytes;
+
+    // tables in, and what must start at zero cleared: the array keeps the previous call's contents
+    cudaStream_t st = (cudaStream_t)stream;
+    SPTMM_CUDA_TRY(cudaMemcpyAsync(scratch + kStaticDescOff, desc.data(), n * sizeof(SeqDesc), cudaMemcpyHostToDevice, st));
+    SPTMM_CUDA_TRY(cudaMemcpyAsync(scratch + kStaticBlkOff, blk.data(), blk.size() * 4, cudaMemcpyHostToDevice, st));
+    SPTMM_CUDA_TRY(cudaMemcpyAsync(scratch + kStaticColOff, col.data(), col.size() * 4, cudaMemcpyHostToDevice, st));
+    SPTMM_CUDA_TRY(cudaMemsetAsync(scratch + kStaticCtrOff, 0, kStaticBytes - kStaticCtrOff, st));
+
+    SeqParams prm;
+    prm.desc = (const SeqDesc *)(scratch + kStaticDescOff);
+    prm.cta_blk = (const uint32_t *)(scratch + kStaticBlkOff);
+    prm.cta_col = (const uint32_t *)(scratch + kStaticColOff);
+    prm.counters = (unsigned long long *)(scratch + kStaticCtrOff);
+    for (uint32_t r = 0; r < kMaxPeers; r++) prm.counter_peers[r] = nullptr;
+    prm.n_peers = 0;
+    prm.status = (uint32_t *)(scratch + kStaticStatusOff);
+    prm.trace = nullptr;
+    prm.target = q.G;                              // counters were just cleared: one run's worth
+    prm.nsteps = n; prm.M = M; prm.max_cols = q.max_cols; prm.ring_slots = q.ring_slots;
+    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks;
+    int rc = SPTMM_OK;
+    switch (q.mt) {
+        case 1: rc = seq_launch<1>(&q, prm, st); break;
+        case 4: rc = seq_launch<4>(&q, prm, st); break;
+        default: rc = seq_launch<16>(&q, prm, st); break;
+    }
+    q.device = -1;                                 // the host object owns nothing to release
+    if (rc != SPTMM_OK) return rc;
+    if (status_out) {
+        SPTMM_CUDA_TRY(cudaStreamSynchronize(st));
+        SPTMM_CUDA_TRY(cudaMemcpy(status_out, scratch + kStaticStatusOff, 4, cudaMemcpyDeviceToHost));
+        if (*status_out) return fail(SPTMM_ERR_STATE, "seq_run_static: a bounded wait ran out (status %u)", *status_out);
+    }
+    return SPTMM_OK;
+}
