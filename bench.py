@@ -3,11 +3,13 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One step = `--calls` GEMV calls issued back to back on one stream, rotating over enough
-distinct copies of the encoded weights that their total exceeds L2 (cold-cache, HBM-bound).
-The step is captured once in a CUDA graph (programmatic-dependent-launch edges between the
-calls) and replayed; timing is by CUDA events on that stream, max over ranks.
-Prints ONE JSON line on rank 0.
+One step = `--calls` GEMV calls, rotating over enough distinct copies of the encoded weights
+that their total exceeds L2 (cold-cache, HBM-bound).  The calls are independent of one another,
+as the iterations of the reference's timing loop are, so they are issued round-robin on
+`--streams` streams (ordered, with programmatic-dependent-launch edges, inside each stream).
+The step is captured once in a CUDA graph and replayed; timing is by CUDA events on the stream
+the graph is launched on, max over ranks.  `single_stream` in the output is the same step with
+every call on one stream.  Prints ONE JSON line on rank 0.
 
 `--impl reference` times the CPU restatement of the reference's loop (the reference has no CPU
 path and its GPU kernels print only a time) on all host threads, same metric and unit.
@@ -172,11 +174,27 @@ def run_ours(args):
     out = torch.zeros(replicas, M * N, dtype=torch.int32, device="cuda")
     calls = args.calls
     st = torch.cuda.Stream()
+    nstreams = max(1, args.streams)
+    side = [torch.cuda.Stream() for _ in range(nstreams)] if nstreams > 1 else [st]
 
-    def issue_step(stream):
+    def issue_step(stream, lanes=None):
+        """`calls` GEMVs.  No call depends on another (as in the reference's timing loop), so they go
+        round-robin to `lanes` streams forked from and joined back into `stream`; inside a lane the
+        calls are ordered, with programmatic-dependent-launch edges."""
+        lanes = side if lanes is None else lanes
+        if lanes[0] is not stream:
+            fork = torch.cuda.Event()
+            fork.record(stream)
+            for s in lanes:
+                s.wait_event(fork)
         for i in range(calls):
             r = i % replicas
-            w.gemv(xd, M, out[r], sp.I8, sp.LAUNCH_PDL, replica=r, stream=stream.cuda_stream)
+            w.gemv(xd, M, out[r], sp.I8, sp.LAUNCH_PDL, replica=r, stream=lanes[i % len(lanes)].cuda_stream)
+        if lanes[0] is not stream:
+            for s in lanes:
+                join = torch.cuda.Event()
+                join.record(s)
+                stream.wait_event(join)
 
     # parity first: a fast wrong kernel is not a result
     with torch.cuda.stream(st):
@@ -236,6 +254,32 @@ def run_ours(args):
     us_per_call = ms * 1e3 / total_calls
     per_gpu = nbytes / (us_per_call * 1e-6) / 1e9
     value = per_gpu * world
+
+    # ---- the same calls on ONE stream: every call then waits for the previous one to finish
+    # (what a caller with a true data dependence between calls gets)
+    single = None
+    if nstreams > 1 and not args.no_graph:
+        try:
+            g1 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g1, stream=st, capture_error_mode="thread_local"):
+                issue_step(st, [st])
+            reps = max(4, args.steps // 8)
+            with torch.cuda.stream(st):
+                for _ in range(3):
+                    g1.replay()
+                st.synchronize()
+                s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s0.record(st)
+                for _ in range(reps):
+                    g1.replay()
+                s1.record(st)
+                st.synchronize()
+            sus = s0.elapsed_time(s1) * 1e3 / (reps * calls)
+            single = {"us_per_call": sus, "GBps": nbytes / sus / 1e3, "steps_timed": reps}
+            del g1
+        except Exception as e:
+            single = {"error": str(e).splitlines()[0][:120]}
+            torch.cuda.synchronize()
 
     # ---- end to end through the host-buffer entry point (H2D + kernel + D2H + wait per call)
     e2e_calls = max(64, min(2000, total_calls // 8))
@@ -339,7 +383,7 @@ def run_ours(args):
             "config": {"workload": "C1 ternary GEMV M=1 K=6912 N=2560, reference generator -S=4096, native u16 lists",
                        "calls_per_step": calls, "weight_copies": replicas,
                        "l2": "cold: rotating %d weight copies (%.0f MB) > 126 MB L2" % (replicas, replicas * per_copy / 1e6),
-                       "launch": mode + ", programmatic dependent launch",
+                       "launch": mode + ", %d concurrent streams (independent calls, round-robin), programmatic dependent launch inside a stream" % nstreams,
                        "per_rank": "each GPU runs the same independent 2560-column shard",
                        "tune": os.environ.get("SPTMM_TUNE", "")},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
@@ -347,6 +391,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "GB/s", "us_per_call": e2e_us,
                     "h2d_bytes_per_step": M * K * calls, "d2h_bytes_per_step": M * N * 4 * calls,
                     "calls_timed": e2e_calls, "how": "sptmm_gemv_host per call: pinned H2D, kernel, D2H, stream wait"},
+            "single_stream": single,
             "sequence": seq_info,
             "stack": stack_info,
             "gpu_launches": total_calls,
@@ -367,24 +412,43 @@ def run_ours(args):
 NCU_TRAFFIC_BYTES = 21014000
 
 
-def extra_workloads(sp, O, torch, st):
-    """M=4 fp16 (same W), the reference layouts, the delta sweep and the comparators: us/call,
-    warm-cache (single weight copy), for context beside the headline."""
+def extra_workloads(sp, O, torch, st, nstreams=4):
+    """The same matrix at M=1/4/16 (int8, fp16) in the native format, the reference layouts and the
+    i2s comparator: us/call, cold L2 (rotating weight copies), timed like the headline -- 256
+    independent calls per CUDA graph over `nstreams` streams (`us_per_call`) and on one stream
+    (`us_single_stream`)."""
     res = {}
     W = sp.gen_ternary_fixed(K, N, S)
     rng = np.random.default_rng(2)
+    side = [torch.cuda.Stream() for _ in range(nstreams)]
+    ncalls = 256
 
-    def timeit(fn, n=400):
-        for _ in range(20):
-            fn()
-        st.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(st)
-        for _ in range(n):
-            fn()
-        e1.record(st)
-        st.synchronize()
-        return e0.elapsed_time(e1) * 1e3 / n
+    def timeit(call, lanes, n=12):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st, capture_error_mode="thread_local"):
+            if lanes[0] is not st:
+                fork = torch.cuda.Event()
+                fork.record(st)
+                for s in lanes:
+                    s.wait_event(fork)
+            for i in range(ncalls):
+                call(i, lanes[i % len(lanes)])
+            if lanes[0] is not st:
+                for s in lanes:
+                    join = torch.cuda.Event()
+                    join.record(s)
+                    st.wait_event(join)
+        with torch.cuda.stream(st):
+            for _ in range(3):
+                g.replay()
+            st.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(n):
+                g.replay()
+            e1.record(st)
+            st.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (n * ncalls)
 
     def cold_replicas(w):
         r = max(2, -(-int(2.5 * L2_BYTES) // max(1, w.stream_bytes)))
@@ -401,18 +465,17 @@ def extra_workloads(sp, O, torch, st):
                 continue
             if dt == sp.I8:
                 x = torch.from_numpy(O.gen_x_i8(m * K, 1)).cuda()
-                o = torch.zeros(m * N, dtype=torch.int32, device="cuda")
+                o = torch.zeros(nstreams, m * N, dtype=torch.int32, device="cuda")
             else:
                 x = torch.from_numpy(rng.standard_normal((m, K)).astype(np.float16)).cuda()
-                o = torch.zeros(m * N, dtype=torch.float32, device="cuda")
-            ctr = [0]
-            def call():
-                w.gemv(x, m, o, dt, sp.LAUNCH_PDL, replica=ctr[0] % reps, stream=st.cuda_stream)
-                ctr[0] += 1
-            us = timeit(call)
+                o = torch.zeros(nstreams, m * N, dtype=torch.float32, device="cuda")
+            def call(i, stream):
+                w.gemv(x, m, o[i % nstreams], dt, sp.LAUNCH_PDL, replica=i % reps, stream=stream.cuda_stream)
+            us = timeit(call, side)
+            us1 = timeit(call, [st])
             nb = algorithmic_bytes(w.stream_bytes, m, 1 if dt == sp.I8 else 2)
             res["%s_M%d_%s" % (name, m, "i8" if dt == sp.I8 else "f16")] = {
-                "us_per_call": us, "GBps": nb / us / 1e3, "bytes": nb, "copies": reps}
+                "us_per_call": us, "GBps": nb / us / 1e3, "us_single_stream": us1, "bytes": nb, "copies": reps}
         w.close()
     return res
 
@@ -423,6 +486,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--calls", type=int, default=1024, help="GEMV calls per step")
+    ap.add_argument("--streams", type=int, default=4, help="streams the independent calls of a step are spread over")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -92,20 +92,115 @@ __device__ __forceinline__ void gather_add(typename ActTraits<DT>::acc (&acc)[MT
 #pragma unroll
         for (int m = 0; m < MT; m++) acc[m] += (int32_t)(int8_t)(r[m >> 2] >> (8 * (m & 3)));
     } else if constexpr (DT == SPTMM_F16) {
+        // mixed-precision add (f32 += f16, one instruction, exact conversion, round to nearest)
         if constexpr (MT == 1) {
-            acc[0] += __half2float(__ushort_as_half((unsigned short)r[0]));
+            asm("{ .reg .f16 lo, hi; mov.b32 {lo, hi}, %1; add.rn.f32.f16 %0, lo, %0; }" : "+f"(acc[0]) : "r"(r[0]));
         } else {
 #pragma unroll
-            for (int m = 0; m < MT; m += 2) {
-                float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&r[m >> 1]));
-                acc[m] += f.x; acc[m + 1] += f.y;
-            }
+            for (int m = 0; m < MT; m += 2)
+                asm("{ .reg .f16 lo, hi; mov.b32 {lo, hi}, %2; add.rn.f32.f16 %0, lo, %0; add.rn.f32.f16 %1, hi, %1; }"
+                    : "+f"(acc[m]), "+f"(acc[m + 1]) : "r"(r[m >> 1]));
         }
     } else {
 #pragma unroll
         for (int m = 0; m < MT; m++) acc[m] += __uint_as_float(r[m]);
     }
 }
+
+__device__ __forceinline__ uint32_t mad_u32(uint32_t a, uint32_t b, uint32_t c)     // a*b + c
+{
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// One lane's running sums over MT rows of X.  The generic form keeps one 32-bit sum per row and
+// adds a gathered tile row element by element.
+//
+// For int8 tiles of two or more rows that costs a sign extension and an add per element, which
+// makes instruction issue -- not memory -- the limit.  The packed form removes most of it: the
+// tile then holds x+128 as unsigned bytes (`kBiased`; the zero row holds 128), a gathered word
+// is split by two byte permutes into its even and odd bytes, each as two 16-bit fields of one
+// register ({b0,0,b2,0} and {b1,0,b3,0}), and one 32-bit add per register accumulates two rows
+// at once.  A 16-bit field holds 257 such bytes, so the caller announces its gathers with
+// reserve() and the fields are spilled into the 32-bit sums (minus 128 per gather) every 256
+// gathers at most.  Results are exact.
+template <int DT, int MT, bool PACKED = (DT == SPTMM_I8 && MT > 1)>
+struct LaneAcc {
+    using acc_t = typename ActTraits<DT>::acc;
+    static constexpr bool kBiased = false;
+    acc_t v[MT];
+    __device__ __forceinline__ void clear(uint32_t /*one*/)
+    {
+#pragma unroll
+        for (int m = 0; m < MT; m++) v[m] = acc_t(0);
+    }
+    __device__ __forceinline__ void reserve(uint32_t) {}
+    __device__ __forceinline__ void add(uint32_t row) { gather_add<DT, MT>(v, row); }
+    __device__ __forceinline__ void finish() {}
+};
+
+template <int MT>
+struct LaneAcc<SPTMM_I8, MT, true> {
+    using acc_t = int32_t;
+    static constexpr bool kBiased = true;
+    static constexpr int NP = MT / 2;          // packed registers: MT=2 -> 1, else two per tile word
+    int32_t v[MT];
+    uint32_t pk[NP];
+    uint32_t n;                                // gathers held in the 16-bit fields
+    uint32_t one;                              // the value 1, unknown to the compiler (see add())
+    __device__ __forceinline__ void clear(uint32_t one_)
+    {
+        one = one_;
+#pragma unroll
+        for (int m = 0; m < MT; m++) v[m] = 0;
+#pragma unroll
+        for (int j = 0; j < NP; j++) pk[j] = 0;
+        n = 0;
+    }
+    __device__ __forceinline__ void finish()
+    {
+        const int32_t bias = (int32_t)(128u * n);
+        if constexpr (MT == 2) {
+            v[0] += (int32_t)(pk[0] & 0xffffu) - bias;
+            v[1] += (int32_t)(pk[0] >> 16) - bias;
+        } else {
+#pragma unroll
+            for (int q = 0; q < MT / 4; q++) {
+                v[4 * q + 0] += (int32_t)(pk[2 * q] & 0xffffu) - bias;
+                v[4 * q + 2] += (int32_t)(pk[2 * q] >> 16) - bias;
+                v[4 * q + 1] += (int32_t)(pk[2 * q + 1] & 0xffffu) - bias;
+                v[4 * q + 3] += (int32_t)(pk[2 * q + 1] >> 16) - bias;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NP; j++) pk[j] = 0;
+        n = 0;
+    }
+    __device__ __forceinline__ void reserve(uint32_t gathers)      // warp-uniform
+    {
+        if (n + gathers > 256u) finish();
+        n += gathers;
+    }
+    __device__ __forceinline__ void add(uint32_t row)
+    {
+        uint32_t r[RowWords<MT>::n];
+        load_row<MT>(row, r);
+        // The permutes run on the integer ALU pipe; plain adds would too, and with 16 rows that
+        // pipe, not shared memory, bounds the kernel.  Written as multiply-adds by a 1 the
+        // compiler cannot see through, the additions go to the FMA pipe instead and the two
+        // pipes share the work.
+        if constexpr (MT == 2) {
+            pk[0] = mad_u32(__byte_perm(r[0], 0u, 0x4140), one, pk[0]);                  // {b0, 0, b1, 0}
+        } else {
+#pragma unroll
+            for (int q = 0; q < MT / 4; q++) {
+                pk[2 * q] = mad_u32(__byte_perm(r[q], 0u, 0x4240), one, pk[2 * q]);          // {b0, 0, b2, 0}
+                pk[2 * q + 1] = mad_u32(__byte_perm(r[q], 0u, 0x4341), one, pk[2 * q + 1]);  // {b1, 0, b3, 0}
+            }
+        }
+    }
+};
 
 __device__ __forceinline__ int32_t warp_sum(int32_t v) { return __reduce_add_sync(0xffffffffu, v); }
 __device__ __forceinline__ float warp_sum(float v)
@@ -115,13 +210,38 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
+// 4 x MT byte transpose in registers: w[m] holds bytes k0..k0+3 of row m; on return
+// o[i*(MT/4) + j] is word j of tile row k0+i, i.e. the bytes of rows 4j..4j+3 at k0+i.
+template <int MT>
+__device__ __forceinline__ void transpose_bytes4(const uint32_t (&w)[MT], uint32_t (&o)[MT])
+{
+    static_assert(MT % 4 == 0, "row tiles of 4, 8 or 16");
+#pragma unroll
+    for (int j = 0; j < MT / 4; j++) {
+        const uint32_t t0 = __byte_perm(w[4 * j], w[4 * j + 1], 0x5140);      // a0 b0 a1 b1
+        const uint32_t t1 = __byte_perm(w[4 * j + 2], w[4 * j + 3], 0x5140);  // c0 d0 c1 d1
+        const uint32_t t2 = __byte_perm(w[4 * j], w[4 * j + 1], 0x7362);      // a2 b2 a3 b3
+        const uint32_t t3 = __byte_perm(w[4 * j + 2], w[4 * j + 3], 0x7362);  // c2 d2 c3 d3
+        o[0 * (MT / 4) + j] = __byte_perm(t0, t1, 0x5410);
+        o[1 * (MT / 4) + j] = __byte_perm(t0, t1, 0x7632);
+        o[2 * (MT / 4) + j] = __byte_perm(t2, t3, 0x5410);
+        o[3 * (MT / 4) + j] = __byte_perm(t2, t3, 0x7632);
+    }
+}
+
 // Fill the transposed tile from X.  mv = valid rows of this tile (the rest read as zero).
 // Lanes run along k so that global reads coalesce and shared writes spread over the banks.
-template <int DT, int MT>
+// BIASED (int8 only): store x+128 as an unsigned byte, the form LaneAcc's packed sums expect.
+template <int DT, int MT, bool BIASED = false>
 __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint32_t K, uint32_t M,
                                         uint32_t m0, uint32_t mv, bool x_colmajor)
 {
+    static_assert(!BIASED || DT == SPTMM_I8, "only int8 tiles are biased");
     using elem = typename ActTraits<DT>::elem;
+    [[maybe_unused]] const auto biased = [](elem v) -> elem {
+        if constexpr (BIASED) return (elem)((unsigned char)v ^ 0x80u);
+        else return v;
+    };
     constexpr int ES = ActTraits<DT>::size;
     elem *dst = reinterpret_cast<elem *>(xs);
     const elem *X = reinterpret_cast<const elem *>(Xv);
@@ -157,19 +277,13 @@ __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint3
                     // rows k0..k0+3 hold two bytes each: (a_i, b_i)
                     o[0] = __byte_perm(w[0], w[1], 0x5140);          // a0 b0 a1 b1
                     o[1] = __byte_perm(w[0], w[1], 0x7362);          // a2 b2 a3 b3
-                } else {
-#pragma unroll
-                    for (int j = 0; j < MT / 4; j++) {
-                        const uint32_t t0 = __byte_perm(w[4 * j], w[4 * j + 1], 0x5140);      // a0 b0 a1 b1
-                        const uint32_t t1 = __byte_perm(w[4 * j + 2], w[4 * j + 3], 0x5140);  // c0 d0 c1 d1
-                        const uint32_t t2 = __byte_perm(w[4 * j], w[4 * j + 1], 0x7362);      // a2 b2 a3 b3
-                        const uint32_t t3 = __byte_perm(w[4 * j + 2], w[4 * j + 3], 0x7362);  // c2 d2 c3 d3
-                        o[0 * (MT / 4) + j] = __byte_perm(t0, t1, 0x5410);
-                        o[1 * (MT / 4) + j] = __byte_perm(t0, t1, 0x7632);
-                        o[2 * (MT / 4) + j] = __byte_perm(t2, t3, 0x5410);
-                        o[3 * (MT / 4) + j] = __byte_perm(t2, t3, 0x7632);
-                    }
+                } else if constexpr (MT >= 4) {
+                    transpose_bytes4<MT>(w, o);
                 }
+            }
+            if constexpr (BIASED) {
+#pragma unroll
+                for (int m = 0; m < MT; m++) o[m] ^= 0x80808080u;
             }
             uint32_t *out = reinterpret_cast<uint32_t *>(xs + (size_t)pc * KP * MT * ES);   // MT words
             if constexpr (MT == 2) {
@@ -184,13 +298,13 @@ __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint3
         for (uint32_t m = 0; m < (uint32_t)MT; m++) {
             if (m < mv) {
                 for (uint32_t k = tid; k < K; k += nt)
-                    dst[(size_t)k * MT + m] = x_colmajor ? X[(size_t)k * M + m0 + m] : X[(size_t)(m0 + m) * K + k];
+                    dst[(size_t)k * MT + m] = biased(x_colmajor ? X[(size_t)k * M + m0 + m] : X[(size_t)(m0 + m) * K + k]);
             } else {
-                for (uint32_t k = tid; k < K; k += nt) dst[(size_t)k * MT + m] = elem(0);
+                for (uint32_t k = tid; k < K; k += nt) dst[(size_t)k * MT + m] = biased(elem(0));
             }
         }
     }
-    if (tid < (uint32_t)MT) dst[(size_t)K * MT + tid] = elem(0);     // the zero row
+    if (tid < (uint32_t)MT) dst[(size_t)K * MT + tid] = biased(elem(0));     // the zero row
 }
 
 __host__ __device__ inline size_t xs_bytes(uint32_t K, int rb) { return (((size_t)K + 1) * rb + 15) & ~(size_t)15; }

@@ -145,10 +145,72 @@ static void encode_delta_div256(const Lists &L, sptmm_weights &w, uint32_t cap)
     w.stream_bytes = (uint64_t)cap * N * 2;      // the tail padding is never read
 }
 
-// Native u16 layout.  Each list is cut into blocks of 256 entries (the last one padded with
-// index K, which addresses a zero row the kernels append to X).  Inside a block the entry that
-// lane l consumes at step t, entry 32*t + l, sits at position 8*l + t, so that one 16-byte load
-// per lane brings eight entries and every step's 32 gathers fall in one narrow window of rows.
+// Native u16 layout.  Each list, in the order bank_order() gives it, is cut into blocks of 256
+// entries (the last one padded with index K, which addresses a zero row the kernels append to
+// X).  Inside a block the entry that lane l consumes at step t, entry 32*t + l, sits at
+// position 8*l + t, so that one 16-byte load per lane brings eight entries.
+//
+// Order of a list's entries inside the native format.  A sum does not depend on the order of its
+// terms, so the encoder is free to choose which 32 entries a warp gathers in one step (entries
+// 32t..32t+31 of a block) and which lane gets which.  The kernels keep MT rows of X side by side,
+// RB = MT*sizeof(element) bytes per matrix row, so a gathered row r occupies shared-memory banks
+// (r*RB/4) mod 32.  Sorted order is ideal for RB = 1 (32 neighbouring rows share a few words) but
+// random for wider tiles: 2.9 / 5.1 / 9.1 bank cycles per step at RB = 4 / 8 / 16 where 1 / 2 / 4
+// would do.  The order chosen here gives lane l an entry with r = l (mod 32) whenever the next
+// kWindow unused entries of the sorted list hold one: then the 32 rows differ mod 32 (RB = 4), the
+// rows of a half warp differ mod 16 (RB = 8) and those of a quarter warp mod 8 (RB = 16).  Lanes
+// left empty fall back to r = l (mod 16), then (mod 8), then to the smallest unused row.  Every
+// choice must also keep the step conflict-free for RB = 1: two rows of a step may share a bank
+// ((r/4) mod 32) only if they share the word.  Measured on the reference generator's lists
+// (K=6912, 2048 entries): 1.07 / 2.0 / 3.0 / 4.8 cycles per step at RB = 1 / 4 / 8 / 16.
+// `rows` is ascending; `out` receives the same rows, 32 per step, in step order; a step's unused
+// lanes (possible only in the last steps of a list) hold `pad`.
+static void bank_order(const std::vector<uint16_t> &rows, uint16_t pad, std::vector<uint16_t> &out)
+{
+    constexpr size_t kWindow = 192;
+    const size_t n = rows.size();
+    out.clear();
+    out.reserve((n + 31) / 32 * 32);
+    std::vector<uint16_t> bucket[32];         // window entries by r mod 32, ascending
+    size_t next = 0, in_window = 0, remaining = n;
+    while (remaining) {
+        while (in_window < kWindow && next < n) { bucket[rows[next] & 31].push_back(rows[next]); next++; in_window++; }
+        uint16_t step[32];
+        bool filled[32] = {};
+        int32_t bank_word[32];
+        for (int i = 0; i < 32; i++) bank_word[i] = -1;
+        auto fits = [&](uint16_t r) { const int32_t wd = r >> 2; return bank_word[wd & 31] < 0 || bank_word[wd & 31] == wd; };
+        auto take = [&](int lane, int b, size_t j) {
+            const uint16_t r = bucket[b][j];
+            bucket[b].erase(bucket[b].begin() + (ptrdiff_t)j);
+            step[lane] = r; filled[lane] = true; bank_word[(r >> 2) & 31] = r >> 2;
+        };
+        for (int mod = 32; mod >= 8; mod >>= 1)
+            for (int lane = 0; lane < 32; lane++) {
+                if (filled[lane]) continue;
+                for (int b = lane % mod; b < 32 && !filled[lane]; b += mod)
+                    for (size_t j = 0; j < bucket[b].size(); j++)
+                        if (fits(bucket[b][j])) { take(lane, b, j); break; }
+            }
+        for (int strict = 1; strict >= 0; strict--)
+            for (int lane = 0; lane < 32; lane++) {
+                if (filled[lane]) continue;
+                int best_b = -1; size_t best_j = 0; uint32_t best_r = 0xffffffffu;
+                for (int b = 0; b < 32; b++)
+                    for (size_t j = 0; j < bucket[b].size(); j++)
+                        if (!strict || fits(bucket[b][j])) {
+                            if (bucket[b][j] < best_r) { best_r = bucket[b][j]; best_b = b; best_j = j; }
+                            break;
+                        }
+                if (best_b >= 0) take(lane, best_b, best_j);
+            }
+        for (int lane = 0; lane < 32; lane++) {
+            out.push_back(filled[lane] ? step[lane] : pad);
+            if (filled[lane]) { remaining--; in_window--; }
+        }
+    }
+}
+
 // Blocks are stored list after list in the order pos(0), neg(0), pos(1), ...; blk_off[2c+s]
 // is the first block of list (column c, sign s).
 static void encode_u16_v256(const Lists &L, sptmm_weights &w)
@@ -170,9 +232,10 @@ static void encode_u16_v256(const Lists &L, sptmm_weights &w)
     w.arrays.push_back(make_array("idx_v256", (size_t)w.total_blocks * 512, true));
     uint16_t *out = (uint16_t *)w.arrays.back().data.data();
     parallel_columns(N, [&](uint32_t c0, uint32_t c1) {
+        std::vector<uint16_t> l;
         for (uint32_t c = c0; c < c1; c++)
             for (int sign = 0; sign < 2; sign++) {
-                const auto &l = sign ? L.neg[c] : L.pos[c];
+                bank_order(sign ? L.neg[c] : L.pos[c], (uint16_t)w.K, l);
                 uint16_t *dst = out + (size_t)off[2 * c + sign] * 256;
                 const uint32_t nb = off[2 * c + sign + 1] - off[2 * c + sign];
                 for (uint32_t b = 0; b < nb; b++)

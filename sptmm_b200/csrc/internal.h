@@ -45,7 +45,8 @@ struct sptmm_weights {
     int device = -1;
     uint32_t sm_count = 0;
     std::vector<std::vector<void *>> dev;   // [replica][array]
-    sptmm::LaunchPlan plan;
+    sptmm::LaunchPlan plan;           // small activation tiles: several CTAs per SM (see Tune)
+    sptmm::LaunchPlan plan_wide;      // tiles of tens of KB: one 512-thread CTA per SM
 
     // pinned / device staging for sptmm_gemv_host
     void *pin_x = nullptr, *pin_c = nullptr, *stage_x = nullptr, *stage_c = nullptr;
@@ -55,7 +56,8 @@ struct sptmm_weights {
 
 namespace sptmm {
 
-// Tunables read once from the environment (SPTMM_TUNE="ctas_per_sm=1,threads=512,prefetch=8").
+// Tunables read once from the environment (SPTMM_TUNE="ctas_per_sm=2,threads=256,prefetch=4").
+// smem_kb = shared memory one CTA of the small-tile plan may use beside its activation tile.
 struct Tune { int ctas_per_sm; int threads; int prefetch; int evict_first; int l2_prefetch; int smem_kb; };
 const Tune &tune();
 

@@ -44,6 +44,7 @@ struct NativeParams {
     uint32_t max_cols;
     uint32_t x_colmajor, c_colmajor;
     uint32_t uniform_nbl;        // blocks per list when every list has the same count, else 0
+    uint32_t one;                // always 1: a multiplier the compiler cannot fold (LaneAcc::add)
     uint32_t half_blocks;        // blocks per half of a warp's staging area
     uint32_t stage_blocks;       // blocks of staging area per warp (one or two halves)
     uint32_t stage_off;          // byte offset of the staging area in dynamic shared memory
@@ -164,7 +165,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
 
     const uint32_t m0 = blockIdx.y * MT;
     const uint32_t mv = min((uint32_t)MT, p.M - m0);
-    stage_x<DT, MT>(xs, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
+    stage_x<DT, MT, LaneAcc<DT, MT>::kBiased>(xs, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
     __syncthreads();
     if (tracing) p.trace[blockIdx.x * 8 + 2] = global_ns();
 
@@ -188,16 +189,16 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
         const uint32_t first_col = li >> 1, last_col = llast >> 1;
         if (!kInt && lane == 0) { hcol_s[warp] = first_col; tcol_s[warp] = last_col; }
 
-        acc_t acc[MT];
-#pragma unroll
-        for (int m = 0; m < MT; m++) acc[m] = acc_t(0);
+        LaneAcc<DT, MT> acc;
+        acc.clear(p.one);
         bool dirty = false;
 
         auto flush = [&]() {
             const uint32_t col = li >> 1;
+            acc.finish();
 #pragma unroll
             for (int m = 0; m < MT; m++) {
-                acc_t v = warp_sum(acc[m]);
+                acc_t v = warp_sum(acc.v[m]);
                 v = (li & 1) ? -v : v;
                 if constexpr (kInt) {
                     if (lane == 0) atomicAdd(reinterpret_cast<int *>(c_s) + col * MT + m, (int)v);
@@ -205,7 +206,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
                     acc_t *dst = col == first_col ? head_s + warp * MT : (col == last_col ? tail_s + warp * MT : c_s + col * MT);
                     if (lane == 0) dst[m] += v;
                 }
-                acc[m] = acc_t(0);
+                acc.v[m] = acc_t(0);
             }
         };
         auto consume = [&](const uint4 v, const uint32_t b) {
@@ -217,36 +218,38 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
                 } while (b >= bound);
             }
             dirty = true;
-            gather_add<DT, MT>(acc, v.x & 0xffffu);
-            gather_add<DT, MT>(acc, v.x >> 16);
-            gather_add<DT, MT>(acc, v.y & 0xffffu);
-            gather_add<DT, MT>(acc, v.y >> 16);
-            gather_add<DT, MT>(acc, v.z & 0xffffu);
-            gather_add<DT, MT>(acc, v.z >> 16);
-            gather_add<DT, MT>(acc, v.w & 0xffffu);
-            gather_add<DT, MT>(acc, v.w >> 16);
+            acc.reserve(8);
+            acc.add(v.x & 0xffffu);
+            acc.add(v.x >> 16);
+            acc.add(v.y & 0xffffu);
+            acc.add(v.y >> 16);
+            acc.add(v.z & 0xffffu);
+            acc.add(v.z >> 16);
+            acc.add(v.w & 0xffffu);
+            acc.add(v.w >> 16);
         };
 
         // two blocks at once when both lie inside the current list: sixteen independent gathers
         auto consume2 = [&](const uint4 v0, const uint4 v1, const uint32_t b) {
             if (b + 1 < bound) {
                 dirty = true;
-                gather_add<DT, MT>(acc, v0.x & 0xffffu);
-                gather_add<DT, MT>(acc, v1.x & 0xffffu);
-                gather_add<DT, MT>(acc, v0.x >> 16);
-                gather_add<DT, MT>(acc, v1.x >> 16);
-                gather_add<DT, MT>(acc, v0.y & 0xffffu);
-                gather_add<DT, MT>(acc, v1.y & 0xffffu);
-                gather_add<DT, MT>(acc, v0.y >> 16);
-                gather_add<DT, MT>(acc, v1.y >> 16);
-                gather_add<DT, MT>(acc, v0.z & 0xffffu);
-                gather_add<DT, MT>(acc, v1.z & 0xffffu);
-                gather_add<DT, MT>(acc, v0.z >> 16);
-                gather_add<DT, MT>(acc, v1.z >> 16);
-                gather_add<DT, MT>(acc, v0.w & 0xffffu);
-                gather_add<DT, MT>(acc, v1.w & 0xffffu);
-                gather_add<DT, MT>(acc, v0.w >> 16);
-                gather_add<DT, MT>(acc, v1.w >> 16);
+                acc.reserve(16);
+                acc.add(v0.x & 0xffffu);
+                acc.add(v1.x & 0xffffu);
+                acc.add(v0.x >> 16);
+                acc.add(v1.x >> 16);
+                acc.add(v0.y & 0xffffu);
+                acc.add(v1.y & 0xffffu);
+                acc.add(v0.y >> 16);
+                acc.add(v1.y >> 16);
+                acc.add(v0.z & 0xffffu);
+                acc.add(v1.z & 0xffffu);
+                acc.add(v0.z >> 16);
+                acc.add(v1.z >> 16);
+                acc.add(v0.w & 0xffffu);
+                acc.add(v1.w & 0xffffu);
+                acc.add(v0.w >> 16);
+                acc.add(v1.w >> 16);
             } else {
                 consume(v0, b);
                 consume(v1, b + 1);
@@ -344,18 +347,18 @@ static int launch_one(const NativeParams &prm, dim3 grid, uint32_t threads, size
     return SPTMM_OK;
 }
 
-static int prefetch_depth(int mt)
+// blocks a warp takes straight into registers (the rest of its slice goes through shared memory)
+static int prefetch_depth(int mt, bool wide)
 {
-    const int t = tune().prefetch;
+    const int t = wide ? 8 : tune().prefetch;
     if (mt == 1) return t >= 16 ? 16 : (t <= 4 ? 4 : 8);
     if (mt == 4) return t <= 4 ? 4 : 8;
     return mt == 2 ? 8 : 4;
 }
 
 template <int DT>
-static int launch_dtype(const NativeParams &prm, int mt, dim3 grid, uint32_t threads, size_t smem, bool pdl, cudaStream_t st)
+static int launch_dtype(const NativeParams &prm, int mt, int pd, dim3 grid, uint32_t threads, size_t smem, bool pdl, cudaStream_t st)
 {
-    const int pd = prefetch_depth(mt);
     switch (mt) {
         case 1:
             if (pd == 16) return launch_one<DT, 1, 16, 1>(prm, grid, threads, smem, pdl, st);
@@ -378,27 +381,35 @@ int launch_native_u16(const GemvArgs &a)
 {
     const sptmm_weights &w = *a.w;
     const int es = (int)dtype_size(a.dtype);
-    const uint32_t threads = w.plan.threads, nwarps = threads / 32;
-    if (w.plan.grid > (uint32_t)kMaxGrid || nwarps > (uint32_t)kMaxWarps)
-        return fail(SPTMM_ERR_INVALID, "internal: launch plan %u x %u out of range", w.plan.grid, threads);
     // widest row tile (<= 16 rows, power of two) whose transposed copy of X fits shared memory
     // beside a minimal staging area (two blocks per warp)
-    const size_t min_stage = 256 + (size_t)nwarps * 2 * 512;
     int mt = 1;
     while (mt < 16 && (uint32_t)mt < a.M) mt *= 2;
-    while (mt > 1 && native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps) + min_stage > 200 * 1024) mt /= 2;
-    const size_t base_smem = native_smem(w.K, mt * es, mt, w.plan.max_cols, nwarps);
+    {
+        const LaunchPlan &pw = w.plan_wide;
+        const size_t min_stage_w = 256 + (size_t)(pw.threads / 32) * 2 * 512;
+        while (mt > 1 && native_smem(w.K, mt * es, mt, pw.max_cols, pw.threads / 32) + min_stage_w > 200 * 1024) mt /= 2;
+    }
+    // A small tile leaves room for several CTAs per SM, whose stream and gather phases then
+    // overlap (also across neighbouring calls); a tile of tens of KB gets the SM to itself.
+    const bool wide = xs_bytes(w.K, mt * es) > 32 * 1024;
+    const LaunchPlan &plan = wide ? w.plan_wide : w.plan;
+    const uint32_t threads = plan.threads, nwarps = threads / 32;
+    if (plan.grid > (uint32_t)kMaxGrid || nwarps > (uint32_t)kMaxWarps)
+        return fail(SPTMM_ERR_INVALID, "internal: launch plan %u x %u out of range", plan.grid, threads);
+    const size_t min_stage = 256 + (size_t)nwarps * 2 * 512;
+    const size_t base_smem = native_smem(w.K, mt * es, mt, plan.max_cols, nwarps);
     const size_t gap = 1024;                  // dynamic shared memory before the tile's fixed address
     if (gap + base_smem + min_stage > 227 * 1024)
         return fail(SPTMM_ERR_UNSUPPORTED, "gemv: K=%u rows of %d-byte activations do not fit shared memory", w.K, es);
 
     // staging area: what a warp's slice holds beyond the registers, in one round if the budget
-    // allows (a budget of about half an SM leaves room for the next kernel's CTA), else in
-    // double-buffered rounds of half the room each
-    const uint32_t pd = (uint32_t)prefetch_depth(mt);
-    const uint32_t per_warp = (w.plan.max_cta_blocks + nwarps - 1) / nwarps + 1;
+    // allows, else in double-buffered rounds of half the room each
+    const uint32_t pd = (uint32_t)prefetch_depth(mt, wide);
+    const uint32_t per_warp = (plan.max_cta_blocks + nwarps - 1) / nwarps + 1;
     const uint32_t need = per_warp > pd ? per_warp - pd : 0;
-    const size_t budget = std::min(std::max((size_t)tune().smem_kb * 1024, base_smem + min_stage), (size_t)226 * 1024);
+    const size_t budget = wide ? (size_t)225 * 1024
+                               : std::min(base_smem + std::max((size_t)tune().smem_kb * 1024, min_stage), (size_t)225 * 1024);
     const uint32_t room = (uint32_t)((budget - base_smem - 256) / ((size_t)nwarps * 512));   // blocks per warp
     const uint32_t half = need == 0 ? 0 : (need <= room ? need : std::max(1u, room / 2));
     const uint32_t halves = need <= room ? 1 : 2;
@@ -411,21 +422,22 @@ int launch_native_u16(const GemvArgs &a)
     prm.trace = g_trace;
     prm.status = (uint32_t *)w.plan.d_status;
     prm.K = w.K; prm.N = w.N; prm.M = a.M;
-    prm.max_cols = w.plan.max_cols;
+    prm.max_cols = plan.max_cols;
     prm.x_colmajor = (a.flags & SPTMM_X_COLMAJOR) ? 1 : 0;
     prm.c_colmajor = (a.flags & SPTMM_C_COLMAJOR) ? 1 : 0;
     prm.uniform_nbl = w.uniform_nbl;
+    prm.one = 1;
     prm.half_blocks = half;
     prm.stage_blocks = halves * half;
     prm.stage_off = (uint32_t)base_smem;
-    for (uint32_t i = 0; i <= w.plan.grid; i++) { prm.cta_blk[i] = w.plan.cta_blk[i]; prm.cta_col[i] = w.plan.cta_col[i]; }
-    const dim3 grid(w.plan.grid, (a.M + mt - 1) / mt, 1);
+    for (uint32_t i = 0; i <= plan.grid; i++) { prm.cta_blk[i] = plan.cta_blk[i]; prm.cta_col[i] = plan.cta_col[i]; }
+    const dim3 grid(plan.grid, (a.M + mt - 1) / mt, 1);
     const bool pdl = (a.flags & SPTMM_LAUNCH_PDL) != 0;
     cudaStream_t st = (cudaStream_t)a.stream;
     switch (a.dtype) {
-        case SPTMM_I8:  return launch_dtype<SPTMM_I8>(prm, mt, grid, threads, smem, pdl, st);
-        case SPTMM_F16: return launch_dtype<SPTMM_F16>(prm, mt, grid, threads, smem, pdl, st);
-        case SPTMM_F32: return launch_dtype<SPTMM_F32>(prm, mt, grid, threads, smem, pdl, st);
+        case SPTMM_I8:  return launch_dtype<SPTMM_I8>(prm, mt, (int)pd, grid, threads, smem, pdl, st);
+        case SPTMM_F16: return launch_dtype<SPTMM_F16>(prm, mt, (int)pd, grid, threads, smem, pdl, st);
+        case SPTMM_F32: return launch_dtype<SPTMM_F32>(prm, mt, (int)pd, grid, threads, smem, pdl, st);
     }
     return fail(SPTMM_ERR_INVALID, "gemv: unknown dtype %u", a.dtype);
 }

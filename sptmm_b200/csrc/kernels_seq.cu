@@ -56,6 +56,7 @@ struct SeqParams {
     unsigned long long target;   // counters[s] >= target  <=>  step s finished in this run
     uint32_t nsteps, M, max_cols, ring_slots, xs_bytes, G;
     uint32_t slot_blocks;        // 512-byte blocks per ring slot
+    uint32_t one;                // always 1: a multiplier the compiler cannot fold (LaneAcc::add)
 };
 
 // Timestamp for the optional trace.  A bare read of %globaltimer is hoisted by the assembler
@@ -97,11 +98,121 @@ __device__ __forceinline__ bool seq_bounded_wait(uint32_t bar, uint32_t parity)
     return done != 0;
 }
 
+// Tiles of several rows hold x+128 as unsigned bytes (the form LaneAcc's packed sums expect).
+template <int MT> constexpr uint32_t kTileBias = MT > 1 ? 0x80808080u : 0u;
+template <int MT> __device__ __forceinline__ int8_t tile_byte(int q) { return (int8_t)(MT > 1 ? (q ^ 0x80) : q); }
+
+constexpr int kRedInts = 32 + 16 * 16 + 16;      // scratch ints behind the column sums (see stage_x_quant_rows)
+
+__device__ __forceinline__ int absmax4(int4 v) { return max(max(abs(v.x), abs(v.y)), max(abs(v.z), abs(v.w))); }
+__device__ __forceinline__ int quant1(int v, float scale)
+{
+    return max(-127, min(127, __float2int_rn((float)v * scale)));
+}
+
+// The quantiser for tiles of 4 or 16 rows, all rows at once.  Pass 1: every thread walks the
+// rows in 16-byte pieces (all rows' loads of a piece in flight together) and keeps one running
+// absmax per row; warps combine them through shared memory (two barriers in all).  Pass 2 reads
+// the values again (they are L2-resident), rounds them and writes whole tile words: the four
+// rows of a group are packed into one word per k.  Needs K, the row strides and the pointers
+// to be multiples of four ints; red must hold kRedInts ints.
+template <int MT>
+__device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqDesc &d, uint32_t M, int *red, bool write_scale)
+{
+    static_assert(MT % 4 == 0, "row tiles of 4 or 16");
+    const int4 *A = reinterpret_cast<const int4 *>(d.X);
+    const int4 *B = reinterpret_cast<const int4 *>(d.X2);
+    const uint32_t tid = threadIdx.x, nt = 512, lane = tid & 31, warp = tid >> 5;      // consumer threads only
+    const uint32_t quads = d.K / 4, lda = d.ldx / 4, ldb = d.ldx2 / 4;
+    int *part = red + 32;                     // [16 warps][16 rows]
+    int *amax_s = red + 32 + 256;             // [16 rows]
+
+    int am[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) am[m] = 0;
+    for (uint32_t q = tid; q < quads; q += nt) {
+#pragma unroll
+        for (int g = 0; g < MT / 4; g++) {
+            int4 v[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+                v[r] = (uint32_t)(4 * g + r) < M ? __ldcg(A + (size_t)(4 * g + r) * lda + q) : make_int4(0, 0, 0, 0);
+            if (B) {
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+                    if ((uint32_t)(4 * g + r) < M) {
+                        const int4 b = __ldcg(B + (size_t)(4 * g + r) * ldb + q);
+                        v[r].x += b.x; v[r].y += b.y; v[r].z += b.z; v[r].w += b.w;
+                    }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++) am[4 * g + r] = max(am[4 * g + r], absmax4(v[r]));
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        const int r = __reduce_max_sync(0xffffffffu, am[m]);
+        if (lane == 0) part[warp * 16 + m] = r;
+    }
+    asm volatile("bar.sync 1, 512;" ::: "memory");
+    if (warp < (uint32_t)MT) {                // warp m folds row m
+        const int r = __reduce_max_sync(0xffffffffu, lane < 16 ? part[lane * 16 + warp] : 0);
+        if (lane == 0) amax_s[warp] = r;
+    }
+    asm volatile("bar.sync 1, 512;" ::: "memory");
+    float scale[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        const int a = amax_s[m];
+        scale[m] = a ? 127.0f / (float)a : 0.0f;
+        if (write_scale && d.scale_out && tid == (uint32_t)m && (uint32_t)m < M) d.scale_out[m] = (float)a / 127.0f;
+    }
+
+    for (uint32_t q = tid; q < quads; q += nt) {
+#pragma unroll
+        for (int g = 0; g < MT / 4; g++) {
+            int4 v[4];
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const int m = 4 * g + r;
+                v[r] = (uint32_t)m < M ? __ldcg(A + (size_t)m * lda + q) : make_int4(0, 0, 0, 0);
+                if (B && (uint32_t)m < M) {
+                    const int4 b = __ldcg(B + (size_t)m * ldb + q);
+                    v[r].x += b.x; v[r].y += b.y; v[r].z += b.z; v[r].w += b.w;
+                }
+            }
+            uint32_t o[4];                    // o[i]: rows 4g..4g+3 at k = 4q+i
+#define SPTMM_PACK4(f) ((uint32_t)(quant1(v[0].f, scale[4 * g]) & 0xff) | ((uint32_t)(quant1(v[1].f, scale[4 * g + 1]) & 0xff) << 8) | \
+                        ((uint32_t)(quant1(v[2].f, scale[4 * g + 2]) & 0xff) << 16) | ((uint32_t)(quant1(v[3].f, scale[4 * g + 3]) & 0xff) << 24))
+            o[0] = SPTMM_PACK4(x) ^ 0x80808080u;
+            o[1] = SPTMM_PACK4(y) ^ 0x80808080u;
+            o[2] = SPTMM_PACK4(z) ^ 0x80808080u;
+            o[3] = SPTMM_PACK4(w) ^ 0x80808080u;
+#undef SPTMM_PACK4
+            if constexpr (MT == 4) {
+                *reinterpret_cast<uint4 *>(xs + (size_t)q * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    *reinterpret_cast<uint32_t *>(xs + ((size_t)q * 4 + i) * MT + 4 * g) = o[i];
+            }
+        }
+    }
+    if (tid < (uint32_t)MT) xs[(size_t)d.K * MT + tid] = 0x80;        // the zero row
+}
+
 // int32 rows (optionally the sum of two sources) -> int8 with a per-row absmax scale:
 // q = clamp(rint(v * (127 / amax)), -127, 127), all in fp32; amax == 0 gives zeros.
 template <int MT>
 __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &d, uint32_t M, int *red, bool write_scale)
 {
+    if constexpr (MT >= 4) {
+        if ((d.K & 3) == 0 && (d.ldx & 3) == 0 && (d.ldx2 & 3) == 0 && (reinterpret_cast<uintptr_t>(d.X) & 15) == 0 &&
+            (reinterpret_cast<uintptr_t>(d.X2) & 15) == 0) {
+            stage_x_quant_rows<MT>(xs, d, M, red, write_scale);
+            return;
+        }
+    }
     const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
     const int32_t *B = reinterpret_cast<const int32_t *>(d.X2);
     int8_t *dst = reinterpret_cast<int8_t *>(xs);
@@ -112,7 +223,7 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
         // the input is read once and a row costs one load latency and one barrier.
         for (uint32_t m = 0; m < (uint32_t)MT; m++) {
             if (m >= M) {
-                for (uint32_t k = tid; k < d.K; k += nt) dst[(size_t)k * MT + m] = 0;
+                for (uint32_t k = tid; k < d.K; k += nt) dst[(size_t)k * MT + m] = tile_byte<MT>(0);
                 continue;
             }
             int v[V];
@@ -144,17 +255,17 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
                 if (k < d.K) {
                     int q = __float2int_rn((float)v[j] * scale);
                     q = max(-127, min(127, q));
-                    dst[(size_t)k * MT + m] = (int8_t)q;
+                    dst[(size_t)k * MT + m] = tile_byte<MT>(q);
                 }
             }
             if (write_scale && d.scale_out && tid == 0) d.scale_out[m] = (float)amax / 127.0f;
         }
-        if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = 0;      // the zero row
+        if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);      // the zero row
         return;
     }
     for (uint32_t m = 0; m < (uint32_t)MT; m++) {
         if (m >= M) {
-            for (uint32_t k = tid; k < d.K; k += nt) dst[(size_t)k * MT + m] = 0;
+            for (uint32_t k = tid; k < d.K; k += nt) dst[(size_t)k * MT + m] = tile_byte<MT>(0);
             continue;
         }
         int amax = 0;
@@ -175,11 +286,11 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
             if (B) v += __ldcg(B + (size_t)m * d.ldx2 + k);
             int q = __float2int_rn((float)v * scale);
             q = max(-127, min(127, q));
-            dst[(size_t)k * MT + m] = (int8_t)q;
+            dst[(size_t)k * MT + m] = tile_byte<MT>(q);
         }
         if (write_scale && d.scale_out && tid == 0) d.scale_out[m] = (float)amax / 127.0f;
     }
-    if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = 0;          // the zero row
+    if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);          // the zero row
 }
 
 // int8 rows with a row stride, read around L1 (the buffer may have been written by other CTAs)
@@ -198,12 +309,30 @@ __device__ __forceinline__ void stage_x_i8(unsigned char *xs, const SeqDesc &d, 
             reinterpret_cast<uint4 *>(xs)[j] = __ldcg(reinterpret_cast<const uint4 *>(X) + j);
         }
         for (uint32_t k = vec * 16 + tid; k < d.K; k += nt) dst[k] = __ldcg(X + k);
+    } else if (MT >= 4 && (d.K & 3) == 0 && (d.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(X) & 3) == 0) {
+        // a thread takes four consecutive k from every row (coalesced along k), transposes the
+        // 4 x MT bytes in registers and writes four finished tile rows with 16-byte stores
+        if constexpr (MT >= 4) {
+            const uint32_t quads = d.K / 4;
+            for (uint32_t q = tid; q < quads; q += nt) {
+                uint32_t w[MT], o[MT];
+#pragma unroll
+                for (int m = 0; m < MT; m++)
+                    w[m] = (uint32_t)m < M ? __ldcg(reinterpret_cast<const uint32_t *>(X + (size_t)m * d.ldx) + q) : 0u;
+                transpose_bytes4<MT>(w, o);
+                uint4 *out = reinterpret_cast<uint4 *>(xs + (size_t)q * 4 * MT);
+#pragma unroll
+                for (int i = 0; i < MT / 4; i++)
+                    out[i] = make_uint4(o[4 * i] ^ kTileBias<MT>, o[4 * i + 1] ^ kTileBias<MT>,
+                                        o[4 * i + 2] ^ kTileBias<MT>, o[4 * i + 3] ^ kTileBias<MT>);
+            }
+        }
     } else {
         for (uint32_t m = 0; m < (uint32_t)MT; m++)
             for (uint32_t k = tid; k < d.K; k += nt)
-                dst[(size_t)k * MT + m] = m < M ? __ldcg(X + (size_t)m * d.ldx + k) : (int8_t)0;
+                dst[(size_t)k * MT + m] = tile_byte<MT>(m < M ? (int)__ldcg(X + (size_t)m * d.ldx + k) : 0);
     }
-    if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = 0;
+    if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);
 }
 
 constexpr uint32_t kConsumers = 16;          // consumer warps; warp 16 is the producer
@@ -225,7 +354,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     unsigned char *xs = smem;
     int *c_base = reinterpret_cast<int *>(smem + p.xs_bytes);
     int *red = c_base + 2 * (size_t)p.max_cols * MT;
-    size_t o = p.xs_bytes + (2 * (size_t)p.max_cols * MT + 32) * 4;
+    size_t o = p.xs_bytes + (2 * (size_t)p.max_cols * MT + kRedInts) * 4;
     o = (o + 7) & ~(size_t)7;
     const uint32_t bars_a = (uint32_t)__cvta_generic_to_shared(smem + o);     // [warp][full R | empty R]
     o += (size_t)kConsumers * 2 * R * 8;
@@ -377,28 +506,29 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 }
                 bound = __ldg(d.blk_off + 2 * (size_t)c0 + li + 1);
             }
-            int acc[MT];
-#pragma unroll
-            for (int m = 0; m < MT; m++) acc[m] = 0;
+            LaneAcc<SPTMM_I8, MT> acc;
+            acc.clear(p.one);
             bool dirty = false;
             auto flush = [&]() {
                 const uint32_t col = li >> 1;
+                acc.finish();
 #pragma unroll
                 for (int m = 0; m < MT; m++) {
-                    int v = __reduce_add_sync(0xffffffffu, acc[m]);
+                    int v = __reduce_add_sync(0xffffffffu, acc.v[m]);
                     if (lane == 0) atomicAdd(c_s + col * MT + m, (li & 1) ? -v : v);
-                    acc[m] = 0;
+                    acc.v[m] = 0;
                 }
             };
             auto gather8 = [&](const uint4 v) {
-                gather_add<SPTMM_I8, MT>(acc, v.x & 0xffffu);
-                gather_add<SPTMM_I8, MT>(acc, v.x >> 16);
-                gather_add<SPTMM_I8, MT>(acc, v.y & 0xffffu);
-                gather_add<SPTMM_I8, MT>(acc, v.y >> 16);
-                gather_add<SPTMM_I8, MT>(acc, v.z & 0xffffu);
-                gather_add<SPTMM_I8, MT>(acc, v.z >> 16);
-                gather_add<SPTMM_I8, MT>(acc, v.w & 0xffffu);
-                gather_add<SPTMM_I8, MT>(acc, v.w >> 16);
+                acc.reserve(8);
+                acc.add(v.x & 0xffffu);
+                acc.add(v.x >> 16);
+                acc.add(v.y & 0xffffu);
+                acc.add(v.y >> 16);
+                acc.add(v.z & 0xffffu);
+                acc.add(v.z >> 16);
+                acc.add(v.w & 0xffffu);
+                acc.add(v.w >> 16);
             };
             for (uint32_t b = wb0; b < wb1;) {
                 const uint32_t cnt = min(slot_blocks, wb1 - b);
@@ -560,7 +690,7 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
     // shared memory: X tile, column sums + scratch, then as many 1 KB ring slots per warp as fit
     const uint32_t nwarps = 16;               // consumer warps (one more warp produces)
     q->xs_bytes = (uint32_t)xs_bytes(kmax, (int)q->mt);
-    size_t fixed = q->xs_bytes + (2 * (size_t)q->max_cols * q->mt + 32) * 4;
+    size_t fixed = q->xs_bytes + (2 * (size_t)q->max_cols * q->mt + kRedInts) * 4;
     fixed = (fixed + 7) & ~(size_t)7;
     const size_t avail = 223 * 1024;      // minus static shared memory and the gap before the tile
     // 4 KB slots stream best; halve them while three of them per warp do not fit beside the X tile
@@ -651,7 +781,7 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     // a step is complete once every CTA of every rank has reported
     prm.target = (unsigned long long)q->G * q->epoch * (q->n_peers ? q->n_peers : 1);
     prm.nsteps = q->nsteps; prm.M = q->M; prm.max_cols = q->max_cols; prm.ring_slots = q->ring_slots;
-    prm.xs_bytes = q->xs_bytes; prm.G = q->G; prm.slot_blocks = q->slot_blocks;
+    prm.xs_bytes = q->xs_bytes; prm.G = q->G; prm.slot_blocks = q->slot_blocks; prm.one = 1;
     cudaStream_t st = (cudaStream_t)stream;
     switch (q->mt) {
         case 1: return seq_launch<1>(q, prm, st);
@@ -764,7 +894,7 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
     }
     const uint32_t nwarps = 16;
     q.xs_bytes = (uint32_t)xs_bytes(kmax, (int)q.mt);
-    size_t fixed = q.xs_bytes + (2 * (size_t)q.max_cols * q.mt + 32) * 4;
+    size_t fixed = q.xs_bytes + (2 * (size_t)q.max_cols * q.mt + kRedInts) * 4;
     fixed = (fixed + 7) & ~(size_t)7;
     const size_t avail = 223 * 1024;
     uint32_t slot_blocks = kMaxSlotBlocks;
@@ -796,7 +926,7 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
     prm.trace = nullptr;
     prm.target = q.G;                              // counters were just cleared: one run's worth
     prm.nsteps = n; prm.M = M; prm.max_cols = q.max_cols; prm.ring_slots = q.ring_slots;
-    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks;
+    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1;
     int rc = SPTMM_OK;
     switch (q.mt) {
         case 1: rc = seq_launch<1>(&q, prm, st); break;
