@@ -339,7 +339,8 @@ def run_ours(args):
         del out
         torch.cuda.empty_cache()
         for m_rows in (1, 4, 16):
-            stk = stack_mod.TernaryStack(args.stack_layers, 2560, 6912, 640, M=m_rows, p_zero=1 / 3, seed=0, rank=rank, world=world)
+            stk = stack_mod.TernaryStack(args.stack_layers, 2560, 6912, 640, M=m_rows, p_zero=1 / 3, seed=0, rank=rank, world=world,
+                                          tagged=args.stack_tagged)
             stk.set_input(O.gen_x_i8(m_rows * 2560, 5).reshape(m_rows, 2560))
             with torch.cuda.stream(st):
                 for _ in range(3):
@@ -368,7 +369,8 @@ def run_ours(args):
                 total_bytes = float(tb.item())
             stack_info["M%d" % m_rows] = {"us_per_pass": sms * 1e3, "tokens_per_s": m_rows / (sms * 1e-3),
                                           "encoded_GB": total_bytes / 1e9, "GBps_all_gpus": total_bytes / (sms * 1e-3) / 1e9,
-                                          "status_ok": ok, "layers": args.stack_layers, "steps_per_pass": stk.n_steps}
+                                          "status_ok": ok, "layers": args.stack_layers, "steps_per_pass": stk.n_steps,
+                                          "exchange": "tagged words" if args.stack_tagged else "step counters"}
             del stk
             torch.cuda.empty_cache()
 
@@ -493,6 +495,7 @@ def main():
     ap.add_argument("--no-seq", action="store_true", help="skip the persistent-sequence measurement")
     ap.add_argument("--no-stack", action="store_true", help="skip the layer-stack measurement")
     ap.add_argument("--stack-layers", type=int, default=30)
+    ap.add_argument("--stack-tagged", action="store_true", help="layer stack hands activations on as tagged words (x_kind 2)")
     ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
     args = ap.parse_args()
     if args.impl == "reference":

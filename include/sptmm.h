@@ -154,7 +154,18 @@ typedef struct sptmm_seq_step {
     uint32_t replica;        /* which uploaded copy of w                                          */
     uint32_t x_kind;         /* 0: X is int8.  1: X (and X2, if set) are int32 results of earlier
                                 steps; their sum is quantised per row to int8 with
-                                q = clamp(rint(v * (127/absmax)), -127, 127) before the matmul    */
+                                q = clamp(rint(v * (127/absmax)), -127, 127) before the matmul.
+                                2: as 1, with the tagged exchange: X (and X2) lie in the output of
+                                step `dep`, which then stores every result as
+                                (tag << 24) | (value & 0xffffff) -- the tag changes with every
+                                write of the buffer -- and this step waits for the words
+                                themselves to turn current instead of for a step counter (no
+                                fence, one memory round trip less per step).  Every step that
+                                writes that buffer must feed an x_kind 2 reader; the host sees
+                                tagged words there ((int32)(w << 8) >> 8 recovers the value; it
+                                always fits, since |value| <= 127*K < 2^23).  A buffer may be
+                                rewritten by the second step after the one that reads it, not
+                                by the next one.                                                  */
     const void *X;           /* device, M rows of K elements, row stride ldx (0 = K)              */
     const void *X2;          /* optional second int32 source, row stride ldx2 (0 = K)             */
     void *C;                 /* device int32, M rows of N, row stride ldc (0 = N)                 */

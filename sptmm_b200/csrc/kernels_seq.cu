@@ -42,7 +42,57 @@ struct SeqDesc {
     uint32_t K, N, ldx, ldx2, ldc, uniform_nbl, x_kind;
     int32_t dep;                 // step that must be complete before this one reads X, or -1
     int32_t *Cp[kMaxPeers];      // multi-GPU: this shard's place in every rank's output buffer
+    // Tagged exchange (x_kind 2 consumers).  A tagged output word is (tag << 24) | (value & 0xffffff)
+    // with tag = seq_tag(run, m, j): j counts the steps of one run that write this buffer, m is
+    // their number, so two successive writes of a word never carry the same tag and a reader can
+    // tell a fresh value from the one it replaces without any flag or fence.
+    uint32_t out_tag_m, out_tag_j;   // this step's output: m == 0 -> plain int32
+    uint32_t in_tag_m, in_tag_j;     // x_kind 2: the tag of the step that produces X (and X2)
+    uint32_t release;                // 1: bump the step counter after the output is stored
 };
+
+constexpr uint32_t kPollLimit = 1u << 20;        // reloads of one stale word before giving up
+
+__device__ __forceinline__ uint32_t seq_tag(uint32_t run_mod, uint32_t m, uint32_t j) { return 1u + (run_mod * m + j) % 255u; }
+__device__ __forceinline__ int untag(int v) { return (v << 8) >> 8; }          // sign-extend the low 24 bits
+
+// (poll_batch below is the form the staging code uses: it keeps a thread's reloads in flight together)
+// a load other CTAs' (and, with sys, other GPUs') plain stores become visible to
+__device__ __forceinline__ int ld_fresh(const int32_t *p, bool sys)
+{
+    int v;
+    if (sys) asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    else asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int4 ld_fresh4(const int4 *p, bool sys)
+{
+    int4 v;
+    if (sys) asm volatile("ld.relaxed.sys.global.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    else asm volatile("ld.relaxed.gpu.global.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// v[j] was loaded from base[tid + j*nt] (entries at or beyond K are not used).  Round by round,
+// reload the words that do not carry `tag` yet -- all reloads of a round in flight at once -- until
+// none is stale (bounded); then strip the tags.
+template <int V>
+__device__ __forceinline__ void poll_batch(int (&v)[V], const int32_t *base, uint32_t K, uint32_t tid, uint32_t nt,
+                                           uint32_t tag, bool sys, bool &ok)
+{
+    for (uint32_t it = 0; ok; it++) {
+        bool stale = false;
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+            const uint32_t k = tid + j * nt;
+            if (k < K && ((uint32_t)v[j] >> 24) != tag) { stale = true; v[j] = ld_fresh(base + k, sys); }
+        }
+        if (!stale) break;
+        if (it >= kPollLimit) ok = false;
+    }
+#pragma unroll
+    for (int j = 0; j < V; j++) v[j] = untag(v[j]);
+}
+
 
 struct SeqParams {
     const SeqDesc *desc;
@@ -57,6 +107,7 @@ struct SeqParams {
     uint32_t nsteps, M, max_cols, ring_slots, xs_bytes, G;
     uint32_t slot_blocks;        // 512-byte blocks per ring slot
     uint32_t one;                // always 1: a multiplier the compiler cannot fold (LaneAcc::add)
+    uint32_t run_mod;            // run number mod 255 (tags of the tagged exchange change every run)
 };
 
 // Timestamp for the optional trace.  A bare read of %globaltimer is hoisted by the assembler
@@ -117,8 +168,37 @@ __device__ __forceinline__ int quant1(int v, float scale)
 // rows of a group are packed into one word per k.  Needs K, the row strides and the pointers
 // to be multiples of four ints; red must hold kRedInts ints.
 template <int MT>
-__device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqDesc &d, uint32_t M, int *red, bool write_scale)
+__device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqDesc &d, uint32_t M, int *red, bool write_scale,
+                                                   uint32_t tag, bool sys, bool &ok)
 {
+    // tag != 0: the sources hold tagged words; the first pass waits for each to become current
+    auto stale4 = [&](const int4 &v) {
+        return ((uint32_t)v.x >> 24) != tag || ((uint32_t)v.y >> 24) != tag || ((uint32_t)v.z >> 24) != tag || ((uint32_t)v.w >> 24) != tag;
+    };
+    // rows 4g..4g+3 of one source at piece q; with a tag, reload the stale ones round by round
+    // (the reloads of a round in flight together) until all four are current
+    auto fetch_rows = [&](const int4 *S, uint32_t ld, int g, uint32_t q, int4 (&v)[4]) {
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+            v[r] = (uint32_t)(4 * g + r) < M ? __ldcg(S + (size_t)(4 * g + r) * ld + q) : make_int4(0, 0, 0, 0);
+        if (tag) {
+            for (uint32_t it = 0; ok; it++) {
+                bool stale = false;
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+                    if ((uint32_t)(4 * g + r) < M && stale4(v[r])) { stale = true; v[r] = ld_fresh4(S + (size_t)(4 * g + r) * ld + q, sys); }
+                if (!stale) break;
+                if (it >= kPollLimit) ok = false;
+            }
+#pragma unroll
+            for (int r = 0; r < 4; r++) v[r] = make_int4(untag(v[r].x), untag(v[r].y), untag(v[r].z), untag(v[r].w));
+        }
+    };
+    auto again4 = [&](const int4 *p) {
+        int4 v = __ldcg(p);
+        if (tag) v = make_int4(untag(v.x), untag(v.y), untag(v.z), untag(v.w));
+        return v;
+    };
     static_assert(MT % 4 == 0, "row tiles of 4 or 16");
     const int4 *A = reinterpret_cast<const int4 *>(d.X);
     const int4 *B = reinterpret_cast<const int4 *>(d.X2);
@@ -134,16 +214,12 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
 #pragma unroll
         for (int g = 0; g < MT / 4; g++) {
             int4 v[4];
-#pragma unroll
-            for (int r = 0; r < 4; r++)
-                v[r] = (uint32_t)(4 * g + r) < M ? __ldcg(A + (size_t)(4 * g + r) * lda + q) : make_int4(0, 0, 0, 0);
+            fetch_rows(A, lda, g, q, v);
             if (B) {
+                int4 b[4];
+                fetch_rows(B, ldb, g, q, b);
 #pragma unroll
-                for (int r = 0; r < 4; r++)
-                    if ((uint32_t)(4 * g + r) < M) {
-                        const int4 b = __ldcg(B + (size_t)(4 * g + r) * ldb + q);
-                        v[r].x += b.x; v[r].y += b.y; v[r].z += b.z; v[r].w += b.w;
-                    }
+                for (int r = 0; r < 4; r++) { v[r].x += b[r].x; v[r].y += b[r].y; v[r].z += b[r].z; v[r].w += b[r].w; }
             }
 #pragma unroll
             for (int r = 0; r < 4; r++) am[4 * g + r] = max(am[4 * g + r], absmax4(v[r]));
@@ -175,9 +251,9 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
 #pragma unroll
             for (int r = 0; r < 4; r++) {
                 const int m = 4 * g + r;
-                v[r] = (uint32_t)m < M ? __ldcg(A + (size_t)m * lda + q) : make_int4(0, 0, 0, 0);
+                v[r] = (uint32_t)m < M ? again4(A + (size_t)m * lda + q) : make_int4(0, 0, 0, 0);
                 if (B && (uint32_t)m < M) {
-                    const int4 b = __ldcg(B + (size_t)m * ldb + q);
+                    const int4 b = again4(B + (size_t)m * ldb + q);
                     v[r].x += b.x; v[r].y += b.y; v[r].z += b.z; v[r].w += b.w;
                 }
             }
@@ -203,13 +279,28 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
 
 // int32 rows (optionally the sum of two sources) -> int8 with a per-row absmax scale:
 // q = clamp(rint(v * (127 / amax)), -127, 127), all in fp32; amax == 0 gives zeros.
-template <int MT>
-__device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &d, uint32_t M, int *red, bool write_scale)
+template <int MT, bool TAGGED>
+__device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &d, uint32_t M, int *red, bool write_scale,
+                                              uint32_t tag_in, bool sys, bool &ok)
 {
+    const uint32_t tag = TAGGED ? tag_in : 0u;       // a kernel without tagged steps carries none of the waiting code
+    // tag != 0: the sources hold tagged words (see SeqDesc); wait for each to become current
+    auto first = [&](const int32_t *p) {          // rows too long for the one-pass form: one word at a time
+        int v = __ldcg(p);
+        if (tag) {
+            for (uint32_t it = 0; ok && ((uint32_t)v >> 24) != tag; it++) {
+                if (it >= kPollLimit) { ok = false; break; }
+                v = ld_fresh(p, sys);
+            }
+            v = untag(v);
+        }
+        return v;
+    };
+    auto again = [&](const int32_t *p) { const int v = __ldcg(p); return tag ? untag(v) : v; };
     if constexpr (MT >= 4) {
         if ((d.K & 3) == 0 && (d.ldx & 3) == 0 && (d.ldx2 & 3) == 0 && (reinterpret_cast<uintptr_t>(d.X) & 15) == 0 &&
             (reinterpret_cast<uintptr_t>(d.X2) & 15) == 0) {
-            stage_x_quant_rows<MT>(xs, d, M, red, write_scale);
+            stage_x_quant_rows<MT>(xs, d, M, red, write_scale, tag, sys, ok);
             return;
         }
     }
@@ -230,13 +321,29 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
 #pragma unroll
             for (int j = 0; j < V; j++) {
                 const uint32_t k = tid + j * nt;
-                v[j] = k < d.K ? __ldcg(A + (size_t)m * d.ldx + k) : 0;
+                v[j] = k < d.K ? __ldcg(A + (size_t)m * d.ldx + k) : 0;          // all loads in flight, then the tag checks
             }
-            if (B) {
+            if (tag) poll_batch<V>(v, A + (size_t)m * d.ldx, d.K, tid, nt, tag, sys, ok);
+            if (B && !tag) {
 #pragma unroll
                 for (int j = 0; j < V; j++) {
                     const uint32_t k = tid + j * nt;
                     if (k < d.K) v[j] += __ldcg(B + (size_t)m * d.ldx2 + k);
+                }
+            } else if (B) {
+                constexpr int VB = 14;                            // second source in batches: loads first, checks after
+#pragma unroll
+                for (int j0 = 0; j0 < V; j0 += VB) {
+                    int b[VB];
+#pragma unroll
+                    for (int j = 0; j < VB; j++) {
+                        const uint32_t k = tid + (j0 + j) * nt;
+                        b[j] = k < d.K ? __ldcg(B + (size_t)m * d.ldx2 + k) : 0;
+                    }
+                    const uint32_t done = (uint32_t)j0 * nt;
+                    poll_batch<VB>(b, B + (size_t)m * d.ldx2 + done, d.K > done ? d.K - done : 0u, tid, nt, tag, sys, ok);
+#pragma unroll
+                    for (int j = 0; j < VB; j++) v[j0 + j] += b[j];
                 }
             }
             int amax = 0;
@@ -270,8 +377,8 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
         }
         int amax = 0;
         for (uint32_t k = tid; k < d.K; k += nt) {
-            int v = __ldcg(A + (size_t)m * d.ldx + k);
-            if (B) v += __ldcg(B + (size_t)m * d.ldx2 + k);
+            int v = first(A + (size_t)m * d.ldx + k);
+            if (B) v += first(B + (size_t)m * d.ldx2 + k);
             amax = max(amax, abs(v));
         }
         amax = __reduce_max_sync(0xffffffffu, amax);
@@ -282,8 +389,8 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
         for (uint32_t w = 0; w < nwarps; w++) amax = max(amax, red[w]);
         const float scale = amax ? 127.0f / (float)amax : 0.0f;
         for (uint32_t k = tid; k < d.K; k += nt) {
-            int v = __ldcg(A + (size_t)m * d.ldx + k);
-            if (B) v += __ldcg(B + (size_t)m * d.ldx2 + k);
+            int v = again(A + (size_t)m * d.ldx + k);
+            if (B) v += again(B + (size_t)m * d.ldx2 + k);
             int q = __float2int_rn((float)v * scale);
             q = max(-127, min(127, q));
             dst[(size_t)k * MT + m] = tile_byte<MT>(q);
@@ -340,7 +447,7 @@ constexpr uint32_t kConsumerThreads = kConsumers * 32;
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
-template <int MT>
+template <int MT, bool TAGGED>
 __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_constant__ SeqParams p)
 {
     extern __shared__ __align__(128) unsigned char dyn_smem[];
@@ -445,7 +552,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         int *c_s = c_base + (s & 1) * (size_t)p.max_cols * MT;
         const bool tracing = p.trace != nullptr && cta == 0 && tid == 33 && s < 256;
         // ---- wait until the step this one depends on has finished everywhere
-        if (d.dep >= 0) {
+        if (d.dep >= 0 && !(TAGGED && d.x_kind == 2)) {     // tagged inputs are waited for word by word while staging
             if (tid == 0 && !failed) {
                 const unsigned long long *ctr = p.counters + d.dep;
                 unsigned long long v = 0;
@@ -462,6 +569,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
 #ifdef SPTMM_SEQ_PROFILE
         if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
             p.trace[1024 + 64 + (s - 100) * 16 + warp] = seq_ns(&failed);
+        if (p.trace != nullptr && tid == 33 && s >= 100 && s < 104) p.trace[2048 + (s - 100) * 256 + cta] = seq_ns(&failed);   // every CTA: past the wait
 #endif
 
         // ---- activations and column sums
@@ -472,7 +580,12 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         uint32_t nxt = 0;
         if (s + 1 < p.nsteps) nxt = load_step_word(s + 1);
         if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
-        else stage_x_quant<MT>(xs, d, p.M, red, cta == 0);
+        else {
+            bool fresh = failed == 0;          // after a failure nothing waits any more
+            const uint32_t tag = (TAGGED && d.x_kind == 2) ? seq_tag(p.run_mod, d.in_tag_m, d.in_tag_j) : 0u;
+            stage_x_quant<MT, TAGGED>(xs, d, p.M, red, cta == 0, tag, p.n_peers != 0, fresh);
+            if (!fresh && !failed) { failed = 1; atomicOr(p.status, 2u); }      // a producer's word never arrived
+        }
 #ifdef SPTMM_SEQ_PROFILE
         if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
             p.trace[1024 + (s - 100) * 16 + warp] = seq_ns(&failed) + (xs[tid] == 77 && xs[tid + 1] == 78 && xs[tid + 2] == 99);
@@ -484,6 +597,9 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             held_slot = -1;
         }
         if (tracing) p.trace[s * 4 + 1] = seq_ns(&failed);
+#ifdef SPTMM_SEQ_PROFILE
+        if (p.trace != nullptr && tid == 33 && s >= 100 && s < 104) p.trace[3072 + (s - 100) * 256 + cta] = seq_ns(&failed);   // every CTA: X staged
+#endif
 
         // ---- gather this warp's blocks out of its ring
         const uint32_t nb = b1 - b0;
@@ -568,28 +684,35 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         if (s + 1 < p.nsteps) store_step_word(s + 1, nxt);
         consumer_sync();
         if (tracing) p.trace[s * 4 + 2] = seq_ns(&failed);
+#ifdef SPTMM_SEQ_PROFILE
+        if (p.trace != nullptr && tid == 33 && s >= 100 && s < 104) p.trace[4096 + (s - 100) * 256 + cta] = seq_ns(&failed);   // every CTA: gathered
+#endif
 
         // ---- results out, then tell the other CTAs this step is done here.  Warp 0 does it alone
         // while the others move on (the next step accumulates into the other buffer).
         if (warp == 0) {
+            // a tagged output carries its tag in the top byte (|value| < 2^23 because K < 65536)
+            const bool tag_out = TAGGED && d.out_tag_m != 0;
+            const uint32_t otag = tag_out ? seq_tag(p.run_mod, d.out_tag_m, d.out_tag_j) << 24 : 0u;
+            auto out_word = [&](int v) { return tag_out ? (int)(otag | ((uint32_t)v & 0xffffffu)) : v; };
             if (p.n_peers == 0) {
                 for (uint32_t i = lane; i < ncols * p.M; i += 32) {
                     const uint32_t m = i / ncols, col = i - m * ncols;
-                    d.C[(size_t)m * d.ldc + c0 + col] = c_s[col * MT + m];
+                    d.C[(size_t)m * d.ldc + c0 + col] = out_word(c_s[col * MT + m]);
                 }
                 __syncwarp();
                 // the release orders this warp's stores (seen by lane 0 through __syncwarp) before the count
-                if (lane == 0) asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
+                if (lane == 0 && (!TAGGED || d.release)) asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
             } else {
                 // the exchange: this CTA's columns go straight into every rank's buffer over NVLink
                 // (plain peer stores), then every rank's counter for the step is bumped
                 for (uint32_t i = lane; i < ncols * p.M; i += 32) {
                     const uint32_t m = i / ncols, col = i - m * ncols;
-                    const int v = c_s[col * MT + m];
+                    const int v = out_word(c_s[col * MT + m]);
                     for (uint32_t r = 0; r < p.n_peers; r++) d.Cp[r][(size_t)m * d.ldc + c0 + col] = v;
                 }
                 __syncwarp();
-                if (lane < p.n_peers)
+                if (lane < p.n_peers && (!TAGGED || d.release))
                     asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p.counter_peers[lane] + s) : "memory");
             }
         }
@@ -611,6 +734,7 @@ struct sptmm_seq {
     void *d_desc = nullptr, *d_blk = nullptr, *d_col = nullptr, *d_counters = nullptr, *d_status = nullptr;
     void *d_trace = nullptr;
     uint32_t n_peers = 0, my_rank = 0;
+    bool tagged = false;             // some step reads tagged words: run the kernel variant that knows them
     void *counter_peers[kMaxPeers] = {};
 };
 
@@ -663,7 +787,8 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         if (!w || !st.X || (!st.C && !n_peers)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u has a null pointer", s);
         else if (w->format != SPTMM_FMT_U16_V256) rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u is not in the native u16 format", s);
         else if (w->device != dev || st.replica >= w->dev.size()) rc = fail(SPTMM_ERR_STATE, "seq_create: step %u weights are not uploaded to device %d (replica %u)", s, dev, st.replica);
-        else if (st.x_kind > 1) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
+        else if (st.x_kind > 2) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
+        else if (st.x_kind == 2 && st.dep < 0) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u reads tagged words but names no producer (dep)", s);
         else if (st.dep >= (int32_t)s) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u depends on step %d, which does not precede it", s, st.dep);
         if (rc != SPTMM_OK) { seq_release(q); return rc; }
         SeqDesc &d = desc[s];
@@ -687,6 +812,42 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         kmax = std::max(kmax, w->K);
         q->stream_bytes += w->stream_bytes;
     }
+    // Tagged exchange: a step with x_kind 2 makes the step it names in `dep` store tagged words.
+    // Every step writing that buffer must then be tagged (a plain value could pass for a tag), and
+    // nobody may wait for such a step through its counter, which it no longer bumps.
+    {
+        std::vector<char> tagged(n, 0);
+        for (uint32_t s = 0; s < n; s++)
+            if (steps[s].x_kind == 2) { tagged[(uint32_t)steps[s].dep] = 1; q->tagged = true; }
+        int rc = SPTMM_OK;
+        for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++) {
+            desc[s].release = tagged[s] ? 0 : 1;
+            if (steps[s].x_kind != 2 && steps[s].dep >= 0 && tagged[(uint32_t)steps[s].dep])
+                rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u waits for step %d, whose output is tagged for an x_kind 2 reader", s, steps[s].dep);
+            if (!tagged[s]) continue;
+            uint32_t m = 0, j = 0;
+            for (uint32_t t = 0; t < n; t++)
+                if (desc[t].C == desc[s].C) {
+                    if (!tagged[t]) rc = fail(SPTMM_ERR_INVALID, "seq_create: steps %u and %u write the same buffer, but only one of them feeds an x_kind 2 reader", s, t);
+                    if (t < s) j++;
+                    m++;
+                }
+            desc[s].out_tag_m = m; desc[s].out_tag_j = j;
+        }
+        for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++)
+            if (steps[s].x_kind == 2) {
+                const SeqDesc &pd = desc[(uint32_t)steps[s].dep];
+                desc[s].in_tag_m = pd.out_tag_m; desc[s].in_tag_j = pd.out_tag_j;
+                // the producer's rows are ldc wide and its columns (one shard of them, on several
+                // GPUs) start somewhere inside the first row: accept any address within the rows
+                const char *lo = (const char *)pd.C - (size_t)(pd.ldc - pd.N) * 4, *hi = (const char *)pd.C + (size_t)M * pd.ldc * 4;
+                const char *x = (const char *)steps[s].X, *x2 = (const char *)steps[s].X2;
+                if (x < lo || x >= hi || (x2 && (x2 < lo || x2 >= hi)))
+                    rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u reads tagged words outside the output of step %d", s, steps[s].dep);
+            }
+        if (rc != SPTMM_OK) { seq_release(q); return rc; }
+    }
+
     // shared memory: X tile, column sums + scratch, then as many 1 KB ring slots per warp as fit
     const uint32_t nwarps = 16;               // consumer warps (one more warp produces)
     q->xs_bytes = (uint32_t)xs_bytes(kmax, (int)q->mt);
@@ -743,12 +904,21 @@ extern "C" int sptmm_seq_create_shared(const sptmm_seq_step *steps, uint32_t n, 
     return seq_create_impl(steps, n, M, C_peers, counter_peers, n_peers, my_rank, out);
 }
 
+template <int MT, bool TAGGED>
+static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st);
+
 template <int MT>
 static int seq_launch(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
 {
+    return q->tagged ? seq_launch_as<MT, true>(q, prm, st) : seq_launch_as<MT, false>(q, prm, st);
+}
+
+template <int MT, bool TAGGED>
+static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
+{
     static int configured_device = -1;
     if (configured_device != q->device) {
-        SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_seq<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_seq<MT, TAGGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured_device = q->device;
     }
     cudaLaunchConfig_t cfg = {};
@@ -757,7 +927,7 @@ static int seq_launch(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
     attr[0].id = cudaLaunchAttributeCooperative;      // all CTAs resident at once, or the launch fails
     attr[0].val.cooperative = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    SPTMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, k_seq<MT>, prm));
+    SPTMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, k_seq<MT, TAGGED>, prm));
     return SPTMM_OK;
 }
 
@@ -782,6 +952,7 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     prm.target = (unsigned long long)q->G * q->epoch * (q->n_peers ? q->n_peers : 1);
     prm.nsteps = q->nsteps; prm.M = q->M; prm.max_cols = q->max_cols; prm.ring_slots = q->ring_slots;
     prm.xs_bytes = q->xs_bytes; prm.G = q->G; prm.slot_blocks = q->slot_blocks; prm.one = 1;
+    prm.run_mod = (uint32_t)(q->epoch % 255);
     cudaStream_t st = (cudaStream_t)stream;
     switch (q->mt) {
         case 1: return seq_launch<1>(q, prm, st);
@@ -885,6 +1056,7 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
         d.ldx = st.ldx ? st.ldx : w->K; d.ldx2 = st.ldx2 ? st.ldx2 : w->K; d.ldc = st.ldc ? st.ldc : w->N;
         d.uniform_nbl = w->uniform_nbl; d.x_kind = st.x_kind; d.dep = st.dep < 0 ? -1 : st.dep;
         for (uint32_t r = 0; r < kMaxPeers; r++) d.Cp[r] = nullptr;
+        d.release = 1;
         uint32_t mc = 1, mb = 0;
         plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q.G, tb, tc, mc, mb);
         blk.insert(blk.end(), tb.begin(), tb.end());
@@ -926,7 +1098,7 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
     prm.trace = nullptr;
     prm.target = q.G;                              // counters were just cleared: one run's worth
     prm.nsteps = n; prm.M = M; prm.max_cols = q.max_cols; prm.ring_slots = q.ring_slots;
-    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1;
+    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1; prm.run_mod = 0;
     int rc = SPTMM_OK;
     switch (q.mt) {
         case 1: rc = seq_launch<1>(&q, prm, st); break;

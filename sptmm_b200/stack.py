@@ -48,11 +48,12 @@ def stack_weights(layers: int, hidden: int, ffn: int, kv: int, p_zero: float, se
 
 class TernaryStack:
     def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, M=1, p_zero=1 / 3, seed=0,
-                 rank=0, world=1, group=None, keep_dense=False):
+                 rank=0, world=1, group=None, keep_dense=False, tagged=False):
         import torch
         self.torch = torch
         self.layers, self.hidden, self.ffn, self.kv, self.M = layers, hidden, ffn, kv, M
         self.rank, self.world = rank, world
+        self.tagged = tagged        # steps hand their outputs on as tagged words (x_kind 2): no counters, no fences
         self.dense = [] if keep_dense else None
         shapes = layer_shapes(hidden, ffn, kv)
         widths = {name: N for name, _, N in shapes}
@@ -72,7 +73,8 @@ class TernaryStack:
         n_steps = 4 * layers
         off, cur = {}, 0
         off["counters"] = cur; cur += n_steps * 8
-        for name in ("qkv", "o", "gu", "down"):
+        widths["out"] = widths["down"]           # the last step's result: never tagged, no reader inside the kernel
+        for name in ("qkv", "o", "gu", "down", "out"):
             cur = (cur + 255) & ~255
             off[name] = cur; cur += M * widths[name] * 4
         cur = (cur + 255) & ~255
@@ -94,6 +96,7 @@ class TernaryStack:
 
         # ---- the step list
         steps = []
+        xk = 2 if tagged else 1
         for l in range(layers):
             for i, (name, K, N) in enumerate(shapes):
                 s = 4 * l + i
@@ -103,17 +106,18 @@ class TernaryStack:
                     if l == 0:
                         st.update(X=self.x_in, x_kind=0)
                     else:
-                        st.update(X=mine + off["down"], x_kind=1, ldx=hidden)
+                        st.update(X=mine + off["down"], x_kind=xk, ldx=hidden)
                 elif name == "o":
-                    st.update(X=mine + off["qkv"], x_kind=1, ldx=widths["qkv"])
+                    st.update(X=mine + off["qkv"], x_kind=xk, ldx=widths["qkv"])
                 elif name == "gu":
-                    st.update(X=mine + off["o"], x_kind=1, ldx=hidden)
+                    st.update(X=mine + off["o"], x_kind=xk, ldx=hidden)
                 else:
-                    st.update(X=mine + off["gu"], X2=mine + off["gu"] + ffn * 4, x_kind=1, ldx=2 * ffn, ldx2=2 * ffn)
+                    st.update(X=mine + off["gu"], X2=mine + off["gu"] + ffn * 4, x_kind=xk, ldx=2 * ffn, ldx2=2 * ffn)
+                dst = "out" if s == n_steps - 1 else name
                 if world > 1:
-                    st["C_peers"] = [b + off[name] + c0 * 4 for b in bases]
+                    st["C_peers"] = [b + off[dst] + c0 * 4 for b in bases]
                 else:
-                    st["C"] = mine + off[name] + c0 * 4
+                    st["C"] = mine + off[dst] + c0 * 4
                 steps.append(st)
         counter_peers = [b + off["counters"] for b in bases] if world > 1 else None
         self.seq = sp.Sequence(steps, M=M, counter_peers=counter_peers, rank=rank)
@@ -126,10 +130,15 @@ class TernaryStack:
         self.seq.run(stream)
 
     def buffer(self, name: str) -> np.ndarray:
-        """This rank's copy of an activation buffer (int32, M x width), after a synchronise."""
+        """This rank's copy of an activation buffer (int32, M x width), after a synchronise: the
+        last values written to "qkv", "o", "gu" and, as "down", the stack's final result."""
         width = dict((n, N) for n, _, N in layer_shapes(self.hidden, self.ffn, self.kv))[name]
-        t = self.arena[self.off[name]: self.off[name] + self.M * width * 4].view(self.torch.int32)
-        return t.cpu().numpy().reshape(self.M, width)
+        src = "out" if name == "down" else name
+        t = self.arena[self.off[src]: self.off[src] + self.M * width * 4].view(self.torch.int32)
+        v = t.cpu().numpy().reshape(self.M, width)
+        if self.tagged and src != "out":
+            v = (v << 8) >> 8                    # drop the tag byte, sign-extend the 24-bit value
+        return v
 
     def status(self) -> int:
         return self.seq.status()

@@ -48,8 +48,9 @@ def gpu_parity():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
     layers, hidden, ffn, kv = 3, 256, 512, 64
-    for M in (1, 4):
-        st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, rank=rank, world=world, keep_dense=True)
+    for M, tagged in ((1, False), (4, False), (1, True), (4, True)):
+        st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, rank=rank, world=world, keep_dense=True,
+                            tagged=tagged)
         x = O.gen_x_i8(M * hidden, 9).reshape(M, hidden)
         st.set_input(x)
         want = S.reference_forward(st.dense, layers, hidden, ffn, kv, x, O.gemv_i8_dense, O.quant_absmax_i8)
@@ -60,7 +61,7 @@ def gpu_parity():
             assert st.status() == 0, "a bounded wait ran out on rank %d" % rank
             dist.barrier()
             for name in ("qkv", "o", "gu", "down"):
-                assert (st.buffer(name) == want[name]).all(), (rank, M, name)
+                assert (st.buffer(name) == want[name]).all(), (rank, M, tagged, name)
         del st
     dist.barrier()
     if rank == 0:

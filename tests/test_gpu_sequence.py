@@ -91,6 +91,62 @@ def test_dependent_chain_with_fused_quantiser(M):
         assert (s2.cpu().numpy() == sc1).all() and (s3.cpu().numpy() == sc2).all()
 
 
+@pytest.mark.parametrize("M", [1, 3, 16])
+def test_dependent_chain_with_tagged_exchange(M):
+    """The same chain with x_kind 2: producers store (tag << 24 | value) and readers wait for the
+    words themselves instead of a step counter.  Several runs in a row (the tag changes every
+    run), a buffer written by two steps of one run, results bit-exact as before."""
+    K1, N1, H, N3 = 512, 384, 320, 200
+    W1 = sp.gen_ternary_iid(K1, N1, 0.4, 1)
+    W2 = sp.gen_ternary_iid(N1, 2 * H, 0.5, 2)
+    W3 = sp.gen_ternary_iid(H, N1, 1 / 3, 3)            # back to width N1: its output reuses W1's buffer
+    W4 = sp.gen_ternary_iid(N1, N3, 0.6, 4)
+    w1, w2, w3, w4 = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (W1, W2, W3, W4))
+    X = O.gen_x_i8(M * K1, 4)
+    c1 = torch.zeros((M, N1), dtype=torch.int32, device="cuda")      # written by steps 0 and 2
+    c2 = torch.zeros((M, 2 * H), dtype=torch.int32, device="cuda")
+    c4 = torch.zeros((M, N3), dtype=torch.int32, device="cuda")
+    seq = sp.Sequence([
+        {"w": w1, "X": dev(X), "C": c1},
+        {"w": w2, "X": c1, "C": c2, "x_kind": 2, "dep": 0},
+        {"w": w3, "X": c2, "X2": c2[:, H:], "ldx": 2 * H, "ldx2": 2 * H, "C": c1, "x_kind": 2, "dep": 1},
+        {"w": w4, "X": c1, "C": c4, "x_kind": 2, "dep": 2},
+    ], M=M)
+    r1 = O.gemv_i8_dense(X, W1)
+    q1, _ = O.quant_absmax_i8(r1)
+    r2 = O.gemv_i8_dense(q1.reshape(-1), W2)
+    q2, _ = O.quant_absmax_i8(r2[:, :H], r2[:, H:])
+    r3 = O.gemv_i8_dense(q2.reshape(-1), W3)
+    q3, _ = O.quant_absmax_i8(r3)
+    r4 = O.gemv_i8_dense(q3.reshape(-1), W4)
+    for run in range(4):
+        seq.run()
+        assert seq.status() == 0
+        assert (c4.cpu().numpy() == r4).all(), "run %d" % run
+        assert (((c1.cpu().numpy() << 8) >> 8) == r3).all()         # intermediate buffers hold tagged words
+        assert (((c2.cpu().numpy() << 8) >> 8) == r2).all()
+        tags = np.unique(c2.cpu().numpy().view(np.uint32) >> 24)
+        assert len(tags) == 1 and tags[0] != 0
+
+
+def test_tagged_exchange_is_validated():
+    W = sp.gen_ternary_iid(256, 256, 0.5, 0)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload()
+    x = dev(O.gen_x_i8(256, 1))
+    a = torch.zeros(256, dtype=torch.int32, device="cuda")
+    b = torch.zeros(256, dtype=torch.int32, device="cuda")
+    with pytest.raises(sp.SptmmError):          # a tagged reader must name its producer
+        sp.Sequence([{"w": w, "X": x, "C": a}, {"w": w, "X": a, "C": b, "x_kind": 2}])
+    with pytest.raises(sp.SptmmError):          # a counter-waiting reader of a tagged output
+        sp.Sequence([{"w": w, "X": x, "C": a}, {"w": w, "X": a, "C": b, "x_kind": 2, "dep": 0},
+                     {"w": w, "X": a, "C": b, "x_kind": 1, "dep": 0}])
+    with pytest.raises(sp.SptmmError):          # tagged and plain writers of one buffer
+        sp.Sequence([{"w": w, "X": x, "C": a}, {"w": w, "X": a, "C": b, "x_kind": 2, "dep": 0},
+                     {"w": w, "X": x, "C": a}])
+    with pytest.raises(sp.SptmmError):          # X outside the producer's output
+        sp.Sequence([{"w": w, "X": x, "C": a}, {"w": w, "X": b, "C": b, "x_kind": 2, "dep": 0}])
+
+
 def test_sequence_errors():
     W = sp.gen_ternary_iid(256, 64, 0.5, 0)
     w = sp.Weights(W, sp.FMT_U16_V256).upload()
