@@ -357,8 +357,16 @@ static int prefetch_depth(int mt, bool wide)
 }
 
 template <int DT>
-static int launch_dtype(const NativeParams &prm, int mt, int pd, dim3 grid, uint32_t threads, size_t smem, bool pdl, cudaStream_t st)
+static int launch_dtype(const NativeParams &prm, int mt, int pd, bool wide, dim3 grid, uint32_t threads, size_t smem, bool pdl, cudaStream_t st)
 {
+    if (wide)                         // one CTA per SM: no reason to cap registers at two CTAs' worth
+        switch (mt) {
+            case 1: return launch_one<DT, 1, 8, 1>(prm, grid, threads, smem, pdl, st);
+            case 2: return launch_one<DT, 2, 8, 1>(prm, grid, threads, smem, pdl, st);
+            case 4: return launch_one<DT, 4, 8, 1>(prm, grid, threads, smem, pdl, st);
+            case 8: return launch_one<DT, 8, 4, 1>(prm, grid, threads, smem, pdl, st);
+            case 16: return launch_one<DT, 16, 4, 1>(prm, grid, threads, smem, pdl, st);
+        }
     switch (mt) {
         case 1:
             if (pd == 16) return launch_one<DT, 1, 16, 1>(prm, grid, threads, smem, pdl, st);
@@ -392,7 +400,8 @@ int launch_native_u16(const GemvArgs &a)
     }
     // A small tile leaves room for several CTAs per SM, whose stream and gather phases then
     // overlap (also across neighbouring calls); a tile of tens of KB gets the SM to itself.
-    const bool wide = xs_bytes(w.K, mt * es) > 32 * 1024;
+    static const size_t wide_kb = [] { const char *e = getenv("SPTMM_WIDE_KB"); return e ? (size_t)atoi(e) : (size_t)32; }();
+    const bool wide = xs_bytes(w.K, mt * es) > wide_kb * 1024;
     const LaunchPlan &plan = wide ? w.plan_wide : w.plan;
     const uint32_t threads = plan.threads, nwarps = threads / 32;
     if (plan.grid > (uint32_t)kMaxGrid || nwarps > (uint32_t)kMaxWarps)
@@ -435,9 +444,9 @@ int launch_native_u16(const GemvArgs &a)
     const bool pdl = (a.flags & SPTMM_LAUNCH_PDL) != 0;
     cudaStream_t st = (cudaStream_t)a.stream;
     switch (a.dtype) {
-        case SPTMM_I8:  return launch_dtype<SPTMM_I8>(prm, mt, (int)pd, grid, threads, smem, pdl, st);
-        case SPTMM_F16: return launch_dtype<SPTMM_F16>(prm, mt, (int)pd, grid, threads, smem, pdl, st);
-        case SPTMM_F32: return launch_dtype<SPTMM_F32>(prm, mt, (int)pd, grid, threads, smem, pdl, st);
+        case SPTMM_I8:  return launch_dtype<SPTMM_I8>(prm, mt, (int)pd, wide, grid, threads, smem, pdl, st);
+        case SPTMM_F16: return launch_dtype<SPTMM_F16>(prm, mt, (int)pd, wide, grid, threads, smem, pdl, st);
+        case SPTMM_F32: return launch_dtype<SPTMM_F32>(prm, mt, (int)pd, wide, grid, threads, smem, pdl, st);
     }
     return fail(SPTMM_ERR_INVALID, "gemv: unknown dtype %u", a.dtype);
 }
