@@ -114,6 +114,21 @@ int sptmm_weights_free(sptmm_weights *w);
 int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M, void *C,
                uint32_t flags, uint32_t replica, void *stream);
 
+/* Split-K across the GPUs of one node: the matmul fused with the reduce-scatter of its partial
+ * sums.  No counterpart in the reference (single GPU).  Every rank holds the rows k0..k1 of W
+ * (encoded as a (k1-k0) x N matrix, native u16 format) and the matching slice of X, and calls this
+ * with the same C_peers: C_peers[r] is rank r's buffer of M x (N*(r+1)/n_peers - N*r/n_peers)
+ * int32 / float, row-major, holding columns N*r/n_peers .. of the result.  Instead of storing a
+ * column's partial sum the kernel ADDS it (red.global.add) to its owner's buffer, over NVLink for a
+ * peer: when all ranks' kernels are done, rank r's buffer holds its columns of X*W summed over the
+ * whole K.  The caller zeroes the buffers and separates zeroing, the calls and reading with a
+ * barrier on the stream (e.g. a collective).  int32 sums are exact; float sums depend on the
+ * order the additions arrive in (last-bit differences between runs).  Peer pointers only ever
+ * see plain reductions -- no multicast or bulk loads touch them. */
+int sptmm_gemv_reduce(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M,
+                      void *const *C_peers, uint32_t n_peers, uint32_t flags, uint32_t replica,
+                      void *stream);
+
 /* Same, but X and C are HOST buffers: copies X in, runs, copies C out, waits.  Uses pinned
  * staging owned by the handle (not re-entrant per handle). */
 int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,

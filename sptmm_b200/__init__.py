@@ -58,6 +58,7 @@ def _load() -> C.CDLL:
         "sptmm_weights_upload_replicas": (i32, [vp, u32]),
         "sptmm_weights_free": (i32, [vp]),
         "sptmm_gemv": (i32, [vp, vp, u32, u32, vp, u32, u32, vp]),
+        "sptmm_gemv_reduce": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, vp]),
         "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32, u32]),
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
@@ -88,7 +89,7 @@ def _load() -> C.CDLL:
 lib = _load()
 EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
-           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_host",
+           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
@@ -171,6 +172,12 @@ class Weights:
     def gemv(self, X, M: int, out, dtype: int = I8, flags: int = 0, replica: int = 0, stream: int = 0) -> None:
         """C = X*W on the device; X and out are device tensors (or addresses)."""
         check(lib.sptmm_gemv(self._h, _ptr(X), dtype, M, _ptr(out), flags, replica, stream))
+
+    def gemv_reduce(self, X, M: int, C_peers, dtype: int = I8, flags: int = 0, replica: int = 0, stream: int = 0) -> None:
+        """Split-K step: adds this rank's partial sums X*W into every column's owner buffer
+        (C_peers[r]: rank r's M x shard-width buffer, device tensors or addresses)."""
+        arr = (C.c_void_p * len(C_peers))(*[_ptr(c) for c in C_peers])
+        check(lib.sptmm_gemv_reduce(self._h, _ptr(X), dtype, M, arr, len(C_peers), flags, replica, stream))
 
     def gemv_host(self, X: np.ndarray, dtype: int = I8, flags: int = 0, replica: int = 0, out: Optional[np.ndarray] = None) -> np.ndarray:
         """Host-buffer call: copies X to the device, runs, copies C back."""

@@ -185,6 +185,29 @@ extern "C" int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype,
     return fail(SPTMM_ERR_UNSUPPORTED, "gemv: format %u", w->format);
 }
 
+extern "C" int sptmm_gemv_reduce(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M,
+                                 void *const *C_peers, uint32_t n_peers, uint32_t flags, uint32_t replica,
+                                 void *stream)
+{
+    if (!w || !X || !C_peers) return fail(SPTMM_ERR_INVALID, "gemv_reduce: null pointer");
+    if (n_peers == 0 || n_peers > 8) return fail(SPTMM_ERR_INVALID, "gemv_reduce: n_peers=%u (1..8 GPUs of one node)", n_peers);
+    for (uint32_t r = 0; r < n_peers; r++)
+        if (!C_peers[r]) return fail(SPTMM_ERR_INVALID, "gemv_reduce: no output buffer for rank %u", r);
+    if (M == 0 || dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv_reduce: bad M or dtype");
+    if (w->format != SPTMM_FMT_U16_V256) return fail(SPTMM_ERR_UNSUPPORTED, "gemv_reduce: weights must be in the native u16 format");
+    if (flags & SPTMM_C_COLMAJOR) return fail(SPTMM_ERR_UNSUPPORTED, "gemv_reduce: the per-rank outputs are row-major");
+    if (w->N < n_peers) return fail(SPTMM_ERR_INVALID, "gemv_reduce: N=%u columns for %u ranks", w->N, n_peers);
+    if (w->device < 0 || w->dev.empty()) return fail(SPTMM_ERR_STATE, "gemv_reduce: weights are not uploaded");
+    if (replica >= w->dev.size()) return fail(SPTMM_ERR_INVALID, "gemv_reduce: replica %u of %zu", replica, w->dev.size());
+    int dev = -1;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != w->device) return fail(SPTMM_ERR_STATE, "gemv_reduce: weights live on device %d, current device is %d", w->device, dev);
+    GemvArgs a{w, w->dev[replica].data(), X, C_peers[0], dtype, M, flags, stream};
+    a.C_peers = C_peers;
+    a.n_peers = n_peers;
+    return launch_native_u16(a);
+}
+
 extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
                                uint32_t flags, uint32_t replica)
 {

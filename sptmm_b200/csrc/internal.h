@@ -67,6 +67,8 @@ struct GemvArgs {
     const void *X; void *C;
     uint32_t dtype, M, flags;
     void *stream;
+    void *const *C_peers = nullptr;   // split-K: per-rank output buffers the partial sums are added to
+    uint32_t n_peers = 0;
 };
 
 int launch_native_u16(const GemvArgs &a);

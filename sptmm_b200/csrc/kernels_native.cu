@@ -45,6 +45,11 @@ struct NativeParams {
     uint32_t x_colmajor, c_colmajor;
     uint32_t uniform_nbl;        // blocks per list when every list has the same count, else 0
     uint32_t one;                // always 1: a multiplier the compiler cannot fold (LaneAcc::add)
+    // split-K over GPUs: n_peers > 0 makes the epilogue add each column's partial sum to the buffer
+    // of the rank that owns the column (columns col_bound[r] .. col_bound[r+1] belong to rank r)
+    uint32_t n_peers;
+    uint32_t col_bound[9];
+    void *Cp[8];
     uint32_t half_blocks;        // blocks per half of a warp's staging area
     uint32_t stage_blocks;       // blocks of staging area per warp (one or two halves)
     uint32_t stage_off;          // byte offset of the staging area in dynamic shared memory
@@ -305,6 +310,16 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
                 }
             }
         }
+        if (p.n_peers) {
+            // fused reduce-scatter: the sum goes to the column's owner (a plain reduction; over
+            // NVLink when the owner is a peer)
+            const uint32_t gcol = c0 + col;
+            uint32_t r = 0;
+            while (r + 1 < p.n_peers && gcol >= p.col_bound[r + 1]) r++;
+            const uint32_t width = p.col_bound[r + 1] - p.col_bound[r];
+            atomicAdd(reinterpret_cast<acc_t *>(p.Cp[r]) + (size_t)(m0 + m) * width + (gcol - p.col_bound[r]), v);
+            continue;
+        }
         const size_t o = p.c_colmajor ? (size_t)(c0 + col) * p.M + m0 + m : (size_t)(m0 + m) * p.N + c0 + col;
         C[o] = v;
     }
@@ -436,6 +451,13 @@ int launch_native_u16(const GemvArgs &a)
     prm.c_colmajor = (a.flags & SPTMM_C_COLMAJOR) ? 1 : 0;
     prm.uniform_nbl = w.uniform_nbl;
     prm.one = 1;
+    prm.n_peers = a.n_peers;
+    for (uint32_t r = 0; r < 8; r++) {
+        prm.Cp[r] = r < a.n_peers ? a.C_peers[r] : nullptr;
+        prm.col_bound[r] = a.n_peers ? (uint32_t)((uint64_t)w.N * std::min(r, a.n_peers) / a.n_peers) : 0;
+    }
+    prm.col_bound[8] = a.n_peers ? w.N : 0;
+    if (a.n_peers) prm.col_bound[a.n_peers] = w.N;
     prm.half_blocks = half;
     prm.stage_blocks = halves * half;
     prm.stage_off = (uint32_t)base_smem;

@@ -1,0 +1,109 @@
+"""Split-K over GPUs (sptmm_gemv_reduce): shard arithmetic on CPU (incl. a 2-rank gloo run), the
+fused add-to-owner epilogue on one GPU with emulated ranks, and the real multi-GPU path."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import sptmm_b200 as sp
+from sptmm_b200 import splitk as SK
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORKER = os.path.join(ROOT, "tests", "splitk_worker.py")
+
+
+def test_k_ranges_partition_the_rows_on_aligned_boundaries():
+    for K in (16, 400, 2560, 6912, 28672, 100):
+        for world in (1, 2, 3, 4, 8):
+            cuts = [SK.k_range(K, r, world) for r in range(world)]
+            assert cuts[0][0] == 0 and cuts[-1][1] == K
+            assert all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
+            assert all(a % 16 == 0 for a, _ in cuts)
+
+
+def test_col_ranges_follow_the_kernel_rule():
+    for N in (256, 2560, 28672, 17):
+        for world in (1, 2, 4, 8):
+            cuts = [SK.col_range(N, r, world) for r in range(world)]
+            assert cuts[0][0] == 0 and cuts[-1][1] == N and all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
+
+
+def test_split_k_partials_add_up_gloo():
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29541", WORKER, "cpu"],
+                       capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "split-k shards ok" in r.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,dtype,ranks", [(1, sp.I8, 2), (5, sp.I8, 3), (16, sp.I8, 2), (4, sp.F16, 2), (2, sp.F32, 4)])
+def test_fused_reduce_scatter_with_emulated_ranks(M, dtype, ranks):
+    """One GPU plays every rank in turn: each has its K range of W and adds its partial sums into
+    per-rank output buffers; afterwards buffer r holds rank r's columns of the full product."""
+    import torch
+    torch.cuda.set_device(0)
+    K, N = 1040, 200                                         # N not divisible by 3: ragged column ranges
+    W = sp.gen_ternary_iid(K, N, 0.5, 41)
+    rng = np.random.default_rng(42)
+    if dtype == sp.I8:
+        X = O.gen_x_i8(M * K, 43).reshape(M, K)
+        want = O.gemv_i8_dense(X.reshape(-1), W).reshape(M, N)
+        out_t = torch.int32
+    else:
+        X = rng.standard_normal((M, K)).astype(np.float16 if dtype == sp.F16 else np.float32)
+        want = X.astype(np.float64) @ W.T.astype(np.float64)
+        out_t = torch.float32
+    cols = [SK.col_range(N, r, ranks) for r in range(ranks)]
+    bufs = [torch.zeros(M, c1 - c0, dtype=out_t, device="cuda") for c0, c1 in cols]
+    for r in range(ranks):
+        k0, k1 = SK.k_range(K, r, ranks)
+        w = sp.Weights(np.ascontiguousarray(W[:, k0:k1]), sp.FMT_U16_V256).upload()
+        xs = torch.from_numpy(np.ascontiguousarray(X[:, k0:k1])).cuda()
+        w.gemv_reduce(xs, M, bufs, dtype)
+        torch.cuda.synchronize()
+    got = np.concatenate([b.cpu().numpy() for b in bufs], axis=1)
+    if dtype == sp.I8:
+        assert (got == want).all()
+    else:
+        scale = np.abs(X.astype(np.float64)) @ np.abs(W.T.astype(np.float64))
+        tol = 1e-3 if dtype == sp.F16 else 1e-5
+        assert (np.abs(got - want) / scale).max() <= tol
+
+
+@pytest.mark.gpu
+def test_gemv_reduce_is_validated():
+    import torch
+    torch.cuda.set_device(0)
+    W = sp.gen_ternary_iid(256, 64, 0.5, 0)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload()
+    wd = sp.Weights(sp.gen_ternary_fixed(256, 64, 128), sp.FMT_U16_DIV, split=32).upload()
+    x = torch.from_numpy(O.gen_x_i8(256, 1)).cuda()
+    c = torch.zeros(64, dtype=torch.int32, device="cuda")
+    with pytest.raises(sp.SptmmError):
+        wd.gemv_reduce(x, 1, [c])                              # native format only
+    with pytest.raises(sp.SptmmError):
+        w.gemv_reduce(x, 1, [c] * 9)                           # at most 8 ranks
+    with pytest.raises(sp.SptmmError):
+        w.gemv_reduce(x, 1, [c], flags=sp.C_COLMAJOR)
+    w.gemv_reduce(x, 1, [c])                                   # one rank: plain accumulate
+    torch.cuda.synchronize()
+    assert (c.cpu().numpy() == O.gemv_i8_dense(O.gen_x_i8(256, 1), W).reshape(-1)).all()
+
+
+@pytest.mark.gpu
+def test_split_k_multi_gpu():
+    import torch
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    world = 2 if n < 4 else 4
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % world,
+                        "--master-addr", "127.0.0.1", "--master-port", "29542", WORKER, "gpu"],
+                       capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "split-k multi-gpu parity ok" in r.stdout
