@@ -374,6 +374,8 @@ def run_ours(args):
             del stk
             torch.cuda.empty_cache()
 
+    large_info = large_sweep(args, sp, O, torch, dist, rank, world) if args.large else None
+
     line = None
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -403,6 +405,8 @@ def run_ours(args):
             line["cpu_baseline"], _ = cpu_baseline()
         if args.extra:
             line["extra"] = extra_workloads(sp, O, torch, st)
+        if large_info is not None:
+            line["large"] = large_info
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -482,6 +486,69 @@ def extra_workloads(sp, O, torch, st, nstreams=4):
     return res
 
 
+def large_sweep(args, sp, O, torch, dist, rank, world):
+    """Large ternary matrices (P(0)=0.5, fp16 activations, fp32 sums) at M = 1, 8, 64, over all
+    ranks two ways: columns sharded (each rank its N/world columns, X replicated, no exchange) and
+    K split (each rank its K/world rows; partial sums reduce-scattered -- fused into the kernel's
+    epilogue, and through NCCL for comparison).  Times are per matmul, max over ranks; on one
+    rank the 2-bit i2s comparator (int8 activations) runs on the same matrix."""
+    from sptmm_b200 import splitk as SK
+    shapes = [(8192, 28672), (28672, 8192), (16384, 53248)] if args.large == "all" else [(8192, 28672)]
+    res = {}
+    st = torch.cuda.current_stream()
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(n):
+            fn()
+        e1.record(st)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / n
+        if world > 1:
+            t = torch.tensor([us], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+        return us
+
+    for Kl, Nl in shapes:
+        W = sp.gen_ternary_iid(Kl, Nl, 0.5, 7)
+        rng = np.random.default_rng(8)
+        key = "%dx%d" % (Kl, Nl)
+        res[key] = {}
+        c0, c1 = SK.col_range(Nl, rank, world)
+        wn = sp.Weights(np.ascontiguousarray(W[c0:c1]), sp.FMT_U16_V256).upload()
+        for m in (1, 8, 64):
+            X = rng.standard_normal((m, Kl)).astype(np.float16)
+            xd = torch.from_numpy(X).cuda()
+            out = torch.zeros(m, c1 - c0, dtype=torch.float32, device="cuda")
+            entry = {"n_sharded_us": timed(lambda: wn.gemv(xd, m, out, sp.F16, sp.LAUNCH_PDL, stream=st.cuda_stream)),
+                     "encoded_MB_per_rank": wn.stream_bytes / 1e6}
+            mm = SK.SplitKMatmul(W, m, sp.F16, rank, world)
+            xs = torch.from_numpy(np.ascontiguousarray(X[:, mm.k0:mm.k1])).cuda()
+            entry["split_k_fused_us"] = timed(lambda: mm.forward(xs))
+            if world > 1 and Nl % world == 0:
+                entry["split_k_nccl_us"] = timed(lambda: mm.forward_nccl(xs))
+            del mm
+            res[key]["M%d" % m] = entry
+        wn.close()
+        if world == 1:
+            wi = sp.Weights(W, sp.FMT_I2S).upload()
+            for m in (1, 8):
+                xi = torch.from_numpy(O.gen_x_i8(m * Kl, 9)).cuda()
+                oi = torch.zeros(m * Nl, dtype=torch.int32, device="cuda")
+                res[key]["M%d" % m]["i2s_int8_us"] = timed(lambda: wi.gemv(xi, m, oi, sp.I8, stream=st.cuda_stream))
+            wi.close()
+        del W
+    res["note"] = "the dense fp16 cuBLAS comparator of this sweep is not built (the library's dense comparator is int8)"
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -497,6 +564,8 @@ def main():
     ap.add_argument("--stack-layers", type=int, default=30)
     ap.add_argument("--stack-tagged", action="store_true", help="layer stack hands activations on as tagged words (x_kind 2)")
     ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
+    ap.add_argument("--large", nargs="?", const="one", default=None, choices=["one", "all"],
+                    help="also run the large-matrix sweep (column-sharded and split-K over all ranks); 'all' = three shapes")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
