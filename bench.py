@@ -483,6 +483,25 @@ def extra_workloads(sp, O, torch, st, nstreams=4):
             res["%s_M%d_%s" % (name, m, "i8" if dt == sp.I8 else "f16")] = {
                 "us_per_call": us, "GBps": nb / us / 1e3, "us_single_stream": us1, "bytes": nb, "copies": reps}
         w.close()
+
+    # the delta layout's sparsity sweep: P(0) = 0.33 / 0.5 / 0.75 as fixed counts S = 4608 / 3456 / 1728
+    # per column (the reference generator), M=1 int8, beside the native u16 format on the same matrix
+    x = torch.from_numpy(O.gen_x_i8(K, 1)).cuda()
+    o = torch.zeros(nstreams, N, dtype=torch.int32, device="cuda")
+    for s_sweep in (4608, 3456, 1728):
+        Ws = sp.gen_ternary_fixed(K, N, s_sweep)
+        for name, fmt, s_arg in (("delta_div256", sp.FMT_DELTA_DIV256, s_sweep), ("u16_v256", sp.FMT_U16_V256, 0)):
+            w = sp.Weights(Ws, fmt, split=32, S=s_arg)
+            reps = cold_replicas(w)
+            w.upload(reps)
+            def call(i, stream):
+                w.gemv(x, 1, o[i % nstreams], sp.I8, sp.LAUNCH_PDL, replica=i % reps, stream=stream.cuda_stream)
+            us = timeit(call, side)
+            us1 = timeit(call, [st])
+            nb = algorithmic_bytes(w.stream_bytes, 1, 1)
+            res["%s_S%d_M1_i8" % (name, s_sweep)] = {
+                "us_per_call": us, "GBps": nb / us / 1e3, "us_single_stream": us1, "bytes": nb, "copies": reps}
+            w.close()
     return res
 
 

@@ -98,11 +98,11 @@ static void make_plan(sptmm_weights *w)
 {
     LaunchPlan &pl = w->plan;
     const Tune &t = tune();
-    pl.grid = std::min<uint32_t>(w->sm_count * t.ctas_per_sm, 1024);
+    pl.grid = std::min<uint32_t>(w->sm_count * t.ctas_per_sm, kMaxPlanCtas);
     pl.threads = t.threads;
     plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, pl.grid, pl.cta_blk, pl.cta_col, pl.max_cols, pl.max_cta_blocks);
     LaunchPlan &pw = w->plan_wide;
-    pw.grid = std::min<uint32_t>(w->sm_count, 1024);
+    pw.grid = std::min<uint32_t>(w->sm_count, kMaxPlanCtas);
     pw.threads = 512;
     plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, pw.grid, pw.cta_blk, pw.cta_col, pw.max_cols, pw.max_cta_blocks);
 }

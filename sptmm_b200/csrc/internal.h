@@ -18,6 +18,10 @@ struct HostArray {
     bool streamed;      // read once per matmul (counts toward stream_bytes)
 };
 
+// Most CTAs a launch plan may have.  The plan travels in the kernel parameters, and a launch
+// copies all of them: 384 entries (two arrays, 3 KB) cover two CTAs per SM on 192 SMs.
+constexpr uint32_t kMaxPlanCtas = 384;
+
 // One CTA's share of a native-format matrix: columns [c0,c1) and their blocks [b0,b1).
 struct CtaPlan { uint32_t c0, c1, b0, b1; };
 

@@ -30,7 +30,7 @@
 
 namespace sptmm {
 
-constexpr int kMaxGrid = 1024;
+constexpr int kMaxGrid = (int)kMaxPlanCtas;
 constexpr int kMaxWarps = 16;
 
 struct NativeParams {
