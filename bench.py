@@ -460,7 +460,7 @@ def extra_workloads(sp, O, torch, st, nstreams=4):
         r = max(2, -(-int(2.5 * L2_BYTES) // max(1, w.stream_bytes)))
         return min(r, 160)
 
-    cases = [("u16_v256", sp.FMT_U16_V256, 32, 0), ("u16_div32", sp.FMT_U16_DIV, 32, S),
+    cases = [("u16_v256", sp.FMT_U16_V256, 32, 0), ("delta_lane", sp.FMT_DELTA_LANE, 32, 0), ("u16_div32", sp.FMT_U16_DIV, 32, S),
              ("delta_div256", sp.FMT_DELTA_DIV256, 32, S), ("i2s", sp.FMT_I2S, 0, 0)]
     for name, fmt, split, s_arg in cases:
         w = sp.Weights(W, fmt, split=split, S=s_arg)
@@ -490,7 +490,8 @@ def extra_workloads(sp, O, torch, st, nstreams=4):
     o = torch.zeros(nstreams, N, dtype=torch.int32, device="cuda")
     for s_sweep in (4608, 3456, 1728):
         Ws = sp.gen_ternary_fixed(K, N, s_sweep)
-        for name, fmt, s_arg in (("delta_div256", sp.FMT_DELTA_DIV256, s_sweep), ("u16_v256", sp.FMT_U16_V256, 0)):
+        for name, fmt, s_arg in (("delta_lane", sp.FMT_DELTA_LANE, 0), ("delta_div256", sp.FMT_DELTA_DIV256, s_sweep),
+                                 ("u16_v256", sp.FMT_U16_V256, 0)):
             w = sp.Weights(Ws, fmt, split=32, S=s_arg)
             reps = cold_replicas(w)
             w.upload(reps)

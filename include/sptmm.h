@@ -42,7 +42,9 @@ typedef enum sptmm_format {
     SPTMM_FMT_DELTA_DIV256 = 2,
     /* native: u16, 256-entry blocks pre-interleaved for 16-byte-per-lane loads              */
     SPTMM_FMT_U16_V256 = 3,
-    /* native: per-lane u16 base + 14 u8 lane-strided gaps per 16 bytes (480 entries/512 B)  */
+    /* native narrow-integer variant: 304-byte blocks of eight 32-lane gather steps; a step is
+     * a 32-bit base row, a count and one 8-bit offset per lane (1.19 bytes per entry, exact:
+     * a step that would span more than 255 rows is cut short instead)                        */
     SPTMM_FMT_DELTA_LANE = 4,
     /* comparator: 2-bit codes, 16 rows per 32-bit word (bitnet_kernels.cuh:52-72)           */
     SPTMM_FMT_I2S = 5
@@ -64,7 +66,7 @@ typedef struct sptmm_weights sptmm_weights;   /* opaque, host-owned encoded matr
 typedef struct sptmm_weights_info {
     uint32_t K, N;
     uint32_t format;        /* sptmm_format                                                  */
-    uint32_t split;         /* U16_DIV: 8/16/32; DELTA_LANE: lane stride; else 0             */
+    uint32_t split;         /* U16_DIV: 8/16/32; native formats: 32 (lanes per gather step)  */
     uint32_t S;             /* 2 x padded per-sign list capacity (reference -S) where uniform */
     uint32_t max_count;     /* longest single-sign list                                      */
     uint64_t nnz;           /* non-zeros of W                                                */
@@ -91,7 +93,7 @@ int sptmm_gen_ternary_iid(uint32_t K, uint32_t N, double p_zero, uint64_t seed, 
 /* S = 0 derives the per-sign capacity from the longest list (rounded up as the format needs);
  * S > 0 fixes it at S/2 as the reference's -S flag does and fails if a column has more.
  * `split`: U16_DIV 8|16|32 (reference -row_split3_small values, main.cu:998-1059);
- *          DELTA_LANE 0 = choose the widest lane stride whose gaps fit 8 bits; others ignore it. */
+ *          the other formats ignore it. */
 int sptmm_encode(const int8_t *W, uint32_t K, uint32_t N, uint32_t format, uint32_t split,
                  uint32_t S, sptmm_weights **out);
 int sptmm_weights_info_get(const sptmm_weights *w, sptmm_weights_info *info);

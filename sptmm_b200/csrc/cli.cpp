@@ -239,7 +239,7 @@ int main(int argc, char **argv)
     }
     if (f.row_split_delta2 > 0) {
         if (f.row_split_delta2 != 32) die("Wrong split size");            // main.cu:1837-1839
-        run_sptmm("row_split_delta2", SPTMM_FMT_DELTA_DIV256, 32);
+        run_sptmm("row_split_delta2", f.native ? SPTMM_FMT_DELTA_LANE : SPTMM_FMT_DELTA_DIV256, 32);
     }
     if (f.i2s) {
         if (kXCol) die("X must be row-major!\n");                         // main.cu:1852-1854

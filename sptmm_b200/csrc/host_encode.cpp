@@ -252,6 +252,73 @@ static void encode_u16_v256(const Lists &L, sptmm_weights &w)
     w.stream_bytes = (uint64_t)w.total_blocks * 512 + off.size() * 4;
 }
 
+// Native narrow-integer layout (SPTMM_FMT_DELTA_LANE).  A list's sorted rows are cut into gather
+// STEPS of up to 32 entries: a step takes the next entries while they lie within 255 rows of its
+// first one (its base), so every entry is base + an 8-bit offset, exactly; in lists denser than
+// one entry per eight rows nearly every step is full.  Eight steps make a 304-byte block:
+//   [0,256)    offsets: byte 8*lane + t is lane's offset in step t (one 8-byte load per lane)
+//   [256,288)  eight 32-bit bases
+//   [288,296)  eight counts (entries of the step; lanes at or beyond it gather nothing)
+//   [296,304)  zero
+// Blocks are stored list after list like the u16 format's, with the same blk_off array.  Unlike
+// the reference's gap lists (main.cu:376-394) nothing is truncated and no scan across lanes is
+// needed to decode: a lane adds its offset to the step's base.
+static void encode_delta_lane(const Lists &L, sptmm_weights &w)
+{
+    constexpr size_t BB = 304;
+    const uint32_t N = w.N;
+    auto steps_of = [](const std::vector<uint16_t> &l) {
+        uint32_t steps = 0;
+        for (size_t i = 0; i < l.size();) {
+            size_t j = i;
+            while (j < l.size() && j - i < 32 && (uint32_t)(l[j] - l[i]) <= 255u) j++;
+            steps++;
+            i = j;
+        }
+        return steps;
+    };
+    std::vector<uint32_t> off(2 * (size_t)N + 1, 0);
+    uint32_t maxblk = 0;
+    for (uint32_t c = 0; c < N; c++) {
+        const uint32_t bp = (steps_of(L.pos[c]) + 7) / 8, bn = (steps_of(L.neg[c]) + 7) / 8;
+        off[2 * c + 1] = off[2 * c] + bp;
+        off[2 * c + 2] = off[2 * c + 1] + bn;
+        maxblk = std::max(maxblk, std::max(bp, bn));
+    }
+    w.total_blocks = off[2 * (size_t)N];
+    w.entries_per_block = 256;
+    w.uniform_nbl = off[1] - off[0];
+    for (size_t l = 0; l < 2 * (size_t)N; l++)
+        if (off[l + 1] - off[l] != w.uniform_nbl) { w.uniform_nbl = 0; break; }
+    w.arrays.push_back(make_array("idx_delta_lane", (size_t)w.total_blocks * BB, true));     // zero-filled
+    uint8_t *out = w.arrays.back().data.data();
+    parallel_columns(N, [&](uint32_t c0, uint32_t c1) {
+        for (uint32_t c = c0; c < c1; c++)
+            for (int sign = 0; sign < 2; sign++) {
+                const auto &l = sign ? L.neg[c] : L.pos[c];
+                uint8_t *dst = out + (size_t)off[2 * c + sign] * BB;
+                uint32_t step = 0;
+                for (size_t i = 0; i < l.size(); step++) {
+                    uint8_t *blk = dst + (size_t)(step / 8) * BB;
+                    const uint32_t t = step % 8;
+                    size_t j = i;
+                    while (j < l.size() && j - i < 32 && (uint32_t)(l[j] - l[i]) <= 255u) {
+                        blk[8 * (j - i) + t] = (uint8_t)(l[j] - l[i]);
+                        j++;
+                    }
+                    const uint32_t base = l[i];
+                    memcpy(blk + 256 + 4 * t, &base, 4);
+                    blk[288 + t] = (uint8_t)(j - i);
+                    i = j;
+                }
+            }
+    });
+    w.arrays.push_back(make_array("blk_off", off.size() * 4, true));
+    memcpy(w.arrays.back().data.data(), off.data(), off.size() * 4);
+    w.S = 2 * 256 * maxblk;
+    w.stream_bytes = (uint64_t)w.total_blocks * BB + off.size() * 4;
+}
+
 // Comparator packing: word j of column c carries rows 16j..16j+15 as 2-bit codes w+2; row
 // 16j+e sits at bit 8*(e%4) + 2*(e/4)  (the decode order of bitnet_kernels.cuh:57-71).
 static void encode_i2s(const int8_t *W, sptmm_weights &w)
@@ -374,6 +441,10 @@ extern "C" int sptmm_encode(const int8_t *W, uint32_t K, uint32_t N, uint32_t fo
             case SPTMM_FMT_U16_V256:
                 w->split = 32;
                 encode_u16_v256(L, *w);
+                break;
+            case SPTMM_FMT_DELTA_LANE:
+                w->split = 32;
+                encode_delta_lane(L, *w);
                 break;
             default:
                 rc = fail(SPTMM_ERR_UNSUPPORTED, "encode: unknown format %u", format);

@@ -32,6 +32,7 @@ namespace sptmm {
 
 constexpr int kMaxGrid = (int)kMaxPlanCtas;
 constexpr int kMaxWarps = 16;
+constexpr uint32_t kDeltaBlockBytes = 304;     // 256 offsets, 8 bases, 8 counts, padding (SPTMM_FMT_DELTA_LANE)
 
 struct NativeParams {
     const uint4 *idx;            // total_blocks * 32 vectors
@@ -96,6 +97,8 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     using acc_t = typename ActTraits<DT>::acc;
     constexpr int RB = MT * ActTraits<DT>::size;
     constexpr bool kInt = DT == SPTMM_I8;
+    constexpr bool kDelta = P == 0;              // SPTMM_FMT_DELTA_LANE: 304-byte blocks, all through shared memory
+    constexpr uint32_t BB = kDelta ? kDeltaBlockBytes : 512u;
     extern __shared__ __align__(16) unsigned char dyn_smem[];
 
     pdl_launch_dependents();     // the next kernel may start its own weight requests right away
@@ -127,12 +130,13 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     const uint32_t nrounds = H ? (nstaged + H - 1) / H : 0;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + p.stage_off) + 2 * warp;
     const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(bars);
-    const uint4 *wstage = reinterpret_cast<const uint4 *>(smem + p.stage_off + 256 + (size_t)warp * p.stage_blocks * 512);
+    const uint4 *wstage = reinterpret_cast<const uint4 *>(smem + p.stage_off + 256 + (size_t)warp * p.stage_blocks * BB);
     const uint32_t wstage_a = (uint32_t)__cvta_generic_to_shared(wstage);
-    const uint4 *slice = p.idx + (size_t)wb0 * 32;
+    const unsigned char *slice_b = reinterpret_cast<const unsigned char *>(p.idx) + (size_t)wb0 * BB;
+    const uint4 *slice = reinterpret_cast<const uint4 *>(slice_b);
     auto issue_round = [&](uint32_t r) {          // lane 0 only
         const uint32_t cnt = min(H, nstaged - r * H);
-        bulk_fetch(wstage_a + (r & 1) * H * 512, slice + (size_t)(nreg + r * H) * 32, cnt * 512u, bar_a + 8 * (r & 1));
+        bulk_fetch(wstage_a + (r & 1) * H * BB, slice_b + (size_t)(nreg + r * H) * BB, cnt * BB, bar_a + 8 * (r & 1));
     };
     if (lane == 0 && nrounds) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
@@ -142,7 +146,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
         issue_round(0);
         if (nrounds > 1) issue_round(1);
     }
-    uint4 buf[P];
+    uint4 buf[P ? P : 1];
 #pragma unroll
     for (int i = 0; i < P; i++)
         if ((uint32_t)i < nreg) buf[i] = ld_weights16(slice + (size_t)i * 32 + lane);
@@ -261,11 +265,50 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             }
         };
 
-        // the blocks that came straight into registers
+        // A lane-delta block (SPTMM_FMT_DELTA_LANE, see host_encode.cpp): eight gather steps; step
+        // t gathers rows base[t] + off[lane][t] for the first cnt[t] lanes.  Blocks whose steps
+        // are all full (every block but a list's last, and steps cut short by a gap of more than
+        // 255 rows) take the branch without per-lane tests; idle lanes read the zero row.
+        auto consume_delta = [&](const unsigned char *blk, const uint32_t b) {
+            if (b >= bound) {
+                do {
+                    if (dirty) { flush(); dirty = false; }
+                    li++;
+                    bound = nbl ? bound + nbl : off_s[li + 1];
+                } while (b >= bound);
+            }
+            dirty = true;
+            acc.reserve(8);
+            const uint2 off = *reinterpret_cast<const uint2 *>(blk + 8 * lane);
+            const uint4 ba = *reinterpret_cast<const uint4 *>(blk + 256), bb = *reinterpret_cast<const uint4 *>(blk + 272);
+            const uint2 cn = *reinterpret_cast<const uint2 *>(blk + 288);
+            if (cn.x == 0x20202020u && cn.y == 0x20202020u) {
+                acc.add(ba.x + __byte_perm(off.x, 0u, 0x4440));
+                acc.add(ba.y + __byte_perm(off.x, 0u, 0x4441));
+                acc.add(ba.z + __byte_perm(off.x, 0u, 0x4442));
+                acc.add(ba.w + __byte_perm(off.x, 0u, 0x4443));
+                acc.add(bb.x + __byte_perm(off.y, 0u, 0x4440));
+                acc.add(bb.y + __byte_perm(off.y, 0u, 0x4441));
+                acc.add(bb.z + __byte_perm(off.y, 0u, 0x4442));
+                acc.add(bb.w + __byte_perm(off.y, 0u, 0x4443));
+            } else {
+                const uint32_t base[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
-        for (int i = 0; i + 1 < P; i += 2) {
-            if ((uint32_t)i + 1 < nreg) consume2(buf[i], buf[i + 1], wb0 + i);
-            else if ((uint32_t)i < nreg) consume(buf[i], wb0 + i);
+                for (int t = 0; t < 8; t++) {
+                    const uint32_t o = ((t < 4 ? off.x : off.y) >> (8 * (t & 3))) & 0xffu;
+                    const uint32_t c = ((t < 4 ? cn.x : cn.y) >> (8 * (t & 3))) & 0xffu;
+                    acc.add(lane < c ? base[t] + o : p.K);
+                }
+            }
+        };
+
+        // the blocks that came straight into registers
+        if constexpr (!kDelta) {
+#pragma unroll
+            for (int i = 0; i + 1 < P; i += 2) {
+                if ((uint32_t)i + 1 < nreg) consume2(buf[i], buf[i + 1], wb0 + i);
+                else if ((uint32_t)i < nreg) consume(buf[i], wb0 + i);
+            }
         }
 
         // the staged blocks, round by round; a finished half is refilled two rounds ahead
@@ -274,11 +317,16 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             ok = bounded_wait(bar_a + 8 * (r & 1), (r >> 1) & 1);
             if (!ok) break;
             const uint32_t cnt = min(H, nstaged - r * H);
-            const uint4 *half = wstage + (size_t)(r & 1) * H * 32 + lane;
             const uint32_t bfirst = wb0 + nreg + r * H;
-            uint32_t j = 0;
-            for (; j + 1 < cnt; j += 2) consume2(half[(size_t)j * 32], half[(size_t)(j + 1) * 32], bfirst + j);
-            if (j < cnt) consume(half[(size_t)j * 32], bfirst + j);
+            if constexpr (kDelta) {
+                const unsigned char *half_b = reinterpret_cast<const unsigned char *>(wstage) + (size_t)(r & 1) * H * BB;
+                for (uint32_t j = 0; j < cnt; j++) consume_delta(half_b + (size_t)j * BB, bfirst + j);
+            } else {
+                const uint4 *half = wstage + (size_t)(r & 1) * H * 32 + lane;
+                uint32_t j = 0;
+                for (; j + 1 < cnt; j += 2) consume2(half[(size_t)j * 32], half[(size_t)(j + 1) * 32], bfirst + j);
+                if (j < cnt) consume(half[(size_t)j * 32], bfirst + j);
+            }
             if (r + 2 < nrounds) {
                 __syncwarp();
                 if (lane == 0) {
@@ -374,6 +422,14 @@ static int prefetch_depth(int mt, bool wide)
 template <int DT>
 static int launch_dtype(const NativeParams &prm, int mt, int pd, bool wide, dim3 grid, uint32_t threads, size_t smem, bool pdl, cudaStream_t st)
 {
+    if (pd == 0)                      // lane-delta blocks: everything goes through shared memory
+        switch (mt) {
+            case 1: return wide ? launch_one<DT, 1, 0, 1>(prm, grid, threads, smem, pdl, st) : launch_one<DT, 1, 0, 2>(prm, grid, threads, smem, pdl, st);
+            case 2: return wide ? launch_one<DT, 2, 0, 1>(prm, grid, threads, smem, pdl, st) : launch_one<DT, 2, 0, 2>(prm, grid, threads, smem, pdl, st);
+            case 4: return wide ? launch_one<DT, 4, 0, 1>(prm, grid, threads, smem, pdl, st) : launch_one<DT, 4, 0, 2>(prm, grid, threads, smem, pdl, st);
+            case 8: return launch_one<DT, 8, 0, 1>(prm, grid, threads, smem, pdl, st);
+            case 16: return launch_one<DT, 16, 0, 1>(prm, grid, threads, smem, pdl, st);
+        }
     if (wide)                         // one CTA per SM: no reason to cap registers at two CTAs' worth
         switch (mt) {
             case 1: return launch_one<DT, 1, 8, 1>(prm, grid, threads, smem, pdl, st);
@@ -400,9 +456,10 @@ static int launch_dtype(const NativeParams &prm, int mt, int pd, bool wide, dim3
 static unsigned long long *g_trace = nullptr;
 void set_trace_buffer(unsigned long long *dev_ptr) { g_trace = dev_ptr; }
 
-int launch_native_u16(const GemvArgs &a)
+static int launch_native(const GemvArgs &a, const bool delta)
 {
     const sptmm_weights &w = *a.w;
+    const size_t bb = delta ? kDeltaBlockBytes : 512;
     const int es = (int)dtype_size(a.dtype);
     // widest row tile (<= 16 rows, power of two) whose transposed copy of X fits shared memory
     // beside a minimal staging area (two blocks per warp)
@@ -410,7 +467,7 @@ int launch_native_u16(const GemvArgs &a)
     while (mt < 16 && (uint32_t)mt < a.M) mt *= 2;
     {
         const LaunchPlan &pw = w.plan_wide;
-        const size_t min_stage_w = 256 + (size_t)(pw.threads / 32) * 2 * 512;
+        const size_t min_stage_w = 256 + (size_t)(pw.threads / 32) * 2 * bb;
         while (mt > 1 && native_smem(w.K, mt * es, mt, pw.max_cols, pw.threads / 32) + min_stage_w > 200 * 1024) mt /= 2;
     }
     // A small tile leaves room for several CTAs per SM, whose stream and gather phases then
@@ -421,7 +478,7 @@ int launch_native_u16(const GemvArgs &a)
     const uint32_t threads = plan.threads, nwarps = threads / 32;
     if (plan.grid > (uint32_t)kMaxGrid || nwarps > (uint32_t)kMaxWarps)
         return fail(SPTMM_ERR_INVALID, "internal: launch plan %u x %u out of range", plan.grid, threads);
-    const size_t min_stage = 256 + (size_t)nwarps * 2 * 512;
+    const size_t min_stage = 256 + (size_t)nwarps * 2 * bb;
     const size_t base_smem = native_smem(w.K, mt * es, mt, plan.max_cols, nwarps);
     const size_t gap = 1024;                  // dynamic shared memory before the tile's fixed address
     if (gap + base_smem + min_stage > 227 * 1024)
@@ -429,15 +486,15 @@ int launch_native_u16(const GemvArgs &a)
 
     // staging area: what a warp's slice holds beyond the registers, in one round if the budget
     // allows, else in double-buffered rounds of half the room each
-    const uint32_t pd = (uint32_t)prefetch_depth(mt, wide);
+    const uint32_t pd = delta ? 0u : (uint32_t)prefetch_depth(mt, wide);
     const uint32_t per_warp = (plan.max_cta_blocks + nwarps - 1) / nwarps + 1;
     const uint32_t need = per_warp > pd ? per_warp - pd : 0;
     const size_t budget = wide ? (size_t)225 * 1024
                                : std::min(base_smem + std::max((size_t)tune().smem_kb * 1024, min_stage), (size_t)225 * 1024);
-    const uint32_t room = (uint32_t)((budget - base_smem - 256) / ((size_t)nwarps * 512));   // blocks per warp
+    const uint32_t room = (uint32_t)((budget - base_smem - 256) / ((size_t)nwarps * bb));   // blocks per warp
     const uint32_t half = need == 0 ? 0 : (need <= room ? need : std::max(1u, room / 2));
     const uint32_t halves = need <= room ? 1 : 2;
-    const size_t smem = gap + base_smem + 256 + (size_t)nwarps * halves * half * 512;
+    const size_t smem = gap + base_smem + 256 + (size_t)nwarps * halves * half * bb;
 
     NativeParams prm;
     prm.idx = (const uint4 *)a.arrays[0];
@@ -473,9 +530,7 @@ int launch_native_u16(const GemvArgs &a)
     return fail(SPTMM_ERR_INVALID, "gemv: unknown dtype %u", a.dtype);
 }
 
-int launch_native_delta(const GemvArgs &)
-{
-    return fail(SPTMM_ERR_UNSUPPORTED, "gemv: lane-delta format is not built yet");
-}
+int launch_native_u16(const GemvArgs &a) { return launch_native(a, false); }
+int launch_native_delta(const GemvArgs &a) { return launch_native(a, true); }
 
 }  // namespace sptmm

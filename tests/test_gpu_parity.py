@@ -137,6 +137,49 @@ def test_native_u16_float(dtype, rtol, K, N, M):
     assert torch.equal(out, out2)
 
 
+# ---------------------------------------------------------------- native lane-delta format
+
+@pytest.mark.parametrize("p0", [1 / 3, 0.5, 0.75, 0.97, 1.0])
+@pytest.mark.parametrize("K,N", [(700, 40), (6912, 97), (64, 1)])
+def test_delta_lane_ragged_iid(p0, K, N):
+    """Dense lists (all steps full), sparse ones (steps cut short by gaps of more than 255 rows),
+    empty ones; bit-exact against the oracle and the u16 path."""
+    W = sp.gen_ternary_iid(K, N, p0, 6)
+    w = sp.Weights(W, sp.FMT_DELTA_LANE).upload()
+    wu = sp.Weights(W, sp.FMT_U16_V256).upload()
+    for M in (1, 3, 4, 16, 17):
+        X = O.gen_x_i8(M * K, 18)
+        want = O.gemv_i8_dense(X, W)
+        assert (run_i8(w, X, M).reshape(M, N) == want).all()
+        assert (run_i8(wu, X, M).reshape(M, N) == want).all()
+
+
+@pytest.mark.parametrize("S", [4608, 4096, 3456, 1728])
+def test_delta_lane_sparsity_sweep_full_size(S):
+    # BASELINE config 2 on the native narrow-integer format: bit-exact vs the undecoded u16 path
+    K, N = 6912, 2560
+    W = sp.gen_ternary_fixed(K, N, S)
+    X = O.gen_x_i8(K, 1)
+    wd = sp.Weights(W, sp.FMT_DELTA_LANE).upload()
+    wu = sp.Weights(W, sp.FMT_U16_V256).upload()
+    assert wd.info.stream_bytes < 0.75 * wu.info.stream_bytes
+    got = run_i8(wd, X, 1)
+    assert (got == run_i8(wu, X, 1)).all()
+    assert (got.reshape(1, N) == O.gemv_i8_dense(X, W)).all()
+
+
+@pytest.mark.parametrize("dtype,rtol", [(sp.F16, FP16_RTOL), (sp.F32, FP32_RTOL)])
+def test_delta_lane_float(dtype, rtol):
+    K, N, M = 2560, 640, 4
+    W, Xh, ref, dbl, ab = _float_case(K, N, M, 1 / 3, dtype)
+    w = sp.Weights(W, sp.FMT_DELTA_LANE).upload()
+    out = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    w.gemv(dev(Xh), M, out, dtype)
+    torch.cuda.synchronize()
+    err = np.abs(out.cpu().numpy().astype(np.float64) - dbl)
+    assert (err <= rtol * ab + 1e-30).all(), "max err/scale = %g" % (err / np.maximum(ab, 1e-30)).max()
+
+
 def test_native_u16_layout_flags():
     K, N, M = 512, 48, 4
     W = sp.gen_ternary_iid(K, N, 0.4, 9)

@@ -102,6 +102,47 @@ def test_v256_encoding_roundtrip(p0):
     assert w.info.nnz == int((W != 0).sum())
 
 
+def _decode_delta_lane(w: sp.Weights):
+    """Invert the lane-delta layout: 304-byte blocks = 256 offsets (byte 8*lane + t), eight 32-bit
+    bases, eight counts; entry `lane` of step t is base[t] + offset for lane < count[t]."""
+    _, raw, _ = w.array(0)
+    _, off, _ = w.array(1)
+    blocks = raw.view(np.uint8).reshape(-1, 304)
+    off = off.view(np.uint32)
+    lists = []
+    for l in range(len(off) - 1):
+        rows = []
+        for blk in blocks[off[l]:off[l + 1]]:
+            offs = blk[:256].reshape(32, 8)
+            bases = blk[256:288].copy().view(np.uint32)
+            counts = blk[288:296]
+            assert (blk[296:] == 0).all()
+            for t in range(8):
+                rows.extend(int(bases[t]) + int(offs[lane, t]) for lane in range(counts[t]))
+        lists.append(np.array(rows, dtype=np.int64))
+    return lists
+
+
+@pytest.mark.parametrize("p0", [1 / 3, 0.75, 0.97, 1.0])
+def test_delta_lane_encoding_roundtrip(p0):
+    K, N = 1500, 24
+    W = sp.gen_ternary_iid(K, N, p0, 12)
+    w = sp.Weights(W, sp.FMT_DELTA_LANE)
+    lists = _decode_delta_lane(w)
+    for c in range(N):                                   # exact and in ascending order, whatever the gaps
+        assert (lists[2 * c] == np.nonzero(W[c] == 1)[0]).all()
+        assert (lists[2 * c + 1] == np.nonzero(W[c] == -1)[0]).all()
+    _, off, _ = w.array(1)
+    assert w.info.stream_bytes == int(off.view(np.uint32)[-1]) * 304 + (2 * N + 1) * 4
+    assert w.info.nnz == int((W != 0).sum()) and w.info.lossy_entries == 0
+
+
+def test_delta_lane_is_about_0_6_of_the_u16_stream():
+    W = sp.gen_ternary_fixed(6912, 16, 4096)
+    d, u = sp.Weights(W, sp.FMT_DELTA_LANE), sp.Weights(W, sp.FMT_U16_V256)
+    assert 0.55 < d.info.stream_bytes / u.info.stream_bytes < 0.70
+
+
 def _bank_cycles(step_rows: np.ndarray, rb: int) -> int:
     """Shared-memory cycles of one 32-lane gather of `rb`-byte rows: accesses of up to 4 bytes go
     in one phase of 32 lanes, 8-byte ones in half warps, 16-byte ones in quarter warps; a phase
