@@ -373,6 +373,30 @@ def run_ours(args):
                                           "exchange": "tagged words" if stk.tagged else "step counters"}
             del stk
             torch.cuda.empty_cache()
+            if world > 1:
+                # the same hardware used as replicas: every rank runs the whole stack on its own M
+                # rows, nothing is exchanged (world x M tokens per pass)
+                rep = stack_mod.TernaryStack(args.stack_layers, 2560, 6912, 640, M=m_rows, p_zero=1 / 3, seed=0, rank=0, world=1)
+                rep.set_input(O.gen_x_i8(m_rows * 2560, 5 + rank).reshape(m_rows, 2560))
+                with torch.cuda.stream(st):
+                    for _ in range(3):
+                        rep.forward(st.cuda_stream)
+                    st.synchronize()
+                    ok_r = rep.status() == 0
+                    dist.barrier()
+                    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s0.record(st)
+                    for _ in range(passes):
+                        rep.forward(st.cuda_stream)
+                    s1.record(st)
+                    st.synchronize()
+                t = torch.tensor([s0.elapsed_time(s1) / passes, 0.0 if ok_r else 1.0], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                rms = float(t[0].item())
+                stack_info["M%d" % m_rows]["replicas"] = {"us_per_pass": rms * 1e3, "tokens_per_s_all_gpus": world * m_rows / (rms * 1e-3),
+                                                           "status_ok": float(t[1].item()) == 0.0}
+                del rep
+                torch.cuda.empty_cache()
 
     large_info = large_sweep(args, sp, O, torch, dist, rank, world) if args.large else None
 

@@ -107,6 +107,13 @@ int sptmm_weights_upload(sptmm_weights *w);
 int sptmm_weights_upload_replicas(sptmm_weights *w, uint32_t copies);
 int sptmm_weights_free(sptmm_weights *w);
 
+/* Encoded weights on disk (no counterpart in the reference, which re-encodes on the GPU at every
+ * start, main.cu:972).  save writes the host-side arrays with a header (shape, format, counts)
+ * and a checksum; load rebuilds a handle ready for sptmm_weights_upload and rejects files whose
+ * header, array sizes, row indices or checksum do not fit together. */
+int sptmm_weights_save(const sptmm_weights *w, const char *path);
+int sptmm_weights_load(const char *path, sptmm_weights **out);
+
 /* ---- the matmul ---------------------------------------------------------------------------- */
 
 /* C = X*W with uploaded weights of any format.  X: device, `dtype` elements; C: device, int32

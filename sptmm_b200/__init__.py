@@ -58,6 +58,8 @@ def _load() -> C.CDLL:
         "sptmm_weights_upload_replicas": (i32, [vp, u32]),
         "sptmm_weights_free": (i32, [vp]),
         "sptmm_gemv": (i32, [vp, vp, u32, u32, vp, u32, u32, vp]),
+        "sptmm_weights_save": (i32, [vp, C.c_char_p]),
+        "sptmm_weights_load": (i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
         "sptmm_gemv_reduce": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, vp]),
         "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32, u32]),
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
@@ -89,7 +91,7 @@ def _load() -> C.CDLL:
 lib = _load()
 EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
-           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host",
+           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
@@ -144,6 +146,19 @@ class Weights:
         check(lib.sptmm_encode(W.ctypes.data, K, N, fmt, split, S, C.byref(h)))
         self._h = h
         self.info = self._info()
+
+    @classmethod
+    def load(cls, path: str) -> "Weights":
+        """An encoded matrix written by save(); ready for upload()."""
+        h = C.c_void_p()
+        check(lib.sptmm_weights_load(os.fsencode(path), C.byref(h)))
+        self = cls.__new__(cls)
+        self._h = h
+        self.info = self._info()
+        return self
+
+    def save(self, path: str) -> None:
+        check(lib.sptmm_weights_save(self._h, os.fsencode(path)))
 
     def _info(self) -> WeightsInfo:
         info = WeightsInfo()

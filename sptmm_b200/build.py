@@ -24,7 +24,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 NVCC_FLAGS += os.environ.get("SPTMM_NVCC_EXTRA", "").split()      # e.g. -DSPTMM_SEQ_PROFILE for loop timers
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-pthread"]
 
-LIB_SOURCES = ["host_encode.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "kernels_seq.cu", "cublas_cmp.cu"]
+LIB_SOURCES = ["host_encode.cpp", "weights_file.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "kernels_seq.cu", "cublas_cmp.cu"]
 HEADERS = ["internal.h", "device_common.cuh", os.path.join(ROOT, "include", "sptmm.h")]
 
 
@@ -71,6 +71,10 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             if force or _newer(out, [cli, LIB] + hdrs):
                 _run(["g++"] + CXX_FLAGS + [layout, cli, "-o", out, "-L" + PKG, "-lsptmm",
                       "-Wl,-rpath,$ORIGIN/.."], verbose)
+    enc = os.path.join(CSRC, "cli_encode.cpp")
+    out = os.path.join(BIN, "sptmm_encode")
+    if os.path.exists(enc) and (force or _newer(out, [enc, LIB] + hdrs)):
+        _run(["g++"] + CXX_FLAGS + [enc, "-o", out, "-L" + PKG, "-lsptmm", "-Wl,-rpath,$ORIGIN/.."], verbose)
     return LIB
 
 

@@ -39,6 +39,7 @@ struct Flags {
     uint64_t row_split3_small = 0, row_split_delta2 = 0, M = 32, K = 3072, N = 768, S = 256, L = 1, native = 1;
     uint64_t seed = 0;          // 0 = std::random_device, as the reference (main.cu:788)
     uint32_t iter = 10;
+    std::string weights;        // an encoded-weights file (bin/sptmm_encode) to run instead of generating and encoding
 };
 
 [[noreturn]] void die(const char *msg)
@@ -64,7 +65,7 @@ Flags parse(int argc, char **argv)
         {"cu_blas", 'b', &f.cu_blas}, {"i2s", 'b', &f.i2s}, {"check", 'b', &f.check}, {"json", 'b', &f.json},
         {"row_split3_small", 'q', &f.row_split3_small}, {"row_split_delta2", 'q', &f.row_split_delta2},
         {"M", 'q', &f.M}, {"K", 'q', &f.K}, {"N", 'q', &f.N}, {"S", 'q', &f.S}, {"L", 'q', &f.L},
-        {"native", 'q', &f.native}, {"seed", 'q', &f.seed}, {"iter", 'u', &f.iter},
+        {"native", 'q', &f.native}, {"seed", 'q', &f.seed}, {"iter", 'u', &f.iter}, {"weights", 's', &f.weights},
     };
     for (int i = 1; i < argc; i++) {
         const char *a = argv[i];
@@ -80,7 +81,8 @@ Flags parse(int argc, char **argv)
                 if (o.kind == 'b' && !has_val) *(bool *)o.ptr = true;
                 else {
                     if (!has_val && i + 1 < argc) val = argv[++i];
-                    if (o.kind == 'b') *(bool *)o.ptr = !(val == "false" || val == "0");
+                    if (o.kind == 's') *(std::string *)o.ptr = val;
+                    else if (o.kind == 'b') *(bool *)o.ptr = !(val == "false" || val == "0");
                     else if (o.kind == 'q') *(uint64_t *)o.ptr = strtoull(val.c_str(), nullptr, 10);
                     else *(uint32_t *)o.ptr = (uint32_t)strtoul(val.c_str(), nullptr, 10);
                 }
@@ -220,7 +222,14 @@ int main(int argc, char **argv)
 
     auto run_sptmm = [&](const char *mode, uint32_t format, uint32_t split) {
         sptmm_weights *w = nullptr;
-        must(sptmm_encode(weights().data(), (uint32_t)f.K, (uint32_t)f.N, format, split, (uint32_t)f.S, &w), mode);
+        if (!f.weights.empty()) {
+            must(sptmm_weights_load(f.weights.c_str(), &w), "weights");
+            sptmm_weights_info wi;
+            must(sptmm_weights_info_get(w, &wi), "info");
+            if (wi.K != f.K || wi.N != f.N) die("the -weights file does not hold a K x N matrix of the -K and -N given");
+        } else {
+            must(sptmm_encode(weights().data(), (uint32_t)f.K, (uint32_t)f.N, format, split, (uint32_t)f.S, &w), mode);
+        }
         must(sptmm_weights_upload(w), "upload");
         sptmm_weights_info info;
         must(sptmm_weights_info_get(w, &info), "info");

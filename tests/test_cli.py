@@ -69,3 +69,53 @@ def test_readme_commands(binary, args):
     assert m, lines[2]
     assert float(lines[3]) > 0
     assert "check: OK" in r.stderr
+
+
+# ---------------------------------------------------------------- offline encoder
+
+ENC = os.path.join(ROOT, "sptmm_b200", "bin", "sptmm_encode")
+
+
+@pytest.mark.parametrize("fmt_name,fmt_flag", [("u16_v256", []), ("delta_lane", []), ("u16_div", ["-split", "32"]), ("i2s", [])])
+def test_offline_encoder_writes_what_the_library_encodes(tmp_path, fmt_name, fmt_flag):
+    import numpy as np
+    import sptmm_b200 as sp
+    path = str(tmp_path / "w.sptmm")
+    r = run(ENC, "-K", "256", "-N", "48", "-S", "128", "-format", fmt_name, "-o", path, *fmt_flag)
+    assert r.returncode == 0, r.stderr
+    assert "K=256 N=48" in r.stdout
+    fmt = {"u16_v256": sp.FMT_U16_V256, "delta_lane": sp.FMT_DELTA_LANE, "u16_div": sp.FMT_U16_DIV, "i2s": sp.FMT_I2S}[fmt_name]
+    want = sp.Weights(sp.gen_ternary_fixed(256, 48, 128), fmt, split=32, S=128 if fmt == sp.FMT_U16_DIV else 0)
+    got = sp.Weights.load(path)
+    assert got.info.n_arrays == want.info.n_arrays and got.info.nnz == want.info.nnz
+    for i in range(want.info.n_arrays):
+        assert (got.array(i)[1] == want.array(i)[1]).all()
+
+
+def test_offline_encoder_reads_a_dense_matrix_and_checks_its_size(tmp_path):
+    import numpy as np
+    import sptmm_b200 as sp
+    W = sp.gen_ternary_iid(128, 20, 0.5, 9)
+    dense, path = str(tmp_path / "W.i8"), str(tmp_path / "w.sptmm")
+    W.tofile(dense)
+    r = run(ENC, "-K", "128", "-N", "20", "-dense", dense, "-o", path)
+    assert r.returncode == 0, r.stderr
+    want = sp.Weights(W, sp.FMT_U16_V256)
+    assert (sp.Weights.load(path).array(0)[1] == want.array(0)[1]).all()
+    r = run(ENC, "-K", "128", "-N", "21", "-dense", dense, "-o", path)
+    assert r.returncode != 0 and "exactly K*N bytes" in r.stderr
+    r = run(ENC, "-K", "128", "-N", "20", "-o", path)
+    assert r.returncode != 0 and "-S" in r.stderr
+    r = run(ENC, "-K", "128", "-N", "20", "-S", "64", "-format", "nope", "-o", path)
+    assert r.returncode != 0 and "unknown -format" in r.stderr
+
+
+@pytest.mark.gpu
+def test_rcr_runs_an_encoded_weights_file(tmp_path):
+    path = str(tmp_path / "w.sptmm")
+    assert run(ENC, "-K", "6912", "-N", "2560", "-S", "4096", "-format", "u16_v256", "-o", path).returncode == 0
+    r = run(RCR, "-row_split3_small", "32", "-M=4", "-K=6912", "-N=2560", "-S=4096", "-iter=5", "-check", "-seed=3", "-weights", path)
+    assert r.returncode == 0, r.stderr
+    assert "check: OK" in r.stderr
+    r = run(RCR, "-row_split3_small", "32", "-M=1", "-K=256", "-N=2560", "-S=128", "-iter=1", "-weights", path)
+    assert r.returncode != 0 and "-weights file" in r.stderr
