@@ -227,6 +227,7 @@ int main(int argc, char **argv)
             sptmm_weights_info wi;
             must(sptmm_weights_info_get(w, &wi), "info");
             if (wi.K != f.K || wi.N != f.N) die("the -weights file does not hold a K x N matrix of the -K and -N given");
+            if (f.check) weights();       // -check compares with the reference generator's matrix for -K -N -S
         } else {
             must(sptmm_encode(weights().data(), (uint32_t)f.K, (uint32_t)f.N, format, split, (uint32_t)f.S, &w), mode);
         }
