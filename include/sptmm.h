@@ -189,7 +189,12 @@ typedef struct sptmm_seq_step {
                                 tagged words there ((int32)(w << 8) >> 8 recovers the value; it
                                 always fits, since |value| <= 127*K < 2^23).  A buffer may be
                                 rewritten by the second step after the one that reads it, not
-                                by the next one.                                                  */
+                                by the next one.
+                                3: as 1 with no X2, and X is the WHOLE output row of step `dep`
+                                (all columns, all ranks' shards, ldx = that step's ldc).  The
+                                producing step then also records every row's largest magnitude
+                                while it stores its results, and this step quantises in one pass
+                                over X instead of two (absmax first, values second).             */
     const void *X;           /* device, M rows of K elements, row stride ldx (0 = K)              */
     const void *X2;          /* optional second int32 source, row stride ldx2 (0 = K)             */
     void *C;                 /* device int32, M rows of N, row stride ldc (0 = N)                 */
@@ -200,6 +205,11 @@ typedef struct sptmm_seq_step {
                                 whole device.  Buffers are the caller's: a step must not overwrite
                                 memory that a step it does not (transitively) depend on may still
                                 be reading.                                                       */
+    uint32_t c_kind;         /* 0: C holds the N results of a row.  1: pair sums -- C holds N/2
+                                values per row, C[m][j] = result[2j] + result[2j+1] (a fused
+                                "gate | up" matrix with its columns interleaved hands the next
+                                step one source instead of two); N even, ldc counts output
+                                elements                                                          */
 } sptmm_seq_step;
 
 int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, sptmm_seq **out);
@@ -212,9 +222,11 @@ int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, 
  *  - C_peers[s*n_peers + p]: where step s's shard starts in rank p's buffer (peer-mapped device
  *    pointer valid in THIS process, e.g. from CUDA IPC / symmetric memory; p = own rank too).
  *    Each points at column 0 of this rank's shard inside the full-width row (stride ldc).
- *  - counter_peers[p]: rank p's array of n_steps uint64 counters, zeroed once before first use,
+ *  - counter_peers[p]: rank p's synchronisation area of sptmm_seq_shared_bytes(n_steps) bytes
+ *    (step counters, then the row maxima of x_kind 3), zeroed once before first use,
  *    peer-mapped likewise.  All ranks must create the same sequence and run it equally often.
  * steps[].C is ignored when n_peers > 0. */
+uint64_t sptmm_seq_shared_bytes(uint32_t n_steps);
 int sptmm_seq_create_shared(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M,
                             void *const *C_peers, void *const *counter_peers, uint32_t n_peers,
                             uint32_t my_rank, sptmm_seq **out);

@@ -67,6 +67,7 @@ def _load() -> C.CDLL:
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
         "sptmm_seq_create": (i32, [vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_create_shared": (i32, [vp, u32, u32, vp, vp, u32, u32, C.POINTER(vp)]),
+        "sptmm_seq_shared_bytes": (u64, [u32]),
         "sptmm_seq_run": (i32, [vp, vp]),
         "sptmm_seq_run_static": (i32, [vp, u32, u32, vp, C.POINTER(u32)]),
         "sptmm_seq_status": (i32, [vp, C.POINTER(u32), C.POINTER(u64)]),
@@ -93,7 +94,7 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
-           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
+           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
 
@@ -220,7 +221,7 @@ class Weights:
 class SeqStep(C.Structure):
     _fields_ = [("w", C.c_void_p), ("replica", C.c_uint32), ("x_kind", C.c_uint32), ("X", C.c_void_p),
                 ("X2", C.c_void_p), ("C", C.c_void_p), ("scale_out", C.c_void_p),
-                ("ldx", C.c_uint32), ("ldx2", C.c_uint32), ("ldc", C.c_uint32), ("dep", C.c_int32)]
+                ("ldx", C.c_uint32), ("ldx2", C.c_uint32), ("ldc", C.c_uint32), ("dep", C.c_int32), ("c_kind", C.c_uint32)]
 
 
 class Sequence:
@@ -243,7 +244,7 @@ class Sequence:
             a.C = _ptr(s["C"]) if s.get("C") is not None else None
             a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
             a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
-            a.dep = s.get("dep", -1)
+            a.dep = s.get("dep", -1); a.c_kind = s.get("c_kind", 0)
         h = C.c_void_p()
         if counter_peers is None:
             check(lib.sptmm_seq_create(C.cast(arr, C.c_void_p), len(steps), M, C.byref(h)))
@@ -308,7 +309,7 @@ def run_sequence_static(steps, M: int = 1, stream: int = 0, wait: bool = True) -
         a.C = _ptr(s["C"])
         a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
         a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
-        a.dep = s.get("dep", -1)
+        a.dep = s.get("dep", -1); a.c_kind = s.get("c_kind", 0)
     st = C.c_uint32(0)
     check(lib.sptmm_seq_run_static(C.cast(arr, C.c_void_p), len(steps), M, stream, C.byref(st) if wait else None))
     return st.value

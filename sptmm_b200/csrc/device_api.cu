@@ -68,8 +68,10 @@ static void free_device_side(sptmm_weights *w)
 
 // Give each of `grid` CTAs a contiguous run of whole columns holding about total/grid blocks.
 // off = the 2N+1 list boundaries of a native-format matrix.
+// With col_align = 2 every boundary falls on an even column (steps that sum column pairs).
 void plan_columns(const uint32_t *off, uint32_t N, uint32_t grid, std::vector<uint32_t> &cta_blk,
-                  std::vector<uint32_t> &cta_col, uint32_t &max_cols, uint32_t &max_cta_blocks)
+                  std::vector<uint32_t> &cta_col, uint32_t &max_cols, uint32_t &max_cta_blocks,
+                  uint32_t col_align)
 {
     const uint64_t total = off[2 * (size_t)N];
     cta_blk.clear(); cta_col.clear();
@@ -83,6 +85,7 @@ void plan_columns(const uint32_t *off, uint32_t N, uint32_t grid, std::vector<ui
             while (c1 < N && off[2 * (size_t)(c1 + 1)] <= target) c1++;
             // take one more column if that lands closer to the target
             if (c1 < N && (int64_t)off[2 * (size_t)(c1 + 1)] - (int64_t)target < (int64_t)target - (int64_t)off[2 * (size_t)c1]) c1++;
+            if (col_align > 1) c1 = std::min(N, std::max(c, (c1 + col_align - 1) / col_align * col_align));
         }
         cta_blk.push_back(off[2 * (size_t)c]);
         cta_col.push_back(c);

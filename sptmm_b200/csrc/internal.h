@@ -85,7 +85,8 @@ int launch_delta256(const void *X, const uint8_t *dp, const uint8_t *dn, void *C
                     uint32_t M, uint32_t K, uint32_t N, uint32_t S, uint32_t flags, void *stream);
 void set_trace_buffer(unsigned long long *dev_ptr);
 void plan_columns(const uint32_t *off, uint32_t N, uint32_t grid, std::vector<uint32_t> &cta_blk,
-                  std::vector<uint32_t> &cta_col, uint32_t &max_cols, uint32_t &max_cta_blocks);
+                  std::vector<uint32_t> &cta_col, uint32_t &max_cols, uint32_t &max_cta_blocks,
+                  uint32_t col_align = 1);
 int kernels_init();                   // opt in to >48 KB dynamic shared memory, once per process
 
 inline size_t dtype_size(uint32_t d) { return d == SPTMM_I8 ? 1 : d == SPTMM_F16 ? 2 : 4; }

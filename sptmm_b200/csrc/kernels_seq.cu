@@ -49,6 +49,8 @@ struct SeqDesc {
     uint32_t out_tag_m, out_tag_j;   // this step's output: m == 0 -> plain int32
     uint32_t in_tag_m, in_tag_j;     // x_kind 2: the tag of the step that produces X (and X2)
     uint32_t release;                // 1: bump the step counter after the output is stored
+    uint32_t c_kind;                 // 1: the output is the sum of each pair of neighbouring columns (N/2 values)
+    uint32_t want_amax;              // 1: a later x_kind 3 step wants this step's row maxima recorded
 };
 
 constexpr uint32_t kPollLimit = 1u << 20;        // reloads of one stale word before giving up
@@ -108,6 +110,11 @@ struct SeqParams {
     uint32_t slot_blocks;        // 512-byte blocks per ring slot
     uint32_t one;                // always 1: a multiplier the compiler cannot fold (LaneAcc::add)
     uint32_t run_mod;            // run number mod 255 (tags of the tagged exchange change every run)
+    // Row maxima for x_kind 3: amax[(parity * nsteps + step) * 16 + row], on this rank and (peer-mapped)
+    // on every rank; a run uses the half `run_parity` and clears the other half for the next run.
+    uint32_t *amax;
+    uint32_t *amax_peers[kMaxPeers];
+    uint32_t run_parity;
 };
 
 // Timestamp for the optional trace.  A bare read of %globaltimer is hoisted by the assembler
@@ -161,6 +168,12 @@ __device__ __forceinline__ int quant1(int v, float scale)
     return max(-127, min(127, __float2int_rn((float)v * scale)));
 }
 
+// All CTAs stage the same activations at the same time.  Walking them in the same order makes every
+// SM ask the same L2 slice at the same moment (measured: 2 TB/s in all, a third of what L2 gives);
+// each CTA therefore starts at its own offset and wraps around.
+__device__ __forceinline__ uint32_t cta_rotation(uint32_t n) { return (uint32_t)(((uint64_t)blockIdx.x * n) / gridDim.x); }
+__device__ __forceinline__ uint32_t rotated(uint32_t i, uint32_t rot, uint32_t n) { return i + rot < n ? i + rot : i + rot - n; }
+
 // The quantiser for tiles of 4 or 16 rows, all rows at once.  Pass 1: every thread walks the
 // rows in 16-byte pieces (all rows' loads of a piece in flight together) and keeps one running
 // absmax per row; warps combine them through shared memory (two barriers in all).  Pass 2 reads
@@ -210,7 +223,9 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
     int am[MT];
 #pragma unroll
     for (int m = 0; m < MT; m++) am[m] = 0;
-    for (uint32_t q = tid; q < quads; q += nt) {
+    const uint32_t rot = cta_rotation(quads);
+    for (uint32_t q0 = tid; q0 < quads; q0 += nt) {
+        const uint32_t q = rotated(q0, rot, quads);
 #pragma unroll
         for (int g = 0; g < MT / 4; g++) {
             int4 v[4];
@@ -244,7 +259,8 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
         if (write_scale && d.scale_out && tid == (uint32_t)m && (uint32_t)m < M) d.scale_out[m] = (float)a / 127.0f;
     }
 
-    for (uint32_t q = tid; q < quads; q += nt) {
+    for (uint32_t q0 = tid; q0 < quads; q0 += nt) {
+        const uint32_t q = rotated(q0, rot, quads);
 #pragma unroll
         for (int g = 0; g < MT / 4; g++) {
             int4 v[4];
@@ -398,6 +414,76 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
         if (write_scale && d.scale_out && tid == 0) d.scale_out[m] = (float)amax / 127.0f;
     }
     if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);          // the zero row
+}
+
+// x_kind 3: the rows' largest magnitudes are already known (recorded by the producing step), so
+// one pass over X quantises it: q = clamp(rint(v * (127 / amax)), -127, 127) as in stage_x_quant.
+template <int MT>
+__device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc &d, uint32_t M, const uint32_t *amax, bool write_scale)
+{
+    const uint32_t tid = threadIdx.x, nt = 512;                       // consumer threads only
+    float scale[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        const uint32_t a = (uint32_t)m < M ? __ldcg(amax + m) : 0u;
+        scale[m] = a ? 127.0f / (float)a : 0.0f;
+        if (write_scale && d.scale_out && tid == (uint32_t)m && (uint32_t)m < M) d.scale_out[m] = (float)a / 127.0f;
+    }
+    const bool vec = (d.K & 3) == 0 && (d.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(d.X) & 15) == 0;
+    if constexpr (MT == 1) {
+        const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
+        if (vec) {
+            for (uint32_t q = tid; q < d.K / 4; q += nt) {
+                const int4 v = __ldcg(reinterpret_cast<const int4 *>(A) + q);
+                const uint32_t w = (uint32_t)(quant1(v.x, scale[0]) & 0xff) | ((uint32_t)(quant1(v.y, scale[0]) & 0xff) << 8) |
+                                   ((uint32_t)(quant1(v.z, scale[0]) & 0xff) << 16) | ((uint32_t)(quant1(v.w, scale[0]) & 0xff) << 24);
+                reinterpret_cast<uint32_t *>(xs)[q] = w;
+            }
+        } else {
+            for (uint32_t k = tid; k < d.K; k += nt) xs[k] = (unsigned char)quant1(__ldcg(A + k), scale[0]);
+        }
+        if (tid == 0) xs[d.K] = 0;
+    } else {
+        int8_t *dst = reinterpret_cast<int8_t *>(xs);
+        if (vec && MT >= 4) {
+            if constexpr (MT >= 4) {
+                const int4 *A = reinterpret_cast<const int4 *>(d.X);
+                const uint32_t lda = d.ldx / 4;
+                const uint32_t quads = d.K / 4, rot = cta_rotation(quads);
+                for (uint32_t q0 = tid; q0 < quads; q0 += nt) {
+                    const uint32_t q = rotated(q0, rot, quads);
+#pragma unroll
+                    for (int g = 0; g < MT / 4; g++) {
+                        int4 v[4];
+#pragma unroll
+                        for (int r = 0; r < 4; r++)
+                            v[r] = (uint32_t)(4 * g + r) < M ? __ldcg(A + (size_t)(4 * g + r) * lda + q) : make_int4(0, 0, 0, 0);
+                        uint32_t o[4];
+#define SPTMM_PACK4(f) ((uint32_t)(quant1(v[0].f, scale[4 * g]) & 0xff) | ((uint32_t)(quant1(v[1].f, scale[4 * g + 1]) & 0xff) << 8) | \
+                        ((uint32_t)(quant1(v[2].f, scale[4 * g + 2]) & 0xff) << 16) | ((uint32_t)(quant1(v[3].f, scale[4 * g + 3]) & 0xff) << 24))
+                        o[0] = SPTMM_PACK4(x) ^ 0x80808080u;
+                        o[1] = SPTMM_PACK4(y) ^ 0x80808080u;
+                        o[2] = SPTMM_PACK4(z) ^ 0x80808080u;
+                        o[3] = SPTMM_PACK4(w) ^ 0x80808080u;
+#undef SPTMM_PACK4
+                        if constexpr (MT == 4) {
+                            *reinterpret_cast<uint4 *>(xs + (size_t)q * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+                                *reinterpret_cast<uint32_t *>(xs + ((size_t)q * 4 + i) * MT + 4 * g) = o[i];
+                        }
+                    }
+                }
+            }
+        } else {
+            const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
+            for (uint32_t m = 0; m < (uint32_t)MT; m++)
+                for (uint32_t k = tid; k < d.K; k += nt)
+                    dst[(size_t)k * MT + m] = tile_byte<MT>(m < M ? quant1(__ldcg(A + (size_t)m * d.ldx + k), scale[m]) : 0);
+        }
+        if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);
+    }
 }
 
 // int8 rows with a row stride, read around L1 (the buffer may have been written by other CTAs)
@@ -579,7 +665,10 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         // L2 lines) hides behind the gathers
         uint32_t nxt = 0;
         if (s + 1 < p.nsteps) nxt = load_step_word(s + 1);
+        if (p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
+            p.amax[((p.run_parity ^ 1u) * p.nsteps + s) * 16 + tid] = 0u;
         if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
+        else if (d.x_kind == 3) stage_x_scaled<MT>(xs, d, p.M, p.amax + ((size_t)p.run_parity * p.nsteps + (uint32_t)d.dep) * 16, cta == 0);
         else {
             bool fresh = failed == 0;          // after a failure nothing waits any more
             const uint32_t tag = (TAGGED && d.x_kind == 2) ? seq_tag(p.run_mod, d.in_tag_m, d.in_tag_j) : 0u;
@@ -695,25 +784,38 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             const bool tag_out = TAGGED && d.out_tag_m != 0;
             const uint32_t otag = tag_out ? seq_tag(p.run_mod, d.out_tag_m, d.out_tag_j) << 24 : 0u;
             auto out_word = [&](int v) { return tag_out ? (int)(otag | ((uint32_t)v & 0xffffffu)) : v; };
+            // what goes out: every column's sum, or (c_kind 1) the sums of neighbouring column pairs;
+            // the plan gives a pair-summing step even column boundaries
+            const uint32_t nout = d.c_kind ? ncols / 2 : ncols, o0 = d.c_kind ? c0 / 2 : c0;
+            auto value = [&](uint32_t j, uint32_t m) { return d.c_kind ? c_s[(2 * j) * MT + m] + c_s[(2 * j + 1) * MT + m] : c_s[j * MT + m]; };
+            for (uint32_t i = lane; i < nout * p.M; i += 32) {
+                const uint32_t m = i / nout, j = i - m * nout;
+                const int wv = out_word(value(j, m));
+                if (p.n_peers == 0) d.C[(size_t)m * d.ldc + o0 + j] = wv;
+                else                  // the exchange: straight into every rank's buffer over NVLink (plain peer stores)
+                    for (uint32_t r = 0; r < p.n_peers; r++) d.Cp[r][(size_t)m * d.ldc + o0 + j] = wv;
+            }
+            if (d.want_amax) {        // every row's largest magnitude, for the x_kind 3 reader: lane m reports row m
+                uint32_t mine = 0;
+                for (uint32_t m = 0; m < p.M; m++) {
+                    uint32_t mx = 0;
+                    for (uint32_t j = lane; j < nout; j += 32) mx = max(mx, (uint32_t)abs(value(j, m)));
+                    mx = __reduce_max_sync(0xffffffffu, mx);
+                    if (lane == m) mine = mx;
+                }
+                const size_t slot = ((size_t)p.run_parity * p.nsteps + s) * 16 + lane;
+                if (lane < p.M) {
+                    if (p.n_peers == 0) atomicMax(p.amax + slot, mine);
+                    else
+                        for (uint32_t r = 0; r < p.n_peers; r++) atomicMax_system(p.amax_peers[r] + slot, mine);
+                }
+            }
+            __syncwarp();
+            // the release orders this warp's stores and reductions (seen through __syncwarp) before the count
             if (p.n_peers == 0) {
-                for (uint32_t i = lane; i < ncols * p.M; i += 32) {
-                    const uint32_t m = i / ncols, col = i - m * ncols;
-                    d.C[(size_t)m * d.ldc + c0 + col] = out_word(c_s[col * MT + m]);
-                }
-                __syncwarp();
-                // the release orders this warp's stores (seen by lane 0 through __syncwarp) before the count
                 if (lane == 0 && (!TAGGED || d.release)) asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
-            } else {
-                // the exchange: this CTA's columns go straight into every rank's buffer over NVLink
-                // (plain peer stores), then every rank's counter for the step is bumped
-                for (uint32_t i = lane; i < ncols * p.M; i += 32) {
-                    const uint32_t m = i / ncols, col = i - m * ncols;
-                    const int v = out_word(c_s[col * MT + m]);
-                    for (uint32_t r = 0; r < p.n_peers; r++) d.Cp[r][(size_t)m * d.ldc + c0 + col] = v;
-                }
-                __syncwarp();
-                if (lane < p.n_peers && (!TAGGED || d.release))
-                    asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p.counter_peers[lane] + s) : "memory");
+            } else if (lane < p.n_peers && (!TAGGED || d.release)) {
+                asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p.counter_peers[lane] + s) : "memory");
             }
         }
         if (tracing) p.trace[s * 4 + 3] = seq_ns(&failed);
@@ -787,7 +889,9 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         if (!w || !st.X || (!st.C && !n_peers)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u has a null pointer", s);
         else if (w->format != SPTMM_FMT_U16_V256) rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u is not in the native u16 format", s);
         else if (w->device != dev || st.replica >= w->dev.size()) rc = fail(SPTMM_ERR_STATE, "seq_create: step %u weights are not uploaded to device %d (replica %u)", s, dev, st.replica);
-        else if (st.x_kind > 2) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
+        else if (st.x_kind > 3) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
+        else if (st.x_kind == 3 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 3) needs a producer (dep) and takes no X2", s);
+        else if (st.c_kind > 1 || (st.c_kind == 1 && (w->N & 1))) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u c_kind %u (pair sums need an even N)", s, st.c_kind);
         else if (st.x_kind == 2 && st.dep < 0) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u reads tagged words but names no producer (dep)", s);
         else if (st.dep >= (int32_t)s) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u depends on step %d, which does not precede it", s, st.dep);
         if (rc != SPTMM_OK) { seq_release(q); return rc; }
@@ -798,6 +902,8 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         d.K = w->K; d.N = w->N;
         d.ldx = st.ldx ? st.ldx : w->K; d.ldx2 = st.ldx2 ? st.ldx2 : w->K; d.ldc = st.ldc ? st.ldc : w->N;
         d.uniform_nbl = w->uniform_nbl; d.x_kind = st.x_kind; d.dep = st.dep < 0 ? -1 : st.dep;
+        d.c_kind = st.c_kind;
+        d.ldc = st.ldc ? st.ldc : (st.c_kind ? w->N / 2 : w->N);
         for (uint32_t r = 0; r < kMaxPeers; r++) d.Cp[r] = r < n_peers ? (int32_t *)C_peers[(size_t)s * n_peers + r] : nullptr;
         if (n_peers) {
             for (uint32_t r = 0; r < n_peers; r++)
@@ -805,7 +911,7 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
             d.C = d.Cp[my_rank];
         }
         uint32_t mc = 1, mb = 0;
-        plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q->G, tb, tc, mc, mb);
+        plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q->G, tb, tc, mc, mb, st.c_kind ? 2u : 1u);
         blk.insert(blk.end(), tb.begin(), tb.end());
         col.insert(col.end(), tc.begin(), tc.end());
         q->max_cols = std::max(q->max_cols, mc);
@@ -822,6 +928,9 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         int rc = SPTMM_OK;
         for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++) {
             desc[s].release = tagged[s] ? 0 : 1;
+            if (steps[s].x_kind == 3) desc[(uint32_t)steps[s].dep].want_amax = 1;
+            if (tagged[s] && desc[s].c_kind && desc[s].K > 33000)
+                rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u: pair sums over K=%u rows do not fit a tagged word", s, desc[s].K);
             if (steps[s].x_kind != 2 && steps[s].dep >= 0 && tagged[(uint32_t)steps[s].dep])
                 rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u waits for step %d, whose output is tagged for an x_kind 2 reader", s, steps[s].dep);
             if (!tagged[s]) continue;
@@ -840,7 +949,7 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
                 desc[s].in_tag_m = pd.out_tag_m; desc[s].in_tag_j = pd.out_tag_j;
                 // the producer's rows are ldc wide and its columns (one shard of them, on several
                 // GPUs) start somewhere inside the first row: accept any address within the rows
-                const char *lo = (const char *)pd.C - (size_t)(pd.ldc - pd.N) * 4, *hi = (const char *)pd.C + (size_t)M * pd.ldc * 4;
+                const char *lo = (const char *)pd.C - (size_t)pd.ldc * 4, *hi = (const char *)pd.C + (size_t)M * pd.ldc * 4;
                 const char *x = (const char *)steps[s].X, *x2 = (const char *)steps[s].X2;
                 if (x < lo || x >= hi || (x2 && (x2 < lo || x2 >= hi)))
                     rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u reads tagged words outside the output of step %d", s, steps[s].dep);
@@ -882,8 +991,8 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
             q->counter_peers[r] = counter_peers[r];
         }
     } else {
-        if (e == cudaSuccess) e = cudaMalloc(&q->d_counters, (size_t)n * 8);
-        if (e == cudaSuccess) e = cudaMemset(q->d_counters, 0, (size_t)n * 8);
+        if (e == cudaSuccess) e = cudaMalloc(&q->d_counters, sptmm_seq_shared_bytes(n));
+        if (e == cudaSuccess) e = cudaMemset(q->d_counters, 0, sptmm_seq_shared_bytes(n));
     }
     if (e == cudaSuccess) e = cudaMalloc(&q->d_status, 16);
     if (e == cudaSuccess) e = cudaMemset(q->d_status, 0, 16);
@@ -891,6 +1000,9 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
     *out = q;
     return SPTMM_OK;
 }
+
+// step counters (n x u64), then the row maxima (2 halves x n steps x 16 rows x u32)
+extern "C" uint64_t sptmm_seq_shared_bytes(uint32_t n_steps) { return (uint64_t)n_steps * 8 + (uint64_t)2 * n_steps * 16 * 4; }
 
 extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_t M, sptmm_seq **out)
 {
@@ -953,6 +1065,10 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     prm.nsteps = q->nsteps; prm.M = q->M; prm.max_cols = q->max_cols; prm.ring_slots = q->ring_slots;
     prm.xs_bytes = q->xs_bytes; prm.G = q->G; prm.slot_blocks = q->slot_blocks; prm.one = 1;
     prm.run_mod = (uint32_t)(q->epoch % 255);
+    prm.run_parity = (uint32_t)(q->epoch & 1);
+    for (uint32_t r = 0; r < kMaxPeers; r++)
+        prm.amax_peers[r] = q->counter_peers[r] ? (uint32_t *)((char *)q->counter_peers[r] + (size_t)q->nsteps * 8) : nullptr;
+    prm.amax = (uint32_t *)((char *)prm.counters + (size_t)q->nsteps * 8);
     cudaStream_t st = (cudaStream_t)stream;
     switch (q->mt) {
         case 1: return seq_launch<1>(q, prm, st);
@@ -1047,7 +1163,7 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
         if (!w || !st.X || !st.C) return fail(SPTMM_ERR_INVALID, "seq_run_static: step %u has a null pointer", s);
         if (w->format != SPTMM_FMT_U16_V256) return fail(SPTMM_ERR_UNSUPPORTED, "seq_run_static: step %u is not in the native u16 format", s);
         if (w->device != dev || st.replica >= w->dev.size()) return fail(SPTMM_ERR_STATE, "seq_run_static: step %u weights are not uploaded to device %d", s, dev);
-        if (st.x_kind > 1 || st.dep >= (int32_t)s) return fail(SPTMM_ERR_INVALID, "seq_run_static: step %u has a bad x_kind or dep", s);
+        if (st.x_kind > 1 || st.c_kind != 0 || st.dep >= (int32_t)s) return fail(SPTMM_ERR_INVALID, "seq_run_static: step %u has a bad x_kind, c_kind or dep", s);
         SeqDesc &d = desc[s];
         d.idx = (const uint4 *)w->dev[st.replica][0];
         d.blk_off = (const uint32_t *)w->dev[st.replica][1];
@@ -1098,7 +1214,8 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
     prm.trace = nullptr;
     prm.target = q.G;                              // counters were just cleared: one run's worth
     prm.nsteps = n; prm.M = M; prm.max_cols = q.max_cols; prm.ring_slots = q.ring_slots;
-    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1; prm.run_mod = 0;
+    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1; prm.run_mod = 0; prm.run_parity = 0; prm.amax = nullptr;
+    for (uint32_t r = 0; r < kMaxPeers; r++) prm.amax_peers[r] = nullptr;
     int rc = SPTMM_OK;
     switch (q.mt) {
         case 1: rc = seq_launch<1>(&q, prm, st); break;

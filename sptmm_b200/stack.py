@@ -10,8 +10,9 @@ Per layer, four dependent steps (int8 activations, int32 results, per-row absmax
 fused into the next step's input stage):
     qkv  = Wqkv(x)          hidden -> hidden + 2*kv       x: previous layer's `down` output
     o    = Wo(qkv[:, :hidden])                            (stand-in for attention: the q part)
-    gu   = Wgu(o)           hidden -> 2*ffn               (gate | up fused along N)
-    down = Wdown(gu[:, :ffn] + gu[:, ffn:])               ffn -> hidden
+    gu   = Wgu(o)           hidden -> ffn                 (gate | up fused along N with their columns
+                                                           interleaved; the step stores gate_j + up_j)
+    down = Wdown(gu)                                      ffn -> hidden
 
 Multi-GPU: every matrix is sharded by contiguous column ranges over the ranks of one node; each
 rank's kernel stores its output columns into every rank's buffers over NVLink and the step
@@ -48,7 +49,7 @@ def stack_weights(layers: int, hidden: int, ffn: int, kv: int, p_zero: float, se
 
 class TernaryStack:
     def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, M=1, p_zero=1 / 3, seed=0,
-                 rank=0, world=1, group=None, keep_dense=False, tagged=None):
+                 rank=0, world=1, group=None, keep_dense=False, tagged=None, row_maxima=False):
         import torch
         self.torch = torch
         self.layers, self.hidden, self.ffn, self.kv, self.M = layers, hidden, ffn, kv, M
@@ -68,7 +69,10 @@ class TernaryStack:
         for l, name, W in stack_weights(layers, hidden, ffn, kv, p_zero, seed):
             if keep_dense:
                 self.dense.append(W)
+            if name == "gu":                    # columns g0,u0,g1,u1,...: a pair-summing step adds gate_j and up_j
+                W = np.ascontiguousarray(W.reshape(2, ffn, W.shape[1]).transpose(1, 0, 2).reshape(2 * ffn, W.shape[1]))
             c0, c1 = shard_range(W.shape[0], rank, world)
+            assert name != "gu" or (c0 % 2 == 0 and c1 % 2 == 0), "pair sums need even shard boundaries"
             w = sp.Weights(W[c0:c1], sp.FMT_U16_V256).upload()
             self.weights.append(w)
             self.stream_bytes += w.stream_bytes
@@ -77,7 +81,8 @@ class TernaryStack:
         # ---- activation buffers (full width on every rank) and step counters in one arena
         n_steps = 4 * layers
         off, cur = {}, 0
-        off["counters"] = cur; cur += n_steps * 8
+        off["counters"] = cur; cur += int(sp.lib.sptmm_seq_shared_bytes(n_steps))      # step counters + row maxima
+        widths["gu"] = ffn                       # stored as pair sums
         widths["out"] = widths["down"]           # the last step's result: never tagged, no reader inside the kernel
         for name in ("qkv", "o", "gu", "down", "out"):
             cur = (cur + 255) & ~255
@@ -101,28 +106,30 @@ class TernaryStack:
 
         # ---- the step list
         steps = []
-        xk = 2 if tagged else 1
+        xk = 2 if tagged else 1                  # a reader of part of a row finds the row's absmax itself
+        xw = 2 if tagged else (3 if row_maxima else 1)    # row_maxima: a reader of a whole row gets its absmax from the producer
         for l in range(layers):
             for i, (name, K, N) in enumerate(shapes):
                 s = 4 * l + i
                 c0, _ = shard_range(N, rank, world)
-                st = {"w": self.weights[s], "dep": s - 1, "ldc": N, "scale_out": self.scales[s]}
+                st = {"w": self.weights[s], "dep": s - 1, "ldc": widths[name], "scale_out": self.scales[s]}
                 if name == "qkv":
                     if l == 0:
                         st.update(X=self.x_in, x_kind=0)
                     else:
-                        st.update(X=mine + off["down"], x_kind=xk, ldx=hidden)
+                        st.update(X=mine + off["down"], x_kind=xw, ldx=hidden)
                 elif name == "o":
                     st.update(X=mine + off["qkv"], x_kind=xk, ldx=widths["qkv"])
                 elif name == "gu":
-                    st.update(X=mine + off["o"], x_kind=xk, ldx=hidden)
+                    st.update(X=mine + off["o"], x_kind=xw, ldx=hidden, c_kind=1)
                 else:
-                    st.update(X=mine + off["gu"], X2=mine + off["gu"] + ffn * 4, x_kind=xk, ldx=2 * ffn, ldx2=2 * ffn)
+                    st.update(X=mine + off["gu"], x_kind=xw, ldx=ffn)
                 dst = "out" if s == n_steps - 1 else name
+                o0 = c0 // 2 if name == "gu" else c0      # where this rank's first output column lands
                 if world > 1:
-                    st["C_peers"] = [b + off[dst] + c0 * 4 for b in bases]
+                    st["C_peers"] = [b + off[dst] + o0 * 4 for b in bases]
                 else:
-                    st["C"] = mine + off[dst] + c0 * 4
+                    st["C"] = mine + off[dst] + o0 * 4
                 steps.append(st)
         counter_peers = [b + off["counters"] for b in bases] if world > 1 else None
         self.seq = sp.Sequence(steps, M=M, counter_peers=counter_peers, rank=rank)
@@ -137,7 +144,7 @@ class TernaryStack:
     def buffer(self, name: str) -> np.ndarray:
         """This rank's copy of an activation buffer (int32, M x width), after a synchronise: the
         last values written to "qkv", "o", "gu" and, as "down", the stack's final result."""
-        width = dict((n, N) for n, _, N in layer_shapes(self.hidden, self.ffn, self.kv))[name]
+        width = self.ffn if name == "gu" else dict((n, N) for n, _, N in layer_shapes(self.hidden, self.ffn, self.kv))[name]
         src = "out" if name == "down" else name
         t = self.arena[self.off[src]: self.off[src] + self.M * width * 4].view(self.torch.int32)
         v = t.cpu().numpy().reshape(self.M, width)
@@ -163,7 +170,8 @@ def reference_forward(dense, layers, hidden, ffn, kv, x_i8, gemv_dense, quant):
         xq, _ = quant(np.ascontiguousarray(out["qkv"][:, :hidden]))
         out["o"] = gemv_dense(xq.reshape(-1), Wo).reshape(M, -1)
         xo, _ = quant(out["o"])
-        out["gu"] = gemv_dense(xo.reshape(-1), Wgu).reshape(M, -1)
-        xg, _ = quant(np.ascontiguousarray(out["gu"][:, :ffn]), np.ascontiguousarray(out["gu"][:, ffn:]))
+        gu = gemv_dense(xo.reshape(-1), Wgu).reshape(M, -1)
+        out["gu"] = gu[:, :ffn] + gu[:, ffn:]                  # the stack stores gate_j + up_j
+        xg, _ = quant(np.ascontiguousarray(out["gu"]))
         out["down"] = gemv_dense(xg.reshape(-1), Wd).reshape(M, -1)
     return out

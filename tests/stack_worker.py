@@ -48,9 +48,9 @@ def gpu_parity():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
     layers, hidden, ffn, kv = 3, 256, 512, 64
-    for M, tagged in ((1, False), (4, False), (1, True), (4, True)):
+    for M, tagged, row_maxima in ((1, False, False), (4, False, True), (1, True, False), (4, True, False)):
         st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, rank=rank, world=world, keep_dense=True,
-                            tagged=tagged)
+                            tagged=tagged, row_maxima=row_maxima)
         x = O.gen_x_i8(M * hidden, 9).reshape(M, hidden)
         st.set_input(x)
         want = S.reference_forward(st.dense, layers, hidden, ffn, kv, x, O.gemv_i8_dense, O.quant_absmax_i8)

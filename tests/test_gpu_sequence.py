@@ -129,6 +129,47 @@ def test_dependent_chain_with_tagged_exchange(M):
         assert len(tags) == 1 and tags[0] != 0
 
 
+@pytest.mark.parametrize("M", [1, 4, 13])
+def test_pair_sums_and_producer_side_row_maxima(M):
+    """c_kind 1: a step stores result[2j] + result[2j+1]; x_kind 3: its reader quantises with the
+    row maxima the producer recorded, in one pass.  Same numbers as the two-source, two-pass chain
+    of test_dependent_chain_with_fused_quantiser; several runs (the maxima are kept per run)."""
+    K1, N1, H, N3 = 512, 384, 320, 200
+    W1 = sp.gen_ternary_iid(K1, N1, 0.4, 1)
+    W2 = sp.gen_ternary_iid(N1, 2 * H, 0.5, 2)                                  # gate | up
+    W2i = np.ascontiguousarray(W2.reshape(2, H, N1).transpose(1, 0, 2).reshape(2 * H, N1))    # g0 u0 g1 u1 ...
+    W3 = sp.gen_ternary_iid(H, N3, 1 / 3, 3)
+    w1, w2, w3 = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (W1, W2i, W3))
+    X = O.gen_x_i8(M * K1, 4)
+    c1 = torch.zeros((M, N1), dtype=torch.int32, device="cuda")
+    c2 = torch.zeros((M, H), dtype=torch.int32, device="cuda")
+    c3 = torch.zeros((M, N3), dtype=torch.int32, device="cuda")
+    s2 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    s3 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    seq = sp.Sequence([
+        {"w": w1, "X": dev(X), "C": c1},
+        {"w": w2, "X": c1, "C": c2, "x_kind": 3, "dep": 0, "scale_out": s2, "c_kind": 1},
+        {"w": w3, "X": c2, "C": c3, "x_kind": 3, "dep": 1, "scale_out": s3},
+    ], M=M)
+    r1 = O.gemv_i8_dense(X, W1)
+    q1, sc1 = O.quant_absmax_i8(r1)
+    r2 = O.gemv_i8_dense(q1.reshape(-1), W2)
+    q2, sc2 = O.quant_absmax_i8(r2[:, :H], r2[:, H:])
+    r3 = O.gemv_i8_dense(q2.reshape(-1), W3)
+    for run in range(4):
+        seq.run()
+        assert seq.status() == 0
+        assert (c1.cpu().numpy() == r1).all()
+        assert (c2.cpu().numpy() == r2[:, :H] + r2[:, H:]).all()
+        assert (c3.cpu().numpy() == r3).all(), "run %d" % run
+        assert (s2.cpu().numpy() == sc1).all() and (s3.cpu().numpy() == sc2).all()
+    with pytest.raises(sp.SptmmError):          # pair sums need an even number of columns
+        sp.Sequence([{"w": sp.Weights(sp.gen_ternary_iid(64, 33, 0.5, 1), sp.FMT_U16_V256).upload(), "X": dev(O.gen_x_i8(64, 1)),
+                      "C": c1, "c_kind": 1}])
+    with pytest.raises(sp.SptmmError):          # x_kind 3 takes one source and needs its producer
+        sp.Sequence([{"w": w1, "X": dev(X), "C": c1}, {"w": w2, "X": c1, "X2": c1, "C": c2, "x_kind": 3, "dep": 0}], M=M)
+
+
 def test_tagged_exchange_is_validated():
     W = sp.gen_ternary_iid(256, 256, 0.5, 0)
     w = sp.Weights(W, sp.FMT_U16_V256).upload()
