@@ -248,7 +248,13 @@ extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dt
     SPTMM_CUDA_TRY(cudaMemcpyAsync(w->stage_x, w->pin_x, xb, cudaMemcpyHostToDevice, st));
     int rc = sptmm_gemv(w, w->stage_x, dtype, M, w->stage_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, replica, st);
     if (rc != SPTMM_OK) return rc;
-    SPTMM_CUDA_TRY(cudaStreamSynchronize(st));
+    // a short busy wait first: for a call of a few microseconds polling the stream returns sooner
+    // than the blocking wait does (replaying copy + kernel as one instantiated graph was tried as
+    // well: no gain at M=1, slower at M=4)
+    cudaError_t qe = cudaErrorNotReady;
+    for (int spin = 0; spin < 20000 && qe == cudaErrorNotReady; spin++) qe = cudaStreamQuery(st);
+    if (qe == cudaErrorNotReady) qe = cudaStreamSynchronize(st);
+    if (qe != cudaSuccess) return fail(SPTMM_ERR_CUDA, "gemv_host: %s", cudaGetErrorString(qe));
     memcpy(C_host, w->pin_c, cb);
     return SPTMM_OK;
 }
