@@ -588,8 +588,14 @@ def large_sweep(args, sp, O, torch, dist, rank, world):
                 oi = torch.zeros(m * Nl, dtype=torch.int32, device="cuda")
                 res[key]["M%d" % m]["i2s_int8_us"] = timed(lambda: wi.gemv(xi, m, oi, sp.I8, stream=st.cuda_stream))
             wi.close()
+            wd = torch.from_numpy(W).cuda().to(torch.float16)          # dense K x N, column-major: 2 bytes per weight
+            for m in (1, 8, 64):
+                xc = torch.from_numpy(np.ascontiguousarray(rng.standard_normal((m, Kl)).astype(np.float16).T)).cuda()
+                oc = torch.zeros(Nl, m, dtype=torch.float32, device="cuda")
+                res[key]["M%d" % m]["cublas_fp16_dense_us"] = timed(
+                    lambda: sp.dense_cublas_gemm_f16(xc, wd, oc, m, Kl, Nl, stream=st.cuda_stream))
+            del wd
         del W
-    res["note"] = "the dense fp16 cuBLAS comparator of this sweep is not built (the library's dense comparator is int8)"
     return res
 
 

@@ -164,6 +164,10 @@ int sptmm_row_split_delta2(const int8_t *X, const uint8_t *W_pos_delta, const ui
  * filled (the reference passes a null W, main.cu:837,863).  Reported reference only. */
 int sptmm_dense_cublas_gemm(const int8_t *X_colmajor, const int8_t *W_dense, int32_t *C_colmajor,
                             uint32_t M, uint32_t K, uint32_t N, void *stream);
+/* The same with fp16 X and W (W holds -1, 0, +1 as fp16), fp32 accumulation and output: the dense
+ * comparator of the large fp16 sweeps.  No counterpart in the reference. */
+int sptmm_dense_cublas_gemm_f16(const void *X_colmajor, const void *W_dense, float *C_colmajor,
+                                uint32_t M, uint32_t K, uint32_t N, void *stream);
 
 /* ---- sequences of matmuls in one launch ----------------------------------------------------- */
 

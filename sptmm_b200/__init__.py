@@ -65,6 +65,7 @@ def _load() -> C.CDLL:
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
+        "sptmm_dense_cublas_gemm_f16": (i32, [vp, vp, vp, u32, u32, u32, vp]),
         "sptmm_seq_create": (i32, [vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_create_shared": (i32, [vp, u32, u32, vp, vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_shared_bytes": (u64, [u32]),
@@ -93,7 +94,7 @@ lib = _load()
 EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host",
-           "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm",
+           "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
@@ -317,3 +318,8 @@ def run_sequence_static(steps, M: int = 1, stream: int = 0, wait: bool = True) -
 
 def dense_cublas_gemm(X_colmajor, W_dense, out_colmajor, M: int, K: int, N: int, stream: int = 0) -> None:
     check(lib.sptmm_dense_cublas_gemm(_ptr(X_colmajor), _ptr(W_dense), _ptr(out_colmajor), M, K, N, stream))
+
+
+def dense_cublas_gemm_f16(X_colmajor, W_dense, out_colmajor, M: int, K: int, N: int, stream: int = 0) -> None:
+    """fp16 x fp16 -> fp32 dense comparator (column-major operands, W holds -1/0/+1 as fp16)."""
+    check(lib.sptmm_dense_cublas_gemm_f16(_ptr(X_colmajor), _ptr(W_dense), _ptr(out_colmajor), M, K, N, stream))

@@ -379,6 +379,21 @@ def test_cublas_comparator():
     assert (out.cpu().numpy().T == O.gemv_i8_dense(X, W)).all()
 
 
+def test_cublas_fp16_comparator_agrees_with_the_ternary_kernel():
+    M, K, N = 8, 2560, 640
+    W = sp.gen_ternary_iid(K, N, 0.5, 3)
+    Xh = np.random.default_rng(4).standard_normal((M, K)).astype(np.float16)
+    out = torch.zeros((N, M), dtype=torch.float32, device="cuda")    # column-major M x N
+    sp.dense_cublas_gemm_f16(dev(np.ascontiguousarray(Xh.T)), dev(W.astype(np.float16)), out, M, K, N)
+    ours = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    sp.Weights(W, sp.FMT_U16_V256).upload().gemv(dev(Xh), M, ours, sp.F16)
+    torch.cuda.synchronize()
+    want = Xh.astype(np.float64) @ W.T.astype(np.float64)
+    scale = np.abs(Xh.astype(np.float64)) @ np.abs(W.T.astype(np.float64))
+    assert (np.abs(out.cpu().numpy().T - want) <= FP16_RTOL * scale + 1e-30).all()
+    assert (np.abs(ours.cpu().numpy() - want) <= FP16_RTOL * scale + 1e-30).all()
+
+
 # ---------------------------------------------------------------- golden fixtures
 
 def _golden_cases():
