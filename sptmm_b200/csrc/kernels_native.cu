@@ -91,6 +91,19 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity)
     return done != 0;
 }
 
+__device__ __forceinline__ uint2 lds64(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+
 template <int DT, int MT, int P, int MINB>
 __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ NativeParams p)
 {
@@ -269,7 +282,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
         // t gathers rows base[t] + off[lane][t] for the first cnt[t] lanes.  Blocks whose steps
         // are all full (every block but a list's last, and steps cut short by a gap of more than
         // 255 rows) take the branch without per-lane tests; idle lanes read the zero row.
-        auto consume_delta = [&](const unsigned char *blk, const uint32_t b) {
+        auto consume_delta = [&](const uint32_t blk, const uint32_t b) {       // blk: shared-space address
             if (b >= bound) {
                 do {
                     if (dirty) { flush(); dirty = false; }
@@ -279,9 +292,9 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             }
             dirty = true;
             acc.reserve(8);
-            const uint2 off = *reinterpret_cast<const uint2 *>(blk + 8 * lane);
-            const uint4 ba = *reinterpret_cast<const uint4 *>(blk + 256), bb = *reinterpret_cast<const uint4 *>(blk + 272);
-            const uint2 cn = *reinterpret_cast<const uint2 *>(blk + 288);
+            const uint2 off = lds64(blk + 8 * lane);
+            const uint4 ba = lds128(blk + 256), bb = lds128(blk + 272);
+            const uint2 cn = lds64(blk + 288);
             if (cn.x == 0x20202020u && cn.y == 0x20202020u) {
                 acc.add(ba.x + __byte_perm(off.x, 0u, 0x4440));
                 acc.add(ba.y + __byte_perm(off.x, 0u, 0x4441));
@@ -302,6 +315,38 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             }
         };
 
+        // two full blocks of one list at once: sixteen independent gathers in flight
+        auto consume_delta2 = [&](const uint32_t blk0, const uint32_t blk1, const uint32_t b) {
+            if (b + 1 < bound) {
+                const uint2 o0 = lds64(blk0 + 8 * lane), o1 = lds64(blk1 + 8 * lane);
+                const uint4 a0 = lds128(blk0 + 256), b0v = lds128(blk0 + 272), a1 = lds128(blk1 + 256), b1v = lds128(blk1 + 272);
+                const uint2 c0v = lds64(blk0 + 288), c1v = lds64(blk1 + 288);
+                if (c0v.x == 0x20202020u && c0v.y == 0x20202020u && c1v.x == 0x20202020u && c1v.y == 0x20202020u) {
+                    dirty = true;
+                    acc.reserve(16);
+                    acc.add(a0.x + __byte_perm(o0.x, 0u, 0x4440));
+                    acc.add(a1.x + __byte_perm(o1.x, 0u, 0x4440));
+                    acc.add(a0.y + __byte_perm(o0.x, 0u, 0x4441));
+                    acc.add(a1.y + __byte_perm(o1.x, 0u, 0x4441));
+                    acc.add(a0.z + __byte_perm(o0.x, 0u, 0x4442));
+                    acc.add(a1.z + __byte_perm(o1.x, 0u, 0x4442));
+                    acc.add(a0.w + __byte_perm(o0.x, 0u, 0x4443));
+                    acc.add(a1.w + __byte_perm(o1.x, 0u, 0x4443));
+                    acc.add(b0v.x + __byte_perm(o0.y, 0u, 0x4440));
+                    acc.add(b1v.x + __byte_perm(o1.y, 0u, 0x4440));
+                    acc.add(b0v.y + __byte_perm(o0.y, 0u, 0x4441));
+                    acc.add(b1v.y + __byte_perm(o1.y, 0u, 0x4441));
+                    acc.add(b0v.z + __byte_perm(o0.y, 0u, 0x4442));
+                    acc.add(b1v.z + __byte_perm(o1.y, 0u, 0x4442));
+                    acc.add(b0v.w + __byte_perm(o0.y, 0u, 0x4443));
+                    acc.add(b1v.w + __byte_perm(o1.y, 0u, 0x4443));
+                    return;
+                }
+            }
+            consume_delta(blk0, b);
+            consume_delta(blk1, b + 1);
+        };
+
         // the blocks that came straight into registers
         if constexpr (!kDelta) {
 #pragma unroll
@@ -319,8 +364,10 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             const uint32_t cnt = min(H, nstaged - r * H);
             const uint32_t bfirst = wb0 + nreg + r * H;
             if constexpr (kDelta) {
-                const unsigned char *half_b = reinterpret_cast<const unsigned char *>(wstage) + (size_t)(r & 1) * H * BB;
-                for (uint32_t j = 0; j < cnt; j++) consume_delta(half_b + (size_t)j * BB, bfirst + j);
+                const uint32_t half_a = wstage_a + (r & 1) * H * BB;
+                uint32_t j = 0;
+                for (; j + 1 < cnt; j += 2) consume_delta2(half_a + j * BB, half_a + (j + 1) * BB, bfirst + j);
+                if (j < cnt) consume_delta(half_a + j * BB, bfirst + j);
             } else {
                 const uint4 *half = wstage + (size_t)(r & 1) * H * 32 + lane;
                 uint32_t j = 0;
