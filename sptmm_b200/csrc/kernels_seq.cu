@@ -188,23 +188,27 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
     auto stale4 = [&](const int4 &v) {
         return ((uint32_t)v.x >> 24) != tag || ((uint32_t)v.y >> 24) != tag || ((uint32_t)v.z >> 24) != tag || ((uint32_t)v.w >> 24) != tag;
     };
-    // rows 4g..4g+3 of one source at piece q; with a tag, reload the stale ones round by round
-    // (the reloads of a round in flight together) until all four are current
-    auto fetch_rows = [&](const int4 *S, uint32_t ld, int g, uint32_t q, int4 (&v)[4]) {
+    // A thread's loads go out a group of GR rows at a time: each group is one round trip to L2, and
+    // the round trips -- not bandwidth -- are what the quantiser costs, so 16-row tiles use groups
+    // of eight rows (32 registers in flight).
+    constexpr int GR = MT == 16 ? 8 : 4;
+    // rows row0..row0+GR-1 of one source at piece q; with a tag, reload the stale ones round by
+    // round (the reloads of a round in flight together) until all are current
+    auto fetch_rows = [&](const int4 *S, uint32_t ld, int row0, uint32_t q, int4 (&v)[GR]) {
 #pragma unroll
-        for (int r = 0; r < 4; r++)
-            v[r] = (uint32_t)(4 * g + r) < M ? __ldcg(S + (size_t)(4 * g + r) * ld + q) : make_int4(0, 0, 0, 0);
+        for (int r = 0; r < GR; r++)
+            v[r] = (uint32_t)(row0 + r) < M ? __ldcg(S + (size_t)(row0 + r) * ld + q) : make_int4(0, 0, 0, 0);
         if (tag) {
             for (uint32_t it = 0; ok; it++) {
                 bool stale = false;
 #pragma unroll
-                for (int r = 0; r < 4; r++)
-                    if ((uint32_t)(4 * g + r) < M && stale4(v[r])) { stale = true; v[r] = ld_fresh4(S + (size_t)(4 * g + r) * ld + q, sys); }
+                for (int r = 0; r < GR; r++)
+                    if ((uint32_t)(row0 + r) < M && stale4(v[r])) { stale = true; v[r] = ld_fresh4(S + (size_t)(row0 + r) * ld + q, sys); }
                 if (!stale) break;
                 if (it >= kPollLimit) ok = false;
             }
 #pragma unroll
-            for (int r = 0; r < 4; r++) v[r] = make_int4(untag(v[r].x), untag(v[r].y), untag(v[r].z), untag(v[r].w));
+            for (int r = 0; r < GR; r++) v[r] = make_int4(untag(v[r].x), untag(v[r].y), untag(v[r].z), untag(v[r].w));
         }
     };
     auto again4 = [&](const int4 *p) {
@@ -224,20 +228,21 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
 #pragma unroll
     for (int m = 0; m < MT; m++) am[m] = 0;
     const uint32_t rot = cta_rotation(quads);
+
     for (uint32_t q0 = tid; q0 < quads; q0 += nt) {
         const uint32_t q = rotated(q0, rot, quads);
 #pragma unroll
-        for (int g = 0; g < MT / 4; g++) {
-            int4 v[4];
-            fetch_rows(A, lda, g, q, v);
+        for (int g = 0; g < MT / GR; g++) {
+            int4 v[GR];
+            fetch_rows(A, lda, GR * g, q, v);
             if (B) {
-                int4 b[4];
-                fetch_rows(B, ldb, g, q, b);
+                int4 b[GR];
+                fetch_rows(B, ldb, GR * g, q, b);
 #pragma unroll
-                for (int r = 0; r < 4; r++) { v[r].x += b[r].x; v[r].y += b[r].y; v[r].z += b[r].z; v[r].w += b[r].w; }
+                for (int r = 0; r < GR; r++) { v[r].x += b[r].x; v[r].y += b[r].y; v[r].z += b[r].z; v[r].w += b[r].w; }
             }
 #pragma unroll
-            for (int r = 0; r < 4; r++) am[4 * g + r] = max(am[4 * g + r], absmax4(v[r]));
+            for (int r = 0; r < GR; r++) am[GR * g + r] = max(am[GR * g + r], absmax4(v[r]));
         }
     }
 #pragma unroll
@@ -262,17 +267,27 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
     for (uint32_t q0 = tid; q0 < quads; q0 += nt) {
         const uint32_t q = rotated(q0, rot, quads);
 #pragma unroll
-        for (int g = 0; g < MT / 4; g++) {
-            int4 v[4];
+        for (int g8 = 0; g8 < MT / GR; g8++) {
+            int4 w[GR];
 #pragma unroll
-            for (int r = 0; r < 4; r++) {
-                const int m = 4 * g + r;
-                v[r] = (uint32_t)m < M ? again4(A + (size_t)m * lda + q) : make_int4(0, 0, 0, 0);
-                if (B && (uint32_t)m < M) {
-                    const int4 b = again4(B + (size_t)m * ldb + q);
-                    v[r].x += b.x; v[r].y += b.y; v[r].z += b.z; v[r].w += b.w;
+            for (int r = 0; r < GR; r++) {
+                const int m = GR * g8 + r;
+                w[r] = (uint32_t)m < M ? again4(A + (size_t)m * lda + q) : make_int4(0, 0, 0, 0);
+            }
+            if (B) {
+#pragma unroll
+                for (int r = 0; r < GR; r++) {
+                    const int m = GR * g8 + r;
+                    if ((uint32_t)m < M) {
+                        const int4 b = again4(B + (size_t)m * ldb + q);
+                        w[r].x += b.x; w[r].y += b.y; w[r].z += b.z; w[r].w += b.w;
+                    }
                 }
             }
+#pragma unroll
+          for (int h = 0; h < GR / 4; h++) {
+            const int g = g8 * (GR / 4) + h;
+            const int4 (&v)[4] = *reinterpret_cast<const int4 (*)[4]>(&w[4 * h]);
             uint32_t o[4];                    // o[i]: rows 4g..4g+3 at k = 4q+i
 #define SPTMM_PACK4(f) ((uint32_t)(quant1(v[0].f, scale[4 * g]) & 0xff) | ((uint32_t)(quant1(v[1].f, scale[4 * g + 1]) & 0xff) << 8) | \
                         ((uint32_t)(quant1(v[2].f, scale[4 * g + 2]) & 0xff) << 16) | ((uint32_t)(quant1(v[3].f, scale[4 * g + 3]) & 0xff) << 24))
@@ -288,6 +303,7 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
                 for (int i = 0; i < 4; i++)
                     *reinterpret_cast<uint32_t *>(xs + ((size_t)q * 4 + i) * MT + 4 * g) = o[i];
             }
+          }
         }
     }
     if (tid < (uint32_t)MT) xs[(size_t)d.K * MT + tid] = 0x80;        // the zero row
