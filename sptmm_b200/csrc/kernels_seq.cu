@@ -681,10 +681,11 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         // L2 lines) hides behind the gathers
         uint32_t nxt = 0;
         if (s + 1 < p.nsteps) nxt = load_step_word(s + 1);
-        if (p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
+        // (TAGGED kernels are the ones that also know row maxima: plain sequences carry neither)
+        if (TAGGED && p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
             p.amax[((p.run_parity ^ 1u) * p.nsteps + s) * 16 + tid] = 0u;
         if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
-        else if (d.x_kind == 3) stage_x_scaled<MT>(xs, d, p.M, p.amax + ((size_t)p.run_parity * p.nsteps + (uint32_t)d.dep) * 16, cta == 0);
+        else if (TAGGED && d.x_kind == 3) stage_x_scaled<MT>(xs, d, p.M, p.amax + ((size_t)p.run_parity * p.nsteps + (uint32_t)d.dep) * 16, cta == 0);
         else {
             bool fresh = failed == 0;          // after a failure nothing waits any more
             const uint32_t tag = (TAGGED && d.x_kind == 2) ? seq_tag(p.run_mod, d.in_tag_m, d.in_tag_j) : 0u;
@@ -811,7 +812,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 else                  // the exchange: straight into every rank's buffer over NVLink (plain peer stores)
                     for (uint32_t r = 0; r < p.n_peers; r++) d.Cp[r][(size_t)m * d.ldc + o0 + j] = wv;
             }
-            if (d.want_amax) {        // every row's largest magnitude, for the x_kind 3 reader: lane m reports row m
+            if (TAGGED && d.want_amax) {        // every row's largest magnitude, for the x_kind 3 reader: lane m reports row m
                 uint32_t mine = 0;
                 for (uint32_t m = 0; m < p.M; m++) {
                     uint32_t mx = 0;
@@ -853,6 +854,7 @@ struct sptmm_seq {
     void *d_trace = nullptr;
     uint32_t n_peers = 0, my_rank = 0;
     bool tagged = false;             // some step reads tagged words: run the kernel variant that knows them
+    bool uses_amax = false;          // some step is x_kind 3: the row-maxima area is in use
     void *counter_peers[kMaxPeers] = {};
 };
 
@@ -944,7 +946,7 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         int rc = SPTMM_OK;
         for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++) {
             desc[s].release = tagged[s] ? 0 : 1;
-            if (steps[s].x_kind == 3) desc[(uint32_t)steps[s].dep].want_amax = 1;
+            if (steps[s].x_kind == 3) { desc[(uint32_t)steps[s].dep].want_amax = 1; q->uses_amax = true; }
             if (tagged[s] && desc[s].c_kind && desc[s].K > 33000)
                 rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u: pair sums over K=%u rows do not fit a tagged word", s, desc[s].K);
             if (steps[s].x_kind != 2 && steps[s].dep >= 0 && tagged[(uint32_t)steps[s].dep])
@@ -1038,7 +1040,9 @@ static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t 
 template <int MT>
 static int seq_launch(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
 {
-    return q->tagged ? seq_launch_as<MT, true>(q, prm, st) : seq_launch_as<MT, false>(q, prm, st);
+    // one kernel variant knows tagged words and row maxima, the other neither (and is smaller, which
+    // shows: 0.7 us per step on the 6912x2560 sequence)
+    return (q->tagged || q->uses_amax) ? seq_launch_as<MT, true>(q, prm, st) : seq_launch_as<MT, false>(q, prm, st);
 }
 
 template <int MT, bool TAGGED>
@@ -1082,9 +1086,10 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     prm.xs_bytes = q->xs_bytes; prm.G = q->G; prm.slot_blocks = q->slot_blocks; prm.one = 1;
     prm.run_mod = (uint32_t)(q->epoch % 255);
     prm.run_parity = (uint32_t)(q->epoch & 1);
+    // the row maxima sit behind the counters; a sequence without x_kind 3 steps never touches them
     for (uint32_t r = 0; r < kMaxPeers; r++)
-        prm.amax_peers[r] = q->counter_peers[r] ? (uint32_t *)((char *)q->counter_peers[r] + (size_t)q->nsteps * 8) : nullptr;
-    prm.amax = (uint32_t *)((char *)prm.counters + (size_t)q->nsteps * 8);
+        prm.amax_peers[r] = q->uses_amax && q->counter_peers[r] ? (uint32_t *)((char *)q->counter_peers[r] + (size_t)q->nsteps * 8) : nullptr;
+    prm.amax = q->uses_amax ? (uint32_t *)((char *)prm.counters + (size_t)q->nsteps * 8) : nullptr;
     cudaStream_t st = (cudaStream_t)stream;
     switch (q->mt) {
         case 1: return seq_launch<1>(q, prm, st);
