@@ -139,9 +139,19 @@ int sptmm_gemv_reduce(const sptmm_weights *w, const void *X, uint32_t dtype, uin
                       void *stream);
 
 /* Same, but X and C are HOST buffers: copies X in, runs, copies C out, waits.  Uses pinned
- * staging owned by the handle (not re-entrant per handle). */
+ * staging owned by the handle (slot 0 of the asynchronous form below; not re-entrant per handle). */
 int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
                     uint32_t flags, uint32_t replica);
+
+/* The host-buffer call in two halves, so that independent calls overlap: _async copies X into the
+ * slot's pinned staging, enqueues the copy to the device and the kernel on the slot's own stream
+ * and returns; _wait blocks until that call is done and copies the result (which the kernel stored
+ * straight into mapped pinned memory) to the C_host given to _async.  Eight slots per handle;
+ * issuing on a busy slot waits for it first.  X_host may be reused as soon as _async returns,
+ * C_host must stay valid until _wait.  One host thread per handle. */
+int sptmm_gemv_host_async(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
+                          uint32_t flags, uint32_t replica, uint32_t slot);
+int sptmm_gemv_host_wait(sptmm_weights *w, uint32_t slot);
 
 /* Raw-pointer forms with the reference's kernel argument convention (X, W_pos, W_neg, C), for a
  * caller that built the reference layouts itself.

@@ -62,6 +62,8 @@ def _load() -> C.CDLL:
         "sptmm_weights_load": (i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
         "sptmm_gemv_reduce": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, vp]),
         "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32, u32]),
+        "sptmm_gemv_host_async": (i32, [vp, vp, u32, u32, vp, u32, u32, u32]),
+        "sptmm_gemv_host_wait": (i32, [vp, u32]),
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
@@ -93,7 +95,7 @@ def _load() -> C.CDLL:
 lib = _load()
 EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
-           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host",
+           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
@@ -206,6 +208,17 @@ class Weights:
             out = np.empty((self.N, M) if flags & C_COLMAJOR else (M, self.N), dtype=_OUT_DTYPE[dtype])
         check(lib.sptmm_gemv_host(self._h, X.ctypes.data, dtype, M, out.ctypes.data, flags, replica))
         return out
+
+    def gemv_host_async(self, X: np.ndarray, out: np.ndarray, slot: int, dtype: int = I8, flags: int = 0, replica: int = 0) -> None:
+        """First half of a host-buffer call on `slot` (0..7): returns once the work is enqueued.  X
+        and out must be C-contiguous arrays of the right dtype; `out` is filled by gemv_host_wait."""
+        M = X.shape[0] if X.ndim == 2 else 1
+        if flags & X_COLMAJOR:
+            M = X.shape[1]
+        check(lib.sptmm_gemv_host_async(self._h, X.ctypes.data, dtype, M, out.ctypes.data, flags, replica, slot))
+
+    def gemv_host_wait(self, slot: int) -> None:
+        check(lib.sptmm_gemv_host_wait(self._h, slot))
 
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:

@@ -43,6 +43,15 @@ const Tune &tune()
     return t;
 }
 
+static void free_host_slot(sptmm_weights::HostSlot &h)
+{
+    if (h.dev_x) cudaFree(h.dev_x);
+    if (h.pin_x) cudaFreeHost(h.pin_x);
+    if (h.pin_c) cudaFreeHost(h.pin_c);
+    if (h.stream) cudaStreamDestroy((cudaStream_t)h.stream);
+    h = sptmm_weights::HostSlot();
+}
+
 static void free_device_side(sptmm_weights *w)
 {
     if (w->device >= 0) {
@@ -52,17 +61,15 @@ static void free_device_side(sptmm_weights *w)
         for (auto &rep : w->dev) for (void *p : rep) if (p) cudaFree(p);
         if (w->plan.d_ctas) cudaFree(w->plan.d_ctas);
         if (w->plan.d_status) cudaFree(w->plan.d_status);
-        if (w->stage_x) cudaFree(w->stage_x);
-        if (w->pin_x) cudaFreeHost(w->pin_x);
-        if (w->pin_c) cudaFreeHost(w->pin_c);
-        if (w->stage_stream) cudaStreamDestroy((cudaStream_t)w->stage_stream);
+        for (auto &h : w->slots) {
+            if (h.busy && h.stream) cudaStreamSynchronize((cudaStream_t)h.stream);
+            free_host_slot(h);
+        }
         cudaSetDevice(cur);
     }
     w->dev.clear();
     w->plan = LaunchPlan();
     w->plan_wide = LaunchPlan();
-    w->stage_x = w->stage_c = w->pin_x = w->pin_c = w->stage_stream = nullptr;
-    w->stage_x_bytes = w->stage_c_bytes = 0;
     w->device = -1;
 }
 
@@ -211,52 +218,76 @@ extern "C" int sptmm_gemv_reduce(const sptmm_weights *w, const void *X, uint32_t
     return launch_native_u16(a);
 }
 
-extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
-                               uint32_t flags, uint32_t replica)
+extern "C" int sptmm_gemv_host_wait(sptmm_weights *w, uint32_t slot)
 {
-    if (!w || !X_host || !C_host) return fail(SPTMM_ERR_INVALID, "gemv_host: null pointer");
-    if (M == 0 || dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv_host: bad M or dtype");
-    if (w->device < 0) return fail(SPTMM_ERR_STATE, "gemv_host: weights are not uploaded");
-    const size_t xb = (size_t)M * w->K * dtype_size(dtype), cb = (size_t)M * w->N * 4;
-    if (!w->stage_stream) {
-        cudaStream_t s;
-        SPTMM_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
-        w->stage_stream = s;
-    }
-    if (xb > w->stage_x_bytes) {
-        if (w->stage_x) cudaFree(w->stage_x);
-        if (w->pin_x) cudaFreeHost(w->pin_x);
-        w->stage_x = w->pin_x = nullptr; w->stage_x_bytes = 0;
-        SPTMM_CUDA_TRY(cudaMalloc(&w->stage_x, xb));
-        SPTMM_CUDA_TRY(cudaMallocHost(&w->pin_x, xb));
-        w->stage_x_bytes = xb;
-    }
-    if (cb > w->stage_c_bytes) {
-        // The result goes straight into mapped pinned host memory: every output element is
-        // written exactly once, so the kernel's own stores replace a device buffer plus a copy
-        // engine operation (stage_c is the device's address of pin_c, not an allocation).
-        if (w->pin_c) cudaFreeHost(w->pin_c);
-        w->stage_c = w->pin_c = nullptr; w->stage_c_bytes = 0;
-        SPTMM_CUDA_TRY(cudaHostAlloc(&w->pin_c, cb, cudaHostAllocMapped));
-        SPTMM_CUDA_TRY(cudaHostGetDevicePointer(&w->stage_c, w->pin_c, 0));
-        w->stage_c_bytes = cb;
-    }
-    cudaStream_t st = (cudaStream_t)w->stage_stream;
-    memcpy(w->pin_x, X_host, xb);
-    // X does go through a device copy: every CTA reads all of it, and reads of host memory are
-    // not cached on the device (measured: 87 us per call with X left in pinned host memory).
-    SPTMM_CUDA_TRY(cudaMemcpyAsync(w->stage_x, w->pin_x, xb, cudaMemcpyHostToDevice, st));
-    int rc = sptmm_gemv(w, w->stage_x, dtype, M, w->stage_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, replica, st);
-    if (rc != SPTMM_OK) return rc;
+    if (!w || slot >= sptmm_weights::kHostSlots) return fail(SPTMM_ERR_INVALID, "gemv_host_wait: bad handle or slot %u", slot);
+    sptmm_weights::HostSlot &h = w->slots[slot];
+    if (!h.busy) return SPTMM_OK;
+    cudaStream_t st = (cudaStream_t)h.stream;
     // a short busy wait first: for a call of a few microseconds polling the stream returns sooner
     // than the blocking wait does (replaying copy + kernel as one instantiated graph was tried as
     // well: no gain at M=1, slower at M=4)
     cudaError_t qe = cudaErrorNotReady;
     for (int spin = 0; spin < 20000 && qe == cudaErrorNotReady; spin++) qe = cudaStreamQuery(st);
     if (qe == cudaErrorNotReady) qe = cudaStreamSynchronize(st);
+    h.busy = false;
     if (qe != cudaSuccess) return fail(SPTMM_ERR_CUDA, "gemv_host: %s", cudaGetErrorString(qe));
-    memcpy(C_host, w->pin_c, cb);
+    memcpy(h.user_c, h.pin_c, h.user_c_bytes);
     return SPTMM_OK;
+}
+
+extern "C" int sptmm_gemv_host_async(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
+                                     uint32_t flags, uint32_t replica, uint32_t slot)
+{
+    if (!w || !X_host || !C_host) return fail(SPTMM_ERR_INVALID, "gemv_host: null pointer");
+    if (M == 0 || dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv_host: bad M or dtype");
+    if (slot >= sptmm_weights::kHostSlots) return fail(SPTMM_ERR_INVALID, "gemv_host: slot %u of %u", slot, sptmm_weights::kHostSlots);
+    if (w->device < 0) return fail(SPTMM_ERR_STATE, "gemv_host: weights are not uploaded");
+    sptmm_weights::HostSlot &h = w->slots[slot];
+    if (h.busy) {                              // the slot's previous call has to deliver its result first
+        const int rc = sptmm_gemv_host_wait(w, slot);
+        if (rc != SPTMM_OK) return rc;
+    }
+    const size_t xb = (size_t)M * w->K * dtype_size(dtype), cb = (size_t)M * w->N * 4;
+    if (!h.stream) {
+        cudaStream_t s;
+        SPTMM_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        h.stream = s;
+    }
+    if (xb > h.x_bytes) {
+        if (h.dev_x) cudaFree(h.dev_x);
+        if (h.pin_x) cudaFreeHost(h.pin_x);
+        h.dev_x = h.pin_x = nullptr; h.x_bytes = 0;
+        SPTMM_CUDA_TRY(cudaMalloc(&h.dev_x, xb));
+        SPTMM_CUDA_TRY(cudaMallocHost(&h.pin_x, xb));
+        h.x_bytes = xb;
+    }
+    if (cb > h.c_bytes) {
+        // The result goes straight into mapped pinned host memory: every output element is
+        // written exactly once, so the kernel's own stores replace a device buffer plus a copy
+        // engine operation (dev_c is the device's address of pin_c, not an allocation).
+        if (h.pin_c) cudaFreeHost(h.pin_c);
+        h.dev_c = h.pin_c = nullptr; h.c_bytes = 0;
+        SPTMM_CUDA_TRY(cudaHostAlloc(&h.pin_c, cb, cudaHostAllocMapped));
+        SPTMM_CUDA_TRY(cudaHostGetDevicePointer(&h.dev_c, h.pin_c, 0));
+        h.c_bytes = cb;
+    }
+    cudaStream_t st = (cudaStream_t)h.stream;
+    memcpy(h.pin_x, X_host, xb);
+    // X does go through a device copy: every CTA reads all of it, and reads of host memory are
+    // not cached on the device (measured: 87 us per call with X left in pinned host memory).
+    SPTMM_CUDA_TRY(cudaMemcpyAsync(h.dev_x, h.pin_x, xb, cudaMemcpyHostToDevice, st));
+    const int rc = sptmm_gemv(w, h.dev_x, dtype, M, h.dev_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, replica, st);
+    if (rc != SPTMM_OK) return rc;
+    h.user_c = C_host; h.user_c_bytes = cb; h.busy = true;
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
+                               uint32_t flags, uint32_t replica)
+{
+    const int rc = sptmm_gemv_host_async(w, X_host, dtype, M, C_host, flags, replica, 0);
+    return rc != SPTMM_OK ? rc : sptmm_gemv_host_wait(w, 0);
 }
 
 extern "C" int sptmm_row_split3_small(const int8_t *X, const uint16_t *W_pos_div, const uint16_t *W_neg_div,

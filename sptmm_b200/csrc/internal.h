@@ -52,10 +52,19 @@ struct sptmm_weights {
     sptmm::LaunchPlan plan;           // small activation tiles: several CTAs per SM (see Tune)
     sptmm::LaunchPlan plan_wide;      // tiles of tens of KB: one 512-thread CTA per SM
 
-    // pinned / device staging for sptmm_gemv_host
-    void *pin_x = nullptr, *pin_c = nullptr, *stage_x = nullptr, *stage_c = nullptr;
-    size_t stage_x_bytes = 0, stage_c_bytes = 0;
-    void *stage_stream = nullptr;
+    // Host-buffer calls (sptmm_gemv_host*): each slot has its own pinned input, mapped pinned
+    // output, device copy of X and stream, so that independent calls overlap.
+    struct HostSlot {
+        void *pin_x = nullptr, *dev_x = nullptr;      // pinned host copy of X and its device copy
+        void *pin_c = nullptr, *dev_c = nullptr;      // mapped pinned result and the device's address of it
+        size_t x_bytes = 0, c_bytes = 0;              // capacities
+        void *stream = nullptr;
+        void *user_c = nullptr;                       // where the pending call's result goes
+        size_t user_c_bytes = 0;
+        bool busy = false;
+    };
+    static constexpr uint32_t kHostSlots = 8;
+    HostSlot slots[kHostSlots];
 };
 
 namespace sptmm {

@@ -243,6 +243,26 @@ def test_gemv_host_roundtrip():
         assert (w.gemv_host(X, sp.I8) == O.gemv_i8_dense(X, W)).all()
 
 
+def test_gemv_host_async_slots_overlap_independent_calls():
+    """Eight slots in flight, every call its own activations; results land in the right buffers,
+    a busy slot is waited for on reuse, and waiting on an idle slot is a no-op."""
+    K, N = 1024, 320
+    W = sp.gen_ternary_iid(K, N, 0.5, 7)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload()
+    calls = 40
+    Xs = [O.gen_x_i8(K, 100 + i).reshape(1, K) for i in range(calls)]
+    outs = [np.full((1, N), -7, dtype=np.int32) for _ in range(calls)]
+    for i in range(calls):
+        w.gemv_host_async(Xs[i], outs[i], slot=i % 8)          # reusing a slot first delivers its previous result
+    for s in range(8):
+        w.gemv_host_wait(s)
+        w.gemv_host_wait(s)
+    for i in range(calls):
+        assert (outs[i] == O.gemv_i8_dense(Xs[i].reshape(-1), W)).all(), i
+    with pytest.raises(sp.SptmmError):
+        w.gemv_host_async(Xs[0], outs[0], slot=8)
+
+
 # ---------------------------------------------------------------- reference layouts
 
 @pytest.mark.parametrize("split", [8, 16, 32])
