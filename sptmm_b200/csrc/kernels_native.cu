@@ -39,13 +39,15 @@ struct NativeParams {
     const uint32_t *blk_off;     // 2N+1
     const void *X;
     void *C;
-    unsigned long long *trace;   // optional: 8 timestamps per CTA for the first 8 CTAs
+    unsigned long long *trace;   // optional: 8 timestamps per CTA for the first trace_ctas CTAs
+    uint32_t trace_ctas;
     uint32_t *status;            // device word: set non-zero if a bounded wait ran out
     uint32_t K, N, M;
     uint32_t max_cols;
     uint32_t x_colmajor, c_colmajor;
     uint32_t uniform_nbl;        // blocks per list when every list has the same count, else 0
     uint32_t one;                // always 1: a multiplier the compiler cannot fold (LaneAcc::add)
+    uint32_t x_early;            // X is final when the kernel starts (no programmatic overlap with its producer)
     // split-K over GPUs: n_peers > 0 makes the epilogue add each column's partial sum to the buffer
     // of the rank that owns the column (columns col_bound[r] .. col_bound[r+1] belong to rank r)
     uint32_t n_peers;
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     const uint32_t wb1 = b0 + (uint32_t)(((uint64_t)nb * (warp + 1)) / nwarps);
     const uint32_t n = wb1 - wb0;
     const uint32_t nbl = p.uniform_nbl;
-    const bool tracing = p.trace != nullptr && blockIdx.x < 8 && blockIdx.y == 0 && tid == 33;   // a lane that issues no fences or copies
+    const bool tracing = p.trace != nullptr && blockIdx.x < p.trace_ctas && blockIdx.y == 0 && tid == 33;   // a lane that issues no fences or copies
     if (tracing) p.trace[blockIdx.x * 8 + 0] = global_ns();
 
     // ---- list boundaries (only needed when lists differ in length): ask for them first, so the
@@ -151,18 +153,41 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
         const uint32_t cnt = min(H, nstaged - r * H);
         bulk_fetch(wstage_a + (r & 1) * H * BB, slice_b + (size_t)(nreg + r * H) * BB, cnt * BB, bar_a + 8 * (r & 1));
     };
-    if (lane == 0 && nrounds) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a + 8) : "memory");
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        issue_round(0);
-        if (nrounds > 1) issue_round(1);
-    }
     uint4 buf[P ? P : 1];
+    auto request_weights = [&]() {
+        if (lane == 0 && nrounds) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a + 8) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_round(0);
+            if (nrounds > 1) issue_round(1);
+        }
 #pragma unroll
-    for (int i = 0; i < P; i++)
-        if ((uint32_t)i < nreg) buf[i] = ld_weights16(slice + (size_t)i * 32 + lane);
+        for (int i = 0; i < P; i++)
+            if ((uint32_t)i < nreg) buf[i] = ld_weights16(slice + (size_t)i * 32 + lane);
+    };
+
+    // ---- A call that does not overlap its producer asks for X FIRST: behind the ~140 KB of weight
+    // requests an SM has in flight the activations would arrive last, and no gather can start
+    // without them.  One row (MT == 1) waits in registers while the weights are requested; wider
+    // tiles are transposed into shared memory before the weights are requested.
+    const uint32_t m0 = blockIdx.y * MT;
+    const uint32_t mv = min((uint32_t)MT, p.M - m0);
+    constexpr uint32_t ES = ActTraits<DT>::size;
+    const unsigned char *xrow = reinterpret_cast<const unsigned char *>(p.X) + (size_t)m0 * p.K * ES;
+    const uint32_t xvec = (p.K * ES) / 16;
+    const bool x_regs = MT == 1 && p.x_early && !p.x_colmajor && (p.K * ES) % 16 == 0 &&
+                        (reinterpret_cast<uintptr_t>(xrow) & 15) == 0 && xvec <= 2 * blockDim.x;
+    const bool x_first = p.x_early && !x_regs;
+    [[maybe_unused]] uint4 xr0 = make_uint4(0, 0, 0, 0), xr1 = make_uint4(0, 0, 0, 0);
+    if constexpr (MT == 1) {
+        if (x_regs) {
+            if (tid < xvec) xr0 = __ldg(reinterpret_cast<const uint4 *>(xrow) + tid);
+            if (tid + blockDim.x < xvec) xr1 = __ldg(reinterpret_cast<const uint4 *>(xrow) + tid + blockDim.x);
+        }
+    }
+    if (!x_first) request_weights();
 
     // ---- shared memory carve-up
     unsigned char *xs = smem;
@@ -185,9 +210,16 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     pdl_wait_prior_grid();
     if (tracing) p.trace[blockIdx.x * 8 + 1] = global_ns();
 
-    const uint32_t m0 = blockIdx.y * MT;
-    const uint32_t mv = min((uint32_t)MT, p.M - m0);
-    stage_x<DT, MT, LaneAcc<DT, MT>::kBiased>(xs, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
+    if (x_regs) {
+        if constexpr (MT == 1) {
+            if (tid < xvec) reinterpret_cast<uint4 *>(xs)[tid] = xr0;
+            if (tid + blockDim.x < xvec) reinterpret_cast<uint4 *>(xs)[tid + blockDim.x] = xr1;
+            if (tid < ES) xs[(size_t)p.K * ES + tid] = 0;                     // the zero row
+        }
+    } else {
+        stage_x<DT, MT, LaneAcc<DT, MT>::kBiased>(xs, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
+    }
+    if (x_first) request_weights();
     __syncthreads();
     if (tracing) p.trace[blockIdx.x * 8 + 2] = global_ns();
 
@@ -548,6 +580,8 @@ static int launch_native(const GemvArgs &a, const bool delta)
     prm.blk_off = (const uint32_t *)a.arrays[1];
     prm.X = a.X; prm.C = a.C;
     prm.trace = g_trace;
+    static const uint32_t trace_ctas = [] { const char *e = getenv("SPTMM_TRACE_CTAS"); return e ? (uint32_t)atoi(e) : 8u; }();
+    prm.trace_ctas = trace_ctas;
     prm.status = (uint32_t *)w.plan.d_status;
     prm.K = w.K; prm.N = w.N; prm.M = a.M;
     prm.max_cols = plan.max_cols;
@@ -555,6 +589,8 @@ static int launch_native(const GemvArgs &a, const bool delta)
     prm.c_colmajor = (a.flags & SPTMM_C_COLMAJOR) ? 1 : 0;
     prm.uniform_nbl = w.uniform_nbl;
     prm.one = 1;
+    static const int x_early_env = [] { const char *e = getenv("SPTMM_X_EARLY"); return e ? atoi(e) : 1; }();
+    prm.x_early = ((a.flags & SPTMM_LAUNCH_PDL) == 0 && x_early_env) ? 1 : 0;
     prm.n_peers = a.n_peers;
     for (uint32_t r = 0; r < 8; r++) {
         prm.Cp[r] = r < a.n_peers ? a.C_peers[r] : nullptr;
