@@ -301,19 +301,38 @@ def run_ours(args):
     e2e_sync_us = (time.perf_counter() - t0) / (e2e_calls // 4) * 1e6
     if not np.array_equal(Ch.reshape(-1), want):
         raise SystemExit("parity failure in the host-buffer call")
-    for i in range(2 * e2e_slots):
-        w.gemv_host_async(Xh2, Chs[i % e2e_slots], i % e2e_slots, sp.I8, replica=i % replicas)
-    for sl in range(e2e_slots):
-        w.gemv_host_wait(sl)
+    e2e_threads = max(1, min(e2e_slots, args.e2e_threads))
+    per_thread = e2e_slots // e2e_threads
+    e2e_slots = per_thread * e2e_threads
+    e2e_calls -= e2e_calls % e2e_threads
+
+    def host_calls(t, n):
+        # one host thread, its own slots: issue the next call while earlier ones are in flight
+        torch.cuda.set_device(local)          # the current device is per host thread
+        mine = [t * per_thread + j for j in range(per_thread)]
+        for i in range(n):
+            sl = mine[i % per_thread]
+            w.gemv_host_async(Xh2, Chs[sl], sl, sp.I8, replica=(i * e2e_threads + t) % replicas)
+        for sl in mine:
+            w.gemv_host_wait(sl)
+
+    def host_round(n):
+        if e2e_threads == 1:
+            host_calls(0, n)
+            return
+        th = [threading.Thread(target=host_calls, args=(t, n // e2e_threads)) for t in range(e2e_threads)]
+        for x in th:
+            x.start()
+        for x in th:
+            x.join()
+
+    host_round(4 * e2e_slots)
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
-    for i in range(e2e_calls):
-        w.gemv_host_async(Xh2, Chs[i % e2e_slots], i % e2e_slots, sp.I8, replica=i % replicas)
-    for sl in range(e2e_slots):
-        w.gemv_host_wait(sl)
+    host_round(e2e_calls)
     e2e_s = time.perf_counter() - t0
-    if not all(np.array_equal(c.reshape(-1), want) for c in Chs):
+    if not all(np.array_equal(c.reshape(-1), want) for c in Chs[:e2e_slots]):
         raise SystemExit("parity failure in the asynchronous host-buffer calls")
     if world > 1:
         t = torch.tensor([e2e_s, e2e_sync_us], dtype=torch.float64, device="cuda")
@@ -439,9 +458,9 @@ def run_ours(args):
                          "peak_kind": peak_kind, "algorithmic_bytes_per_launch": nbytes, "traffic": NCU_TRAFFIC_BYTES},
             "e2e": {"value": e2e_value, "unit": "GB/s", "us_per_call": e2e_us,
                     "h2d_bytes_per_step": M * K * calls, "d2h_bytes_per_step": M * N * 4 * calls,
-                    "calls_timed": e2e_calls, "calls_in_flight": e2e_slots,
+                    "calls_timed": e2e_calls, "calls_in_flight": e2e_slots, "host_threads": e2e_threads,
                     "one_at_a_time_us_per_call": e2e_sync_us,
-                    "how": "sptmm_gemv_host_async/_wait per call: host X -> pinned -> device copy, kernel storing C into mapped pinned host memory, stream poll, copy out"},
+                    "how": "sptmm_gemv_host_async/_wait per call from host_threads threads: host X -> pinned -> device copy, kernel storing C into mapped pinned host memory, stream poll, copy out"},
             "single_stream": single,
             "sequence": seq_info,
             "stack": stack_info,
@@ -629,7 +648,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--calls", type=int, default=1024, help="GEMV calls per step")
     ap.add_argument("--streams", type=int, default=4, help="streams the independent calls of a step are spread over")
-    ap.add_argument("--e2e-slots", type=int, default=2, help="host-buffer calls in flight in the e2e measurement (1..8)")
+    ap.add_argument("--e2e-slots", type=int, default=4, help="host-buffer calls in flight in the e2e measurement (1..8)")
+    ap.add_argument("--e2e-threads", type=int, default=2, help="host threads issuing those calls (each owns slots/threads of them)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -148,7 +148,9 @@ int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32
  * and returns; _wait blocks until that call is done and copies the result (which the kernel stored
  * straight into mapped pinned memory) to the C_host given to _async.  Eight slots per handle;
  * issuing on a busy slot waits for it first.  X_host may be reused as soon as _async returns,
- * C_host must stay valid until _wait.  One host thread per handle. */
+ * C_host must stay valid until _wait.  A slot belongs to one host thread at a time; different
+ * slots of one handle may be driven from different host threads at once (each with the handle's
+ * device current), which is how a host gets past one thread's launch rate. */
 int sptmm_gemv_host_async(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
                           uint32_t flags, uint32_t replica, uint32_t slot);
 int sptmm_gemv_host_wait(sptmm_weights *w, uint32_t slot);

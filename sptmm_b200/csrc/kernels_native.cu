@@ -25,6 +25,7 @@
 // Every wait on an mbarrier is bounded; if one runs out the kernel raises a status word and
 // returns instead of hanging.
 #include <algorithm>
+#include <atomic>
 
 #include "device_common.cuh"
 
@@ -470,14 +471,14 @@ static size_t native_smem(uint32_t K, int rb, int mt, uint32_t max_cols, uint32_
 template <int DT, int MT, int P, int MINB>
 static int launch_one(const NativeParams &prm, dim3 grid, uint32_t threads, size_t smem, bool pdl, cudaStream_t st)
 {
-    static int configured_device = -1;
+    static std::atomic<int> configured_device{-1};     // host threads may launch concurrently
     int dev = 0;
     SPTMM_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_device != dev) {
+    if (configured_device.load(std::memory_order_acquire) != dev) {
         SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_u16_v256<DT, MT, P, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_u16_v256<DT, MT, P, MINB>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                             cudaSharedmemCarveoutMaxShared));
-        configured_device = dev;
+        configured_device.store(dev, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smem; cfg.stream = st;

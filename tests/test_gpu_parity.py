@@ -234,6 +234,56 @@ def test_pdl_chain_respects_data_dependency():
         assert np.allclose(y.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("M", [1, 4, 16])
+@pytest.mark.parametrize("flags", [0, sp.LAUNCH_PDL])
+def test_activation_request_order_both_ways(M, flags):
+    # without the flag a call asks for X before its weights, with it X is read only after the
+    # previous kernel has finished: both orders, every row-tile width, int8 and fp16
+    K, N, S = 2304, 640, 1152
+    W = sp.gen_ternary_fixed(K, N, S)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload(replicas=2)
+    X = O.gen_x_i8(M * K, 5)
+    want = O.gemv_i8_dense(X, W)
+    xd = dev(X)
+    Xf = np.random.default_rng(M).standard_normal((M, K)).astype(np.float16)
+    xf = dev(Xf)
+    want_f = Xf.astype(np.float64) @ W.T.astype(np.float64)
+    scale = np.abs(Xf.astype(np.float64)) @ np.abs(W.T.astype(np.float64))
+    st = torch.cuda.Stream()
+    oi = [torch.zeros(M * N, dtype=torch.int32, device="cuda") for _ in range(4)]
+    of = [torch.zeros(M * N, dtype=torch.float32, device="cuda") for _ in range(4)]
+    with torch.cuda.stream(st):
+        for i in range(4):
+            w.gemv(xd, M, oi[i], sp.I8, flags, replica=i % 2, stream=st.cuda_stream)
+            w.gemv(xf, M, of[i], sp.F16, flags, replica=i % 2, stream=st.cuda_stream)
+    st.synchronize()
+    for i in range(4):
+        assert (oi[i].cpu().numpy().reshape(M, N) == want).all()
+        assert (np.abs(of[i].cpu().numpy().reshape(M, N) - want_f) <= 1e-3 * scale + 1e-6).all()
+
+
+def test_plain_stream_order_chain_reads_fresh_activations():
+    # no programmatic overlap: layer 2 asks for its X first thing, which stream order makes final
+    K = N = 1024
+    W1 = sp.gen_ternary_iid(K, N, 0.9, 11)
+    W2 = sp.gen_ternary_iid(K, N, 0.9, 12)
+    w1 = sp.Weights(W1, sp.FMT_U16_V256).upload()
+    w2 = sp.Weights(W2, sp.FMT_U16_V256).upload()
+    st = torch.cuda.Stream()
+    h = torch.zeros(N, dtype=torch.float32, device="cuda")
+    y = torch.zeros(N, dtype=torch.float32, device="cuda")
+    for seed in range(4):
+        X = np.random.default_rng(seed).standard_normal(K).astype(np.float32)
+        xd = dev(X)
+        w1.gemv(xd, 1, h, sp.F32, 0, stream=st.cuda_stream)
+        w2.gemv(h, 1, y, sp.F32, 0, stream=st.cuda_stream)
+        st.synchronize()
+        h_ref = X.astype(np.float64) @ W1.T.astype(np.float64)
+        y_ref = h.cpu().numpy().astype(np.float64) @ W2.T.astype(np.float64)
+        assert np.allclose(h.cpu().numpy(), h_ref, rtol=1e-4, atol=1e-4)
+        assert np.allclose(y.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-3)
+
+
 def test_gemv_host_roundtrip():
     K, N, S = 6912, 2560, 4096
     W = sp.gen_ternary_fixed(K, N, S)
@@ -261,6 +311,38 @@ def test_gemv_host_async_slots_overlap_independent_calls():
         assert (outs[i] == O.gemv_i8_dense(Xs[i].reshape(-1), W)).all(), i
     with pytest.raises(sp.SptmmError):
         w.gemv_host_async(Xs[0], outs[0], slot=8)
+
+
+def test_gemv_host_slots_from_two_host_threads():
+    """Two host threads, each with its own pair of slots, issue calls at the same time."""
+    import threading
+    K, N = 2048, 512
+    W = sp.gen_ternary_iid(K, N, 0.5, 9)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload()
+    calls = 60
+    Xs = [[O.gen_x_i8(K, 1000 * t + i).reshape(1, K) for i in range(calls)] for t in range(2)]
+    outs = [[np.full((1, N), -7, dtype=np.int32) for _ in range(calls)] for t in range(2)]
+    errors = []
+
+    def work(t):
+        try:
+            torch.cuda.set_device(0)
+            for i in range(calls):
+                w.gemv_host_async(Xs[t][i], outs[t][i], slot=2 * t + i % 2)
+            w.gemv_host_wait(2 * t)
+            w.gemv_host_wait(2 * t + 1)
+        except Exception as e:      # surfaced in the main thread below
+            errors.append(e)
+
+    th = [threading.Thread(target=work, args=(t,)) for t in range(2)]
+    for x in th:
+        x.start()
+    for x in th:
+        x.join()
+    assert not errors, errors
+    for t in range(2):
+        for i in range(calls):
+            assert (outs[t][i] == O.gemv_i8_dense(Xs[t][i].reshape(-1), W)).all(), (t, i)
 
 
 # ---------------------------------------------------------------- reference layouts
