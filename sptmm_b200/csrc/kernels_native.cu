@@ -569,8 +569,14 @@ static int launch_native(const GemvArgs &a, const bool delta)
     const uint32_t pd = delta ? 0u : (uint32_t)prefetch_depth(mt, wide);
     const uint32_t per_warp = (plan.max_cta_blocks + nwarps - 1) / nwarps + 1;
     const uint32_t need = per_warp > pd ? per_warp - pd : 0;
+    // Beside a tile of more than 16 KB a smaller staging area pays: three such CTAs fit an SM instead
+    // of two, so a neighbouring call's CTAs stream while this one gathers (6912x2560, 4 streams /
+    // 1 stream: M=4 int8 6.1 -> 5.8 / 9.8 -> 8.5 us, M=1 fp32 5.9 -> 4.7 / 8.7 -> 7.6 us; the
+    // one-row int8 tile wants the larger area: 3.35 against 3.5 us; 14 KB tiles are indifferent).
+    static const size_t stage_big_kb = [] { const char *e = getenv("SPTMM_STAGE_BIG_KB"); return e ? (size_t)atoi(e) : (size_t)30; }();
+    const size_t stage_kb = xs_bytes(w.K, mt * es) > 16 * 1024 ? std::min((size_t)tune().smem_kb, stage_big_kb) : (size_t)tune().smem_kb;
     const size_t budget = wide ? (size_t)225 * 1024
-                               : std::min(base_smem + std::max((size_t)tune().smem_kb * 1024, min_stage), (size_t)225 * 1024);
+                               : std::min(base_smem + std::max(stage_kb * 1024, min_stage), (size_t)225 * 1024);
     const uint32_t room = (uint32_t)((budget - base_smem - 256) / ((size_t)nwarps * bb));   // blocks per warp
     const uint32_t half = need == 0 ? 0 : (need <= room ? need : std::max(1u, room / 2));
     const uint32_t halves = need <= room ? 1 : 2;
