@@ -287,7 +287,7 @@ def run_ours(args):
     # in flight at once (sptmm_gemv_host_async / _wait); `one_at_a_time` is the same through the
     # blocking call.
     e2e_calls = max(64, min(4000, total_calls // 4))
-    e2e_slots = max(1, min(8, args.e2e_slots))
+    e2e_slots = max(1, min(16, args.e2e_slots))
     Xh2 = np.ascontiguousarray(Xh.reshape(M, K))
     Chs = [np.empty((M, N), dtype=np.int32) for _ in range(e2e_slots)]
     Ch = np.empty((M, N), dtype=np.int32)
@@ -301,7 +301,8 @@ def run_ours(args):
     e2e_sync_us = (time.perf_counter() - t0) / (e2e_calls // 4) * 1e6
     if not np.array_equal(Ch.reshape(-1), want):
         raise SystemExit("parity failure in the host-buffer call")
-    e2e_threads = max(1, min(e2e_slots, args.e2e_threads))
+    # at most one issuing thread per host core this rank can count on
+    e2e_threads = max(1, min(e2e_slots, args.e2e_threads, (os.cpu_count() or 1) // world))
     per_thread = e2e_slots // e2e_threads
     e2e_slots = per_thread * e2e_threads
     e2e_calls -= e2e_calls % e2e_threads
@@ -309,12 +310,13 @@ def run_ours(args):
     def host_calls(t, n):
         # one host thread, its own slots: issue the next call while earlier ones are in flight
         torch.cuda.set_device(local)          # the current device is per host thread
-        mine = [t * per_thread + j for j in range(per_thread)]
-        for i in range(n):
-            sl = mine[i % per_thread]
-            w.gemv_host_async(Xh2, Chs[sl], sl, sp.I8, replica=(i * e2e_threads + t) % replicas)
-        for sl in mine:
-            w.gemv_host_wait(sl)
+        # its list of n independent requests goes to the library in one sptmm_gemv_host_batch call
+        # (every request still copies its own X in and gets its own result out)
+        s0 = t * per_thread
+        xa = Xh2.ctypes.data
+        ca = [Chs[s0 + j].ctypes.data for j in range(per_thread)]
+        w.gemv_host_batch([xa] * n, [ca[i % per_thread] for i in range(n)],
+                          [(i * e2e_threads + t) % replicas for i in range(n)], sp.I8, 0, s0, per_thread, M=M)
 
     def host_round(n):
         if e2e_threads == 1:
@@ -460,7 +462,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": M * K * calls, "d2h_bytes_per_step": M * N * 4 * calls,
                     "calls_timed": e2e_calls, "calls_in_flight": e2e_slots, "host_threads": e2e_threads,
                     "one_at_a_time_us_per_call": e2e_sync_us,
-                    "how": "sptmm_gemv_host_async/_wait per call from host_threads threads: host X -> pinned -> device copy, kernel storing C into mapped pinned host memory, stream poll, copy out"},
+                    "how": "sptmm_gemv_host_batch (a list of independent calls, each through sptmm_gemv_host_async/_wait) from host_threads threads: host X -> pinned -> device copy, kernel storing C into mapped pinned host memory, stream poll, copy out"},
             "single_stream": single,
             "sequence": seq_info,
             "stack": stack_info,
@@ -648,8 +650,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--calls", type=int, default=1024, help="GEMV calls per step")
     ap.add_argument("--streams", type=int, default=4, help="streams the independent calls of a step are spread over")
-    ap.add_argument("--e2e-slots", type=int, default=4, help="host-buffer calls in flight in the e2e measurement (1..8)")
-    ap.add_argument("--e2e-threads", type=int, default=2, help="host threads issuing those calls (each owns slots/threads of them)")
+    ap.add_argument("--e2e-slots", type=int, default=16, help="host-buffer calls in flight in the e2e measurement (1..16)")
+    ap.add_argument("--e2e-threads", type=int, default=4, help="host threads issuing those calls (each owns slots/threads of them)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

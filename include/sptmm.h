@@ -146,7 +146,7 @@ int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32
 /* The host-buffer call in two halves, so that independent calls overlap: _async copies X into the
  * slot's pinned staging, enqueues the copy to the device and the kernel on the slot's own stream
  * and returns; _wait blocks until that call is done and copies the result (which the kernel stored
- * straight into mapped pinned memory) to the C_host given to _async.  Eight slots per handle;
+ * straight into mapped pinned memory) to the C_host given to _async.  Sixteen slots per handle;
  * issuing on a busy slot waits for it first.  X_host may be reused as soon as _async returns,
  * C_host must stay valid until _wait.  A slot belongs to one host thread at a time; different
  * slots of one handle may be driven from different host threads at once (each with the handle's
@@ -154,6 +154,15 @@ int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32
 int sptmm_gemv_host_async(sptmm_weights *w, const void *X_host, uint32_t dtype, uint32_t M, void *C_host,
                           uint32_t flags, uint32_t replica, uint32_t slot);
 int sptmm_gemv_host_wait(sptmm_weights *w, uint32_t slot);
+
+/* A list of n independent host-buffer calls on one handle: call i takes X_hosts[i] (M rows each),
+ * delivers to C_hosts[i] and streams weight copy replicas[i] (copy 0 when replicas is null).  The
+ * calls go round the slots slot0 .. slot0+nslots-1 (nslots of them in flight at once) and all have
+ * delivered when the function returns; on an error the calls issued so far are waited for and the
+ * first error is returned.  Two host threads may each run a list on their own slots. */
+int sptmm_gemv_host_batch(sptmm_weights *w, uint32_t n, const void *const *X_hosts, void *const *C_hosts,
+                          const uint32_t *replicas, uint32_t dtype, uint32_t M, uint32_t flags,
+                          uint32_t slot0, uint32_t nslots);
 
 /* Raw-pointer forms with the reference's kernel argument convention (X, W_pos, W_neg, C), for a
  * caller that built the reference layouts itself.

@@ -64,6 +64,7 @@ def _load() -> C.CDLL:
         "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32, u32]),
         "sptmm_gemv_host_async": (i32, [vp, vp, u32, u32, vp, u32, u32, u32]),
         "sptmm_gemv_host_wait": (i32, [vp, u32]),
+        "sptmm_gemv_host_batch": (i32, [vp, u32, vp, vp, vp, u32, u32, u32, u32, u32]),
         "sptmm_row_split3_small": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_row_split_delta2": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, vp]),
         "sptmm_dense_cublas_gemm": (i32, [vp, vp, vp, u32, u32, u32, vp]),
@@ -95,7 +96,7 @@ def _load() -> C.CDLL:
 lib = _load()
 EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
-           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait",
+           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait", "sptmm_gemv_host_batch",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
            "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
@@ -210,7 +211,7 @@ class Weights:
         return out
 
     def gemv_host_async(self, X: np.ndarray, out: np.ndarray, slot: int, dtype: int = I8, flags: int = 0, replica: int = 0) -> None:
-        """First half of a host-buffer call on `slot` (0..7): returns once the work is enqueued.  X
+        """First half of a host-buffer call on `slot` (0..15): returns once the work is enqueued.  X
         and out must be C-contiguous arrays of the right dtype; `out` is filled by gemv_host_wait."""
         M = X.shape[0] if X.ndim == 2 else 1
         if flags & X_COLMAJOR:
@@ -219,6 +220,25 @@ class Weights:
 
     def gemv_host_wait(self, slot: int) -> None:
         check(lib.sptmm_gemv_host_wait(self._h, slot))
+
+    def gemv_host_batch(self, Xs, outs, replicas=None, dtype: int = I8, flags: int = 0, slot0: int = 0, nslots: int = 4,
+                        M: Optional[int] = None) -> None:
+        """A list of independent host-buffer calls (Xs[i] -> outs[i], weight copy replicas[i]) kept
+        `nslots` at a time in flight on slots slot0..; returns when all have delivered.  Entries are
+        C-contiguous numpy arrays, or host addresses (then M must be given)."""
+        n = len(Xs)
+        if len(outs) != n or (replicas is not None and len(replicas) != n):
+            raise ValueError("gemv_host_batch: list lengths differ")
+        if n == 0:
+            return
+        if M is None:
+            M = Xs[0].shape[0] if Xs[0].ndim == 2 else 1
+            if flags & X_COLMAJOR:
+                M = Xs[0].shape[1]
+        xp = (C.c_void_p * n)(*[_ptr(x) for x in Xs])
+        cp = (C.c_void_p * n)(*[_ptr(o) for o in outs])
+        rp = (C.c_uint32 * n)(*replicas) if replicas is not None else None
+        check(lib.sptmm_gemv_host_batch(self._h, n, xp, cp, rp, dtype, M, flags, slot0, nslots))
 
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:

@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <string>
 
 #include "device_common.cuh"
 
@@ -291,6 +292,24 @@ extern "C" int sptmm_gemv_host(sptmm_weights *w, const void *X_host, uint32_t dt
 {
     const int rc = sptmm_gemv_host_async(w, X_host, dtype, M, C_host, flags, replica, 0);
     return rc != SPTMM_OK ? rc : sptmm_gemv_host_wait(w, 0);
+}
+
+extern "C" int sptmm_gemv_host_batch(sptmm_weights *w, uint32_t n, const void *const *X_hosts, void *const *C_hosts,
+                                     const uint32_t *replicas, uint32_t dtype, uint32_t M, uint32_t flags,
+                                     uint32_t slot0, uint32_t nslots)
+{
+    if (!w || (n && (!X_hosts || !C_hosts))) return fail(SPTMM_ERR_INVALID, "gemv_host_batch: null pointer");
+    if (nslots == 0 || slot0 >= sptmm_weights::kHostSlots || nslots > sptmm_weights::kHostSlots - slot0)
+        return fail(SPTMM_ERR_INVALID, "gemv_host_batch: slots %u..%u of %u", slot0, slot0 + nslots, sptmm_weights::kHostSlots);
+    int rc = SPTMM_OK;
+    for (uint32_t i = 0; i < n && rc == SPTMM_OK; i++)
+        rc = sptmm_gemv_host_async(w, X_hosts[i], dtype, M, C_hosts[i], flags, replicas ? replicas[i] : 0, slot0 + i % nslots);
+    std::string first_error = rc != SPTMM_OK ? sptmm_last_error() : "";
+    for (uint32_t s = 0; s < nslots; s++) {
+        const int wrc = sptmm_gemv_host_wait(w, slot0 + s);
+        if (rc == SPTMM_OK && wrc != SPTMM_OK) { rc = wrc; first_error = sptmm_last_error(); }
+    }
+    return rc == SPTMM_OK ? SPTMM_OK : fail(rc, "%s", first_error.c_str());
 }
 
 extern "C" int sptmm_row_split3_small(const int8_t *X, const uint16_t *W_pos_div, const uint16_t *W_neg_div,

@@ -63,7 +63,7 @@ struct sptmm_weights {
         size_t user_c_bytes = 0;
         bool busy = false;
     };
-    static constexpr uint32_t kHostSlots = 8;
+    static constexpr uint32_t kHostSlots = 16;
     HostSlot slots[kHostSlots];
 };
 

@@ -294,7 +294,7 @@ def test_gemv_host_roundtrip():
 
 
 def test_gemv_host_async_slots_overlap_independent_calls():
-    """Eight slots in flight, every call its own activations; results land in the right buffers,
+    """Sixteen slots in flight, every call its own activations; results land in the right buffers,
     a busy slot is waited for on reuse, and waiting on an idle slot is a no-op."""
     K, N = 1024, 320
     W = sp.gen_ternary_iid(K, N, 0.5, 7)
@@ -303,14 +303,35 @@ def test_gemv_host_async_slots_overlap_independent_calls():
     Xs = [O.gen_x_i8(K, 100 + i).reshape(1, K) for i in range(calls)]
     outs = [np.full((1, N), -7, dtype=np.int32) for _ in range(calls)]
     for i in range(calls):
-        w.gemv_host_async(Xs[i], outs[i], slot=i % 8)          # reusing a slot first delivers its previous result
-    for s in range(8):
+        w.gemv_host_async(Xs[i], outs[i], slot=i % 16)         # reusing a slot first delivers its previous result
+    for s in range(16):
         w.gemv_host_wait(s)
         w.gemv_host_wait(s)
     for i in range(calls):
         assert (outs[i] == O.gemv_i8_dense(Xs[i].reshape(-1), W)).all(), i
     with pytest.raises(sp.SptmmError):
-        w.gemv_host_async(Xs[0], outs[0], slot=8)
+        w.gemv_host_async(Xs[0], outs[0], slot=16)
+
+
+def test_gemv_host_batch_delivers_every_call():
+    K, N = 1536, 384
+    W = sp.gen_ternary_iid(K, N, 0.4, 21)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload(replicas=3)
+    n = 25
+    for M in (1, 3):
+        Xs = [O.gen_x_i8(M * K, 300 + i).reshape(M, K) for i in range(n)]
+        outs = [np.full((M, N), -7, dtype=np.int32) for _ in range(n)]
+        w.gemv_host_batch(Xs, outs, [i % 3 for i in range(n)], slot0=2, nslots=3)
+        for i in range(n):
+            assert (outs[i] == O.gemv_i8_dense(Xs[i].reshape(-1), W)).all(), (M, i)
+    w.gemv_host_batch([], [])
+    with pytest.raises(sp.SptmmError):
+        w.gemv_host_batch(Xs, outs, None, slot0=14, nslots=4)       # slots 14..17 of 16
+    with pytest.raises(sp.SptmmError):
+        w.gemv_host_batch(Xs[:3], outs[:3], [0, 1, 9], nslots=2)    # no weight copy 9
+    outs2 = [np.zeros((M, N), dtype=np.int32) for _ in range(2)]
+    w.gemv_host_batch(Xs[:2], outs2, None, nslots=2)                # the handle is usable after an error
+    assert (outs2[1] == O.gemv_i8_dense(Xs[1].reshape(-1), W)).all()
 
 
 def test_gemv_host_slots_from_two_host_threads():
