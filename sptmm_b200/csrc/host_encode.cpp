@@ -162,12 +162,13 @@ static void encode_delta_div256(const Lists &L, sptmm_weights &w, uint32_t cap)
 // left empty fall back to r = l (mod 16), then (mod 8), then to the smallest unused row.  Every
 // choice must also keep the step conflict-free for RB = 1: two rows of a step may share a bank
 // ((r/4) mod 32) only if they share the word.  Measured on the reference generator's lists
-// (K=6912, 2048 entries): 1.07 / 2.0 / 3.0 / 4.8 cycles per step at RB = 1 / 4 / 8 / 16.
+// (K=6912, 2048 entries): 1.10 / 1.46 / 2.56 / 4.6 cycles per step at RB = 1 / 4 / 8 / 16 (a
+// window of 192 entries gave 1.07 / 2.0 / 3.0 / 4.8; beyond 768 nothing changes).
 // `rows` is ascending; `out` receives the same rows, 32 per step, in step order; a step's unused
 // lanes (possible only in the last steps of a list) hold `pad`.
 static void bank_order(const std::vector<uint16_t> &rows, uint16_t pad, std::vector<uint16_t> &out)
 {
-    constexpr size_t kWindow = 192;
+    constexpr size_t kWindow = 768;
     const size_t n = rows.size();
     out.clear();
     out.reserve((n + 31) / 32 * 32);

@@ -168,7 +168,7 @@ def test_v256_entry_order_avoids_bank_conflicts():
     steps = idx.view(np.uint16).reshape(-1, 32, 8).transpose(0, 2, 1).reshape(-1, 32)     # (step, lane)
     steps = steps[(steps != K).all(axis=1)]
     mean = {rb: np.mean([_bank_cycles(s, rb) for s in steps]) for rb in (1, 4, 8, 16)}
-    assert mean[1] < 1.15 and mean[4] < 2.3 and mean[8] < 3.4 and mean[16] < 5.3, mean
+    assert mean[1] < 1.15 and mean[4] < 1.7 and mean[8] < 2.9 and mean[16] < 5.0, mean
     again = sp.Weights(W, sp.FMT_U16_V256).array(0)[1]
     assert (again == idx).all()                                      # deterministic
 
