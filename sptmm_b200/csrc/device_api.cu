@@ -227,7 +227,9 @@ extern "C" int sptmm_gemv_host_wait(sptmm_weights *w, uint32_t slot)
     cudaStream_t st = (cudaStream_t)h.stream;
     // a short busy wait first: for a call of a few microseconds polling the stream returns sooner
     // than the blocking wait does (replaying copy + kernel as one instantiated graph was tried as
-    // well: no gain at M=1, slower at M=4)
+    // well: no gain at M=1, slower at M=4; so was a completion word in pinned host memory, stored
+    // by the kernel's last CTA behind system-wide fences and polled here without driver calls:
+    // 31 us against 28 us per blocking call, 6.8 us against 4.7 us with sixteen calls in flight)
     cudaError_t qe = cudaErrorNotReady;
     for (int spin = 0; spin < 20000 && qe == cudaErrorNotReady; spin++) qe = cudaStreamQuery(st);
     if (qe == cudaErrorNotReady) qe = cudaStreamSynchronize(st);
