@@ -14,7 +14,9 @@
 // with bulk copies (cp.async.bulk, completion on an mbarrier) into a warp-private, double-
 // buffered staging area in shared memory.  Only then does it wait for the previous kernel in
 // the stream (programmatic dependent launch); with two such CTAs resident per SM, DRAM streams
-// this matrix while the previous kernel is still gathering.
+// this matrix while the previous kernel is still gathering.  A call launched without that
+// overlap knows its activations are final at entry and asks for them BEFORE the weights (behind
+// the weight requests they would arrive last, and no gather can start without them).
 // The activation tile sits transposed in shared memory, so one gather serves MT rows of X and
 // the index stream is read once for up to 16 rows.  Nothing is multiplied.
 //
