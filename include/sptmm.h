@@ -123,6 +123,31 @@ int sptmm_weights_load(const char *path, sptmm_weights **out);
 int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M, void *C,
                uint32_t flags, uint32_t replica, void *stream);
 
+/* The steps either side of the matmul in a quantised layer; the reference has neither (its
+ * activations start as int8, main.cu:787-797, and its results stay raw int32, main.cu:591-593).
+ *
+ * sptmm_quantize_absmax: int32 rows -> int8 with one scale per row,
+ *     q = clamp(rint(v * (127 / absmax)), -127, 127),  scale[m] = absmax / 127   (fp32 throughout;
+ *     a row of zeros gives zeros and scale 0).
+ *   X: device int32; element (m, k) at X[m*ldx + k] (ldx 0 = the row length), or, with shard > 0,
+ *   where an all-gather of per-rank column shards leaves it: rank r's M x shard block after rank
+ *   r-1's.  pair != 0: the value quantised is X(m, 2k) + X(m, 2k+1) (a fused gate | up output with
+ *   its columns interleaved).  Xq: device int8, M x K row-major.  scale: device float[M] or NULL.
+ * sptmm_gemv_scaled: the matmul on int8 activations with the de-quantisation fused into its
+ *   epilogue: C (device float, M x N) = float(sum) * (row_scale[m] * w_scale); row_scale is a device
+ *   float[M] (NULL = 1), e.g. the scale sptmm_quantize_absmax wrote; native formats only. */
+int sptmm_quantize_absmax(const int32_t *X, uint32_t M, uint32_t K, uint32_t ldx, uint32_t shard, uint32_t pair,
+                          int8_t *Xq, float *scale, uint32_t flags, void *stream);
+int sptmm_gemv_scaled(const sptmm_weights *w, const int8_t *X, uint32_t M, float *C, const float *row_scale,
+                      float w_scale, uint32_t flags, uint32_t replica, void *stream);
+
+/* The kernels behind sptmm_gemv bound every wait they make (on a bulk copy's barrier); if one runs
+ * out the kernel stores a non-zero word in device memory and finishes with whatever sums it has
+ * (the reference's kernels have no waits and no such word; main.cu:556-594).  This waits for the
+ * device and reads that word: 0 = every call on this handle since upload completed normally.
+ * The host-buffer calls below check it by themselves and return SPTMM_ERR_STATE. */
+int sptmm_gemv_status(const sptmm_weights *w, uint32_t *status);
+
 /* Split-K across the GPUs of one node: the matmul fused with the reduce-scatter of its partial
  * sums.  No counterpart in the reference (single GPU).  Every rank holds the rows k0..k1 of W
  * (encoded as a (k1-k0) x N matrix, native u16 format) and the matching slice of X, and calls this
@@ -219,7 +244,25 @@ typedef struct sptmm_seq_step {
                                 (all columns, all ranks' shards, ldx = that step's ldc).  The
                                 producing step then also records every row's largest magnitude
                                 while it stores its results, and this step quantises in one pass
-                                over X instead of two (absmax first, values second).             */
+                                over X instead of two (absmax first, values second).
+                                4: as 1 with no X2, but the PRODUCING step `dep` does the quantising:
+                                X names the first of the K columns inside that step's output (any
+                                column range of it), every CTA of that step publishes the row maxima
+                                of its own columns, and once it knows the rows' maxima over the
+                                whole range it rounds its own columns and stores them as int8 --
+                                three rows and a tag to a 32-bit word -- where this step picks them
+                                up.  Readers then fetch M*K bytes instead of quantising M*K int32
+                                each, which is what pays from a few rows upward (and across GPUs,
+                                where every rank's kernel stores its columns into every rank's
+                                copy).  The producer still stores its int32 results as usual.
+                                All steps that read one producer this way must read the same range.
+                                5: as 2 (tagged words in the output of step `dep`, no X2), with the
+                                "settled" hand-over: each word is watched by ONE CTA per GPU instead
+                                of by all of them (every CTA owns K/CTAs columns), the CTAs of a GPU
+                                meet at a local counter once their columns have arrived, and --
+                                for two rows or more -- each CTA quantises only its own columns
+                                into a local int8 tile that all CTAs then fetch with one bulk copy.
+                                Nothing but the producer's tagged words crosses NVLink.            */
     const void *X;           /* device, M rows of K elements, row stride ldx (0 = K)              */
     const void *X2;          /* optional second int32 source, row stride ldx2 (0 = K)             */
     void *C;                 /* device int32, M rows of N, row stride ldc (0 = N)                 */
@@ -248,10 +291,13 @@ int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, 
  *    pointer valid in THIS process, e.g. from CUDA IPC / symmetric memory; p = own rank too).
  *    Each points at column 0 of this rank's shard inside the full-width row (stride ldc).
  *  - counter_peers[p]: rank p's synchronisation area of sptmm_seq_shared_bytes(n_steps) bytes
- *    (step counters, then the row maxima of x_kind 3), zeroed once before first use,
- *    peer-mapped likewise.  All ranks must create the same sequence and run it equally often.
+ *    (step counters, then the row maxima of x_kind 3; sptmm_seq_shared_bytes_for() bytes when
+ *    there are x_kind 4 steps), zeroed once before first use, peer-mapped likewise.  All ranks must create the same sequence and run it equally often.
  * steps[].C is ignored when n_peers > 0. */
 uint64_t sptmm_seq_shared_bytes(uint32_t n_steps);
+/* The same for a sequence with x_kind 4 steps, whose producers keep their row maxima and packed
+ * int8 outputs in that area as well: the size depends on the steps and on M (0 on bad arguments). */
+uint64_t sptmm_seq_shared_bytes_for(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M);
 int sptmm_seq_create_shared(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M,
                             void *const *C_peers, void *const *counter_peers, uint32_t n_peers,
                             uint32_t my_rank, sptmm_seq **out);
@@ -269,8 +315,10 @@ int sptmm_seq_status(sptmm_seq *seq, uint32_t *status, uint64_t *stream_bytes);
  *  - steps / M / stream as for sptmm_seq_create + sptmm_seq_run; weights must already be uploaded
  *    (that upload allocates; this call does not).  More than 16 steps, or a device with more than
  *    256 SMs, is refused with SPTMM_ERR_INVALID / SPTMM_ERR_UNSUPPORTED.
- *  - The first call on a device looks the array's device address up and sets kernel attributes;
- *    make that first call outside any stream capture.
+ *  - The first call on a device looks the array's device address up and sets kernel attributes
+ *    (host threads making first calls at the same time are serialised).  Every call copies its
+ *    step tables from host memory that dies with the call, so a stream that is being captured
+ *    into a graph is refused with SPTMM_ERR_STATE.
  *  - All calls share the one array and it keeps the previous call's contents (the counters and the
  *    status word are cleared at every call): two calls whose kernels overlap on the GPU race.
  *    Serialise them on one stream.
@@ -279,16 +327,7 @@ int sptmm_seq_status(sptmm_seq *seq, uint32_t *status, uint64_t *stream_bytes);
 int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, void *stream,
                          uint32_t *status_out);
 
-/* Diagnostics: 4 x uint64 timestamps per step (first 256 steps) from CTA 0; NULL = off. */
-int sptmm_seq_set_trace(sptmm_seq *seq, void *dev_ptr);
 int sptmm_seq_free(sptmm_seq *seq);
-
-/* ---- diagnostics ---------------------------------------------------------------------------- */
-
-/* No counterpart in the reference.  While `dev_ptr` (64 x uint64 of device memory) is set, the
- * native kernel's first 8 CTAs record %globaltimer at entry, after the wait on the previous
- * kernel, after staging X, after the gather loop and at exit.  NULL switches it off. */
-int sptmm_set_trace_buffer(void *dev_ptr);
 
 /* ---- small device helpers so a C caller needs no CUDA headers ------------------------------ */
 int sptmm_device_count(int *count);

@@ -17,7 +17,10 @@ from typing import Optional
 import numpy as np
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libsptmm.so")
+# SPTMM_B200_TUNING=1 loads the tuning build (build.py --tuning: kernel timelines, overridable launch
+# constants) instead of the product library; only measurement scripts set it.
+TUNING = os.environ.get("SPTMM_B200_TUNING", "") not in ("", "0")
+LIB_PATH = os.path.join(_PKG, "libsptmm_tuning.so" if TUNING else "libsptmm.so")
 
 FMT_U16_DIV, FMT_DELTA_DIV256, FMT_U16_V256, FMT_DELTA_LANE, FMT_I2S = 1, 2, 3, 4, 5
 I8, F16, F32 = 0, 1, 2
@@ -43,7 +46,8 @@ class WeightsInfo(C.Structure):
 
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
-        raise ImportError("libsptmm.so is not built: run `python sptmm_b200/build.py` (needs nvcc)")
+        raise ImportError("%s is not built: run `python sptmm_b200/build.py%s` (needs nvcc)"
+                          % (os.path.basename(LIB_PATH), " --tuning" if TUNING else ""))
     lib = C.CDLL(LIB_PATH)
     u32, u64, vp, i32 = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int
     sigs = {
@@ -60,6 +64,9 @@ def _load() -> C.CDLL:
         "sptmm_gemv": (i32, [vp, vp, u32, u32, vp, u32, u32, vp]),
         "sptmm_weights_save": (i32, [vp, C.c_char_p]),
         "sptmm_weights_load": (i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+        "sptmm_gemv_status": (i32, [vp, C.POINTER(u32)]),
+        "sptmm_quantize_absmax": (i32, [vp, u32, u32, u32, u32, u32, vp, vp, u32, vp]),
+        "sptmm_gemv_scaled": (i32, [vp, vp, u32, vp, vp, C.c_float, u32, u32, vp]),
         "sptmm_gemv_reduce": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, vp]),
         "sptmm_gemv_host": (i32, [vp, vp, u32, u32, vp, u32, u32]),
         "sptmm_gemv_host_async": (i32, [vp, vp, u32, u32, vp, u32, u32, u32]),
@@ -72,12 +79,11 @@ def _load() -> C.CDLL:
         "sptmm_seq_create": (i32, [vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_create_shared": (i32, [vp, u32, u32, vp, vp, u32, u32, C.POINTER(vp)]),
         "sptmm_seq_shared_bytes": (u64, [u32]),
+        "sptmm_seq_shared_bytes_for": (u64, [vp, u32, u32]),
         "sptmm_seq_run": (i32, [vp, vp]),
         "sptmm_seq_run_static": (i32, [vp, u32, u32, vp, C.POINTER(u32)]),
         "sptmm_seq_status": (i32, [vp, C.POINTER(u32), C.POINTER(u64)]),
-        "sptmm_seq_set_trace": (i32, [vp, vp]),
         "sptmm_seq_free": (i32, [vp]),
-        "sptmm_set_trace_buffer": (i32, [vp]),
         "sptmm_device_count": (i32, [C.POINTER(C.c_int)]),
         "sptmm_set_device": (i32, [C.c_int]),
         "sptmm_dev_alloc": (i32, [C.POINTER(vp), u64]),
@@ -86,6 +92,9 @@ def _load() -> C.CDLL:
         "sptmm_memcpy_d2h": (i32, [vp, vp, u64]),
         "sptmm_device_sync": (i32, []),
     }
+    if TUNING:                           # csrc/tuning.h
+        sigs["sptmm_seq_set_trace"] = (i32, [vp, vp])
+        sigs["sptmm_set_trace_buffer"] = (i32, [vp])
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)          # AttributeError if the header and the library disagree
         fn.restype = res
@@ -96,10 +105,10 @@ def _load() -> C.CDLL:
 lib = _load()
 EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
-           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait", "sptmm_gemv_host_batch",
+           "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_status", "sptmm_quantize_absmax", "sptmm_gemv_scaled", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait", "sptmm_gemv_host_batch",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
-           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_trace", "sptmm_seq_free",
-           "sptmm_set_trace_buffer", "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
+           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_shared_bytes_for", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_free",
+           "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
 
 
@@ -193,6 +202,17 @@ class Weights:
         """C = X*W on the device; X and out are device tensors (or addresses)."""
         check(lib.sptmm_gemv(self._h, _ptr(X), dtype, M, _ptr(out), flags, replica, stream))
 
+    def gemv_scaled(self, X, M: int, out, row_scale=None, w_scale: float = 1.0, flags: int = 0, replica: int = 0, stream: int = 0) -> None:
+        """C (float) = float(X*W) * (row_scale[m] * w_scale) for int8 X: the de-quantising epilogue."""
+        check(lib.sptmm_gemv_scaled(self._h, _ptr(X), M, _ptr(out), _ptr(row_scale) if row_scale is not None else None,
+                                    float(w_scale), flags, replica, stream))
+
+    def status(self) -> int:
+        """Waits for the device; 0 unless a bounded wait inside a kernel ran out since upload."""
+        st = C.c_uint32(0)
+        check(lib.sptmm_gemv_status(self._h, C.byref(st)))
+        return st.value
+
     def gemv_reduce(self, X, M: int, C_peers, dtype: int = I8, flags: int = 0, replica: int = 0, stream: int = 0) -> None:
         """Split-K step: adds this rank's partial sums X*W into every column's owner buffer
         (C_peers[r]: rank r's M x shard-width buffer, device tensors or addresses)."""
@@ -258,6 +278,31 @@ class SeqStep(C.Structure):
                 ("ldx", C.c_uint32), ("ldx2", C.c_uint32), ("ldc", C.c_uint32), ("dep", C.c_int32), ("c_kind", C.c_uint32)]
 
 
+def _seq_steps(steps):
+    arr = (SeqStep * len(steps))()
+    for a, s in zip(arr, steps):
+        a.w = s["w"]._h
+        a.replica = s.get("replica", 0)
+        a.x_kind = s.get("x_kind", 0)
+        a.X = _ptr(s["X"])
+        a.X2 = _ptr(s["X2"]) if s.get("X2") is not None else None
+        a.C = _ptr(s["C"]) if s.get("C") is not None else None
+        a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
+        a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
+        a.dep = s.get("dep", -1); a.c_kind = s.get("c_kind", 0)
+    return arr
+
+
+def seq_shared_bytes(steps, M: int) -> int:
+    """Bytes of one rank's synchronisation area for this step list (sptmm_seq_shared_bytes_for);
+    only the kinds, dependencies and weights of the steps matter, not their buffer addresses."""
+    arr = _seq_steps(steps)
+    n = int(lib.sptmm_seq_shared_bytes_for(C.cast(arr, C.c_void_p), len(steps), M))
+    if n == 0:
+        raise ValueError("seq_shared_bytes: bad step list or M")
+    return n
+
+
 class Sequence:
     """A fixed list of matmul steps run by one persistent kernel (sptmm_seq_* in the C ABI).
 
@@ -267,18 +312,8 @@ class Sequence:
     def __init__(self, steps, M: int = 1, counter_peers=None, rank: int = 0):
         """counter_peers: for a multi-GPU sequence, the peer-mapped addresses of every rank's
         counter array (len = ranks); each step then carries "C_peers", one address per rank."""
-        arr = (SeqStep * len(steps))()
+        arr = _seq_steps(steps)
         self._keep = list(steps)                     # keep tensors and handles alive
-        for a, s in zip(arr, steps):
-            a.w = s["w"]._h
-            a.replica = s.get("replica", 0)
-            a.x_kind = s.get("x_kind", 0)
-            a.X = _ptr(s["X"])
-            a.X2 = _ptr(s["X2"]) if s.get("X2") is not None else None
-            a.C = _ptr(s["C"]) if s.get("C") is not None else None
-            a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
-            a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
-            a.dep = s.get("dep", -1); a.c_kind = s.get("c_kind", 0)
         h = C.c_void_p()
         if counter_peers is None:
             check(lib.sptmm_seq_create(C.cast(arr, C.c_void_p), len(steps), M, C.byref(h)))
@@ -305,6 +340,7 @@ class Sequence:
         return nb.value
 
     def set_trace(self, dev_tensor) -> None:
+        """Tuning build only (SPTMM_B200_TUNING=1)."""
         check(lib.sptmm_seq_set_trace(self._h, _ptr(dev_tensor) if dev_tensor is not None else None))
 
     def close(self) -> None:
@@ -317,6 +353,13 @@ class Sequence:
             self.close()
         except Exception:
             pass
+
+
+def quantize_absmax(X, M: int, K: int, out, scale=None, ldx: int = 0, shard: int = 0, pair: bool = False, flags: int = 0,
+                    stream: int = 0) -> None:
+    """int32 rows -> int8 with a per-row absmax scale (sptmm_quantize_absmax); device buffers."""
+    check(lib.sptmm_quantize_absmax(_ptr(X), M, K, ldx, shard, 1 if pair else 0, _ptr(out),
+                                    _ptr(scale) if scale is not None else None, flags, stream))
 
 
 def row_split3_small(X, W_pos_div, W_neg_div, out, M: int, K: int, N: int, S: int, split: int, stream: int = 0) -> None:
@@ -333,17 +376,7 @@ def run_sequence_static(steps, M: int = 1, stream: int = 0, wait: bool = True) -
     """sptmm_seq_run_static: run up to 16 steps (dicts as for Sequence) without allocating device
     memory -- for callers that may not call cudaMalloc at that point; the kernel's scratch is a
     fixed array inside the library.  With wait=True the call waits and returns the status word."""
-    arr = (SeqStep * len(steps))()
-    for a, s in zip(arr, steps):
-        a.w = s["w"]._h
-        a.replica = s.get("replica", 0)
-        a.x_kind = s.get("x_kind", 0)
-        a.X = _ptr(s["X"])
-        a.X2 = _ptr(s["X2"]) if s.get("X2") is not None else None
-        a.C = _ptr(s["C"])
-        a.scale_out = _ptr(s["scale_out"]) if s.get("scale_out") is not None else None
-        a.ldx, a.ldx2, a.ldc = s.get("ldx", 0), s.get("ldx2", 0), s.get("ldc", 0)
-        a.dep = s.get("dep", -1); a.c_kind = s.get("c_kind", 0)
+    arr = _seq_steps(steps)
     st = C.c_uint32(0)
     check(lib.sptmm_seq_run_static(C.cast(arr, C.c_void_p), len(steps), M, stream, C.byref(st) if wait else None))
     return st.value

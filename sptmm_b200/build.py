@@ -1,9 +1,13 @@
 """Builds libsptmm.so (and the rcr / ccc command-line programs) in-tree with nvcc for sm_100a.
 
-    python sptmm_b200/build.py [--force] [--verbose] [--ptxas]
+    python sptmm_b200/build.py [--force] [--verbose] [--ptxas] [--tuning]
 
 The shared library is the product: a C ABI (include/sptmm.h) over hand-written CUDA kernels.
 Objects are rebuilt only when their source, or a shared header, is newer.
+
+--tuning builds a second library beside it, libsptmm_tuning.so, compiled with -DSPTMM_TUNING:
+the kernels then carry timestamp hooks for timelines and launch constants can be overridden from
+the environment (csrc/tuning.h).  Nothing in the product library reads the environment.
 """
 from __future__ import annotations
 
@@ -17,15 +21,15 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libsptmm.so")
+LIB_TUNING = os.path.join(PKG, "libsptmm_tuning.so")
 BIN = os.path.join(PKG, "bin")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"] + ARCH
-NVCC_FLAGS += os.environ.get("SPTMM_NVCC_EXTRA", "").split()      # e.g. -DSPTMM_SEQ_PROFILE for loop timers
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-pthread"]
 
-LIB_SOURCES = ["host_encode.cpp", "weights_file.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "kernels_seq.cu", "cublas_cmp.cu"]
-HEADERS = ["internal.h", "device_common.cuh", os.path.join(ROOT, "include", "sptmm.h")]
+LIB_SOURCES = ["host_encode.cpp", "weights_file.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "kernels_seq.cu", "kernels_quant.cu", "cublas_cmp.cu"]
+HEADERS = ["internal.h", "device_common.cuh", "tuning.h", os.path.join(ROOT, "include", "sptmm.h")]
 
 
 def _newer(target: str, deps: list[str]) -> bool:
@@ -45,25 +49,32 @@ def _run(cmd: list[str], verbose: bool) -> None:
         print(r.stdout + r.stderr, flush=True)
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
-    os.makedirs(BIN, exist_ok=True)
+def _build_library(lib: str, obj_dir: str, defines: list[str], force: bool, verbose: bool, ptxas_info: bool) -> None:
+    os.makedirs(obj_dir, exist_ok=True)
     hdrs = [h if os.path.isabs(h) else os.path.join(CSRC, h) for h in HEADERS]
     jobs, objs = [], []
     for src in LIB_SOURCES:
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
+        o = os.path.join(obj_dir, os.path.splitext(src)[0] + ".o")
         objs.append(o)
         if force or _newer(o, [s] + hdrs):
             if src.endswith(".cu"):
-                cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", s, "-o", o]
+                cmd = ["nvcc"] + NVCC_FLAGS + defines + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", s, "-o", o]
             else:
-                cmd = ["g++"] + CXX_FLAGS + ["-c", s, "-o", o]
+                cmd = ["g++"] + CXX_FLAGS + defines + ["-c", s, "-o", o]
             jobs.append(cmd)
     with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as ex:
         list(ex.map(lambda c: _run(c, verbose or ptxas_info), jobs))
-    if force or jobs or not os.path.exists(LIB):
-        _run(["nvcc", "-shared", "-o", LIB] + objs + ARCH + ["-lcublas", "-Xcompiler", "-pthread"], verbose)
+    if force or jobs or not os.path.exists(lib):
+        _run(["nvcc", "-shared", "-o", lib] + objs + ARCH + ["-lcublas", "-Xcompiler", "-pthread"], verbose)
+
+
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, tuning: bool = False) -> str:
+    os.makedirs(BIN, exist_ok=True)
+    hdrs = [h if os.path.isabs(h) else os.path.join(CSRC, h) for h in HEADERS]
+    _build_library(LIB, OBJ, [], force, verbose, ptxas_info)
+    if tuning:
+        _build_library(LIB_TUNING, OBJ + "_tuning", ["-DSPTMM_TUNING"], force, verbose, False)
     cli = os.path.join(CSRC, "cli.cpp")
     if os.path.exists(cli):
         for name, layout in (("rcr", "-DSPTMM_CLI_RCR"), ("ccc", "-DSPTMM_CLI_CCC")):
@@ -79,5 +90,6 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+                 tuning="--tuning" in sys.argv)
     print(path)

@@ -11,44 +11,29 @@ namespace sptmm {
 
 const Tune &tune()
 {
-    static Tune t = [] {
-        // Two 256-thread CTAs per SM, four blocks per warp in registers and a ~50 KB footprint per
-        // CTA: measured best on B200 both for one stream (5.7 us per 6912x2560 GEMV) and for
-        // independent calls on several streams (3.2 us, the HBM copy rate), because up to four
-        // CTAs of neighbouring calls fit one SM and overlap their stream / gather phases.
-        Tune v{2, 256, 4, 0, 1, 43};
-        const char *s = getenv("SPTMM_TUNE");
-        if (s) {
-            std::string str(s);
-            size_t pos = 0;
-            while (pos < str.size()) {
-                size_t end = str.find(',', pos);
-                if (end == std::string::npos) end = str.size();
-                std::string kv = str.substr(pos, end - pos);
-                size_t eq = kv.find('=');
-                if (eq != std::string::npos) {
-                    std::string k = kv.substr(0, eq);
-                    int val = atoi(kv.c_str() + eq + 1);
-                    if (k == "ctas_per_sm" && val >= 1 && val <= 8) v.ctas_per_sm = val;
-                    else if (k == "threads" && val >= 32 && val <= 512 && val % 32 == 0) v.threads = val;
-                    else if (k == "prefetch" && val >= 1 && val <= 16) v.prefetch = val;
-                    else if (k == "evict_first") v.evict_first = val != 0;
-                    else if (k == "l2_prefetch") v.l2_prefetch = val != 0;
-                    else if (k == "smem_kb" && val >= 0 && val <= 220) v.smem_kb = val;
-                }
-                pos = end + 1;
-            }
-        }
-        return v;
-    }();
+    // Two 256-thread CTAs per SM, four blocks per warp in registers and a ~50 KB footprint per
+    // CTA: measured best on B200 both for one stream (5.7 us per 6912x2560 GEMV) and for
+    // independent calls on several streams (3.2 us, the HBM copy rate), because up to four
+    // CTAs of neighbouring calls fit one SM and overlap their stream / gather phases.
+    static const Tune t = {(int)tuning_knob("SPTMM_TUNE_CTAS_PER_SM", 2), (int)tuning_knob("SPTMM_TUNE_THREADS", 256),
+                           (int)tuning_knob("SPTMM_TUNE_PREFETCH", 4), (int)tuning_knob("SPTMM_TUNE_SMEM_KB", 43)};
     return t;
 }
+
+#ifdef SPTMM_TUNING
+long tuning_knob(const char *name, long dflt)
+{
+    const char *e = getenv(name);
+    return e ? atol(e) : dflt;
+}
+#endif
 
 static void free_host_slot(sptmm_weights::HostSlot &h)
 {
     if (h.dev_x) cudaFree(h.dev_x);
     if (h.pin_x) cudaFreeHost(h.pin_x);
     if (h.pin_c) cudaFreeHost(h.pin_c);
+    if (h.pin_status) cudaFreeHost(h.pin_status);
     if (h.stream) cudaStreamDestroy((cudaStream_t)h.stream);
     h = sptmm_weights::HostSlot();
 }
@@ -60,7 +45,6 @@ static void free_device_side(sptmm_weights *w)
         cudaGetDevice(&cur);
         cudaSetDevice(w->device);
         for (auto &rep : w->dev) for (void *p : rep) if (p) cudaFree(p);
-        if (w->plan.d_ctas) cudaFree(w->plan.d_ctas);
         if (w->plan.d_status) cudaFree(w->plan.d_status);
         for (auto &h : w->slots) {
             if (h.busy && h.stream) cudaStreamSynchronize((cudaStream_t)h.stream);
@@ -146,10 +130,7 @@ extern "C" int sptmm_weights_upload_replicas(sptmm_weights *w, uint32_t copies)
         }
     if (w->format == SPTMM_FMT_U16_V256 || w->format == SPTMM_FMT_DELTA_LANE) {
         make_plan(w);
-        const size_t bytes = w->plan.cta_col.size() * sizeof(uint32_t);
-        cudaError_t e = cudaMalloc(&w->plan.d_ctas, bytes);
-        if (e == cudaSuccess) e = cudaMemcpy(w->plan.d_ctas, w->plan.cta_col.data(), bytes, cudaMemcpyHostToDevice);
-        if (e == cudaSuccess) e = cudaMalloc(&w->plan.d_status, 16);
+        cudaError_t e = cudaMalloc(&w->plan.d_status, 16);
         if (e == cudaSuccess) e = cudaMemset(w->plan.d_status, 0, 16);
         if (e != cudaSuccess) {
             free_device_side(w);
@@ -169,8 +150,8 @@ extern "C" int sptmm_weights_free(sptmm_weights *w)
     return SPTMM_OK;
 }
 
-extern "C" int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M, void *C,
-                          uint32_t flags, uint32_t replica, void *stream)
+static int gemv_dispatch(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M, void *C,
+                         uint32_t flags, uint32_t replica, void *stream, uint32_t *status)
 {
     if (!w || !X || !C) return fail(SPTMM_ERR_INVALID, "gemv: null pointer");
     if (M == 0) return fail(SPTMM_ERR_INVALID, "gemv: M must be at least 1");
@@ -182,6 +163,7 @@ extern "C" int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype,
     if (dev != w->device) return fail(SPTMM_ERR_STATE, "gemv: weights live on device %d, current device is %d", w->device, dev);
     const void *const *arr = w->dev[replica].data();
     GemvArgs a{w, arr, X, C, dtype, M, flags, stream};
+    a.status = status;
     switch (w->format) {
         case SPTMM_FMT_U16_V256: return launch_native_u16(a);
         case SPTMM_FMT_DELTA_LANE: return launch_native_delta(a);
@@ -194,6 +176,29 @@ extern "C" int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype,
                                    flags, stream);
     }
     return fail(SPTMM_ERR_UNSUPPORTED, "gemv: format %u", w->format);
+}
+
+extern "C" int sptmm_gemv(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M, void *C,
+                          uint32_t flags, uint32_t replica, void *stream)
+{
+    return gemv_dispatch(w, X, dtype, M, C, flags, replica, stream, nullptr);
+}
+
+extern "C" int sptmm_gemv_scaled(const sptmm_weights *w, const int8_t *X, uint32_t M, float *C, const float *row_scale,
+                                 float w_scale, uint32_t flags, uint32_t replica, void *stream)
+{
+    if (!w || !X || !C) return fail(SPTMM_ERR_INVALID, "gemv_scaled: null pointer");
+    if (M == 0) return fail(SPTMM_ERR_INVALID, "gemv_scaled: M must be at least 1");
+    if (w->format != SPTMM_FMT_U16_V256 && w->format != SPTMM_FMT_DELTA_LANE)
+        return fail(SPTMM_ERR_UNSUPPORTED, "gemv_scaled: weights must be in a native format");
+    if (w->device < 0 || w->dev.empty()) return fail(SPTMM_ERR_STATE, "gemv_scaled: weights are not uploaded");
+    if (replica >= w->dev.size()) return fail(SPTMM_ERR_INVALID, "gemv_scaled: replica %u of %zu", replica, w->dev.size());
+    int dev = -1;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != w->device) return fail(SPTMM_ERR_STATE, "gemv_scaled: weights live on device %d, current device is %d", w->device, dev);
+    GemvArgs a{w, w->dev[replica].data(), X, C, SPTMM_I8, M, flags, stream};
+    a.scaled = true; a.row_scale = row_scale; a.out_scale = w_scale;
+    return w->format == SPTMM_FMT_U16_V256 ? launch_native_u16(a) : launch_native_delta(a);
 }
 
 extern "C" int sptmm_gemv_reduce(const sptmm_weights *w, const void *X, uint32_t dtype, uint32_t M,
@@ -219,6 +224,27 @@ extern "C" int sptmm_gemv_reduce(const sptmm_weights *w, const void *X, uint32_t
     return launch_native_u16(a);
 }
 
+// The per-call kernels' bounded waits raise a word in device memory when they run out (the kernel
+// then finishes with whatever it has); this reads it back.
+static int read_gemv_status(const sptmm_weights *w, uint32_t *word)
+{
+    *word = 0;
+    if (!w->plan.d_status) return SPTMM_OK;            // formats whose kernels have no waits
+    SPTMM_CUDA_TRY(cudaMemcpy(word, w->plan.d_status, 4, cudaMemcpyDeviceToHost));
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_gemv_status(const sptmm_weights *w, uint32_t *status)
+{
+    if (!w || !status) return fail(SPTMM_ERR_INVALID, "gemv_status: null pointer");
+    if (w->device < 0) return fail(SPTMM_ERR_STATE, "gemv_status: weights are not uploaded");
+    int dev = -1;
+    SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != w->device) return fail(SPTMM_ERR_STATE, "gemv_status: weights live on device %d, current device is %d", w->device, dev);
+    SPTMM_CUDA_TRY(cudaDeviceSynchronize());
+    return read_gemv_status(w, status);
+}
+
 extern "C" int sptmm_gemv_host_wait(sptmm_weights *w, uint32_t slot)
 {
     if (!w || slot >= sptmm_weights::kHostSlots) return fail(SPTMM_ERR_INVALID, "gemv_host_wait: bad handle or slot %u", slot);
@@ -235,6 +261,11 @@ extern "C" int sptmm_gemv_host_wait(sptmm_weights *w, uint32_t slot)
     if (qe == cudaErrorNotReady) qe = cudaStreamSynchronize(st);
     h.busy = false;
     if (qe != cudaSuccess) return fail(SPTMM_ERR_CUDA, "gemv_host: %s", cudaGetErrorString(qe));
+    // The status word sits in mapped pinned memory for host-buffer calls (see _async), so this check
+    // is a host load: a call whose bounded wait ran out must not hand back partial sums as a result.
+    if (h.pin_status && *(volatile uint32_t *)h.pin_status != 0)
+        return fail(SPTMM_ERR_STATE, "gemv_host: a bounded wait in the kernel ran out (status %u); the result was dropped",
+                    *(volatile uint32_t *)h.pin_status);
     memcpy(h.user_c, h.pin_c, h.user_c_bytes);
     return SPTMM_OK;
 }
@@ -275,6 +306,11 @@ extern "C" int sptmm_gemv_host_async(sptmm_weights *w, const void *X_host, uint3
         SPTMM_CUDA_TRY(cudaHostGetDevicePointer(&h.dev_c, h.pin_c, 0));
         h.c_bytes = cb;
     }
+    if (!h.pin_status) {
+        SPTMM_CUDA_TRY(cudaHostAlloc(&h.pin_status, 16, cudaHostAllocMapped));
+        SPTMM_CUDA_TRY(cudaHostGetDevicePointer(&h.dev_status, h.pin_status, 0));
+    }
+    *(volatile uint32_t *)h.pin_status = 0;
     cudaStream_t st = (cudaStream_t)h.stream;
     memcpy(h.pin_x, X_host, xb);
     // X does go through a device copy: every CTA reads all of it, and reads of host memory are
@@ -283,7 +319,8 @@ extern "C" int sptmm_gemv_host_async(sptmm_weights *w, const void *X_host, uint3
     // was measured too: 25.8 us against 24.0 us per blocking call -- a PCIe read inside the
     // kernel is slower than the copy engine's.
     SPTMM_CUDA_TRY(cudaMemcpyAsync(h.dev_x, h.pin_x, xb, cudaMemcpyHostToDevice, st));
-    const int rc = sptmm_gemv(w, h.dev_x, dtype, M, h.dev_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, replica, st);
+    const int rc = gemv_dispatch(w, h.dev_x, dtype, M, h.dev_c, flags & ~(uint32_t)SPTMM_LAUNCH_PDL, replica, st,
+                                 (uint32_t *)h.dev_status);
     if (rc != SPTMM_OK) return rc;
     h.user_c = C_host; h.user_c_bytes = cb; h.busy = true;
     return SPTMM_OK;
@@ -329,11 +366,13 @@ extern "C" int sptmm_row_split_delta2(const int8_t *X, const uint8_t *W_pos_delt
     return launch_delta256(X, W_pos_delta, W_neg_delta, C, SPTMM_I8, M, K, N, S, 0, stream);
 }
 
+#ifdef SPTMM_TUNING
 extern "C" int sptmm_set_trace_buffer(void *dev_ptr)
 {
     set_trace_buffer((unsigned long long *)dev_ptr);
     return SPTMM_OK;
 }
+#endif
 
 extern "C" int sptmm_device_count(int *count)
 {

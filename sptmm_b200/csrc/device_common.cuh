@@ -27,27 +27,6 @@ template <> struct ActTraits<SPTMM_F32> { using elem = float;  using acc = float
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait_prior_grid()   { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// 16-byte streaming load that bypasses L1; with `policy` != 0 the line is also marked
-// evict-first in L2 (weights are read once per matmul).
-__device__ __forceinline__ uint64_t l2_evict_first_policy()
-{
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-
-__device__ __forceinline__ uint4 ld_stream16(const uint4 *p, uint64_t policy)
-{
-    uint4 v;
-    if (policy)
-        asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
-                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
-    else
-        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
 // The activation tile lives in shared memory TRANSPOSED: row k holds the MT values
 // X[m0..m0+MT)[k] back to back (RB = MT*sizeof(elem) bytes), so one gather of row k feeds all
 // MT accumulators.  Row K is an all-zero row: padded list entries carry index K.

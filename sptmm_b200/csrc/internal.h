@@ -30,8 +30,7 @@ struct LaunchPlan {                   // derived at upload time from the device'
     uint32_t threads = 0;             // threads per CTA
     uint32_t max_cols = 0;            // most columns any CTA owns
     std::vector<uint32_t> cta_blk;    // grid+1 block boundaries (passed in kernel parameters)
-    std::vector<uint32_t> cta_col;    // grid+1 column boundaries (device copy in d_ctas)
-    void *d_ctas = nullptr;
+    std::vector<uint32_t> cta_col;    // grid+1 column boundaries (passed in kernel parameters)
     void *d_status = nullptr;         // device word set by a kernel whose bounded wait ran out
     uint32_t max_cta_blocks = 0;      // most blocks any CTA owns
 };
@@ -57,6 +56,7 @@ struct sptmm_weights {
     struct HostSlot {
         void *pin_x = nullptr, *dev_x = nullptr;      // pinned host copy of X and its device copy
         void *pin_c = nullptr, *dev_c = nullptr;      // mapped pinned result and the device's address of it
+        void *pin_status = nullptr, *dev_status = nullptr;   // mapped pinned word a kernel sets when a bounded wait runs out
         size_t x_bytes = 0, c_bytes = 0;              // capacities
         void *stream = nullptr;
         void *user_c = nullptr;                       // where the pending call's result goes
@@ -69,10 +69,18 @@ struct sptmm_weights {
 
 namespace sptmm {
 
-// Tunables read once from the environment (SPTMM_TUNE="ctas_per_sm=2,threads=256,prefetch=4").
-// smem_kb = shared memory one CTA of the small-tile plan may use beside its activation tile.
-struct Tune { int ctas_per_sm; int threads; int prefetch; int evict_first; int l2_prefetch; int smem_kb; };
+// Launch constants of the per-call kernel.  smem_kb = shared memory one CTA of the small-tile plan
+// may use beside its activation tile.
+struct Tune { int ctas_per_sm; int threads; int prefetch; int smem_kb; };
 const Tune &tune();
+
+// A build with -DSPTMM_TUNING (build.py --tuning, a separate library used for sweeps and kernel
+// timelines) lets the environment override the constants below; the product library has them fixed.
+#ifdef SPTMM_TUNING
+long tuning_knob(const char *name, long dflt);
+#else
+constexpr long tuning_knob(const char *, long dflt) { return dflt; }
+#endif
 
 struct GemvArgs {
     const sptmm_weights *w;
@@ -82,6 +90,10 @@ struct GemvArgs {
     void *stream;
     void *const *C_peers = nullptr;   // split-K: per-rank output buffers the partial sums are added to
     uint32_t n_peers = 0;
+    uint32_t *status = nullptr;       // where a bounded wait that ran out is reported (null: the handle's device word)
+    bool scaled = false;              // int8 activations, float output: C = sum * row_scale[m] * out_scale
+    const float *row_scale = nullptr; // device float[M], or null for 1
+    float out_scale = 1.0f;
 };
 
 int launch_native_u16(const GemvArgs &a);
@@ -92,11 +104,12 @@ int launch_div(const void *X, const uint16_t *wp, const uint16_t *wn, void *C, u
                void *stream);
 int launch_delta256(const void *X, const uint8_t *dp, const uint8_t *dn, void *C, uint32_t dtype,
                     uint32_t M, uint32_t K, uint32_t N, uint32_t S, uint32_t flags, void *stream);
+#ifdef SPTMM_TUNING
 void set_trace_buffer(unsigned long long *dev_ptr);
+#endif
 void plan_columns(const uint32_t *off, uint32_t N, uint32_t grid, std::vector<uint32_t> &cta_blk,
                   std::vector<uint32_t> &cta_col, uint32_t &max_cols, uint32_t &max_cta_blocks,
                   uint32_t col_align = 1);
-int kernels_init();                   // opt in to >48 KB dynamic shared memory, once per process
 
 inline size_t dtype_size(uint32_t d) { return d == SPTMM_I8 ? 1 : d == SPTMM_F16 ? 2 : 4; }
 

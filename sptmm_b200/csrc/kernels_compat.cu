@@ -9,6 +9,8 @@
 // (transposed, up to 16 rows) in shared memory once, so the index stream is read once for all
 // rows instead of once per row; gathers hit shared memory instead of L1; any shape is accepted
 // at run time instead of a compile-time whitelist.
+#include <atomic>
+
 #include "device_common.cuh"
 
 namespace sptmm {
@@ -50,12 +52,13 @@ __global__ void __launch_bounds__(256) k_div(const DivParams p)
             uint16_t ip[U], in[U];
 #pragma unroll
             for (int u = 0; u < U; u++) { ip[u] = __ldg(bp + (j + u) * stride); in[u] = __ldg(bn + (j + u) * stride); }
+            // a caller-built layout may hold anything: an index past K reads the zero row, not beyond the tile
 #pragma unroll
-            for (int u = 0; u < U; u++) { gather_add<DT, MT>(ap, ip[u]); gather_add<DT, MT>(an, in[u]); }
+            for (int u = 0; u < U; u++) { gather_add<DT, MT>(ap, min((uint32_t)ip[u], p.K)); gather_add<DT, MT>(an, min((uint32_t)in[u], p.K)); }
         }
         for (; j < p.chunks; j++) {
-            gather_add<DT, MT>(ap, __ldg(bp + j * stride));
-            gather_add<DT, MT>(an, __ldg(bn + j * stride));
+            gather_add<DT, MT>(ap, min((uint32_t)__ldg(bp + j * stride), p.K));
+            gather_add<DT, MT>(an, min((uint32_t)__ldg(bn + j * stride), p.K));
         }
         const uint32_t col = g * CPW + lane / SPLIT;
 #pragma unroll
@@ -229,11 +232,18 @@ __global__ void __launch_bounds__(256) k_i2s(const I2sParams p)
 }
 
 // --------------------------------------------------------------------------------------------
-template <typename Kern, typename Prm>
-static int launch_generic(Kern kern, const Prm &prm, dim3 grid, size_t smem, bool pdl, cudaStream_t st)
+template <auto kern, typename Prm>
+static int launch_generic(const Prm &prm, dim3 grid, size_t smem, bool pdl, cudaStream_t st)
 {
-    if (smem > 48 * 1024)
-        SPTMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    if (smem > 48 * 1024) {          // opt in to large dynamic shared memory once per kernel and device
+        static std::atomic<int> configured_device{-1};     // one instance per kernel (the kernel is a template argument)
+        int dev = 0;
+        SPTMM_CUDA_TRY(cudaGetDevice(&dev));
+        if (configured_device.load(std::memory_order_acquire) != dev) {
+            SPTMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            configured_device.store(dev, std::memory_order_release);
+        }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -256,10 +266,10 @@ template <int DT, int SPLIT>
 static int launch_div_mt(const DivParams &prm, int mt, dim3 grid, size_t smem, bool pdl, cudaStream_t st)
 {
     switch (mt) {
-        case 1: return launch_generic(k_div<DT, 1, SPLIT>, prm, grid, smem, pdl, st);
-        case 2: return launch_generic(k_div<DT, 2, SPLIT>, prm, grid, smem, pdl, st);
-        case 4: return launch_generic(k_div<DT, 4, SPLIT>, prm, grid, smem, pdl, st);
-        case 8: return launch_generic(k_div<DT, 8, SPLIT>, prm, grid, smem, pdl, st);
+        case 1: return launch_generic<k_div<DT, 1, SPLIT>>(prm, grid, smem, pdl, st);
+        case 2: return launch_generic<k_div<DT, 2, SPLIT>>(prm, grid, smem, pdl, st);
+        case 4: return launch_generic<k_div<DT, 4, SPLIT>>(prm, grid, smem, pdl, st);
+        case 8: return launch_generic<k_div<DT, 8, SPLIT>>(prm, grid, smem, pdl, st);
     }
     return fail(SPTMM_ERR_INVALID, "internal: row tile %d", mt);
 }
@@ -302,10 +312,10 @@ template <int DT>
 static int launch_delta_mt(const DeltaParams &prm, int mt, dim3 grid, size_t smem, bool pdl, cudaStream_t st)
 {
     switch (mt) {
-        case 1: return launch_generic(k_delta256<DT, 1>, prm, grid, smem, pdl, st);
-        case 2: return launch_generic(k_delta256<DT, 2>, prm, grid, smem, pdl, st);
-        case 4: return launch_generic(k_delta256<DT, 4>, prm, grid, smem, pdl, st);
-        case 8: return launch_generic(k_delta256<DT, 8>, prm, grid, smem, pdl, st);
+        case 1: return launch_generic<k_delta256<DT, 1>>(prm, grid, smem, pdl, st);
+        case 2: return launch_generic<k_delta256<DT, 2>>(prm, grid, smem, pdl, st);
+        case 4: return launch_generic<k_delta256<DT, 4>>(prm, grid, smem, pdl, st);
+        case 8: return launch_generic<k_delta256<DT, 8>>(prm, grid, smem, pdl, st);
     }
     return fail(SPTMM_ERR_INVALID, "internal: row tile %d", mt);
 }
@@ -347,14 +357,12 @@ int launch_i2s(const GemvArgs &a)
     const bool pdl = (a.flags & SPTMM_LAUNCH_PDL) != 0;
     cudaStream_t st = (cudaStream_t)a.stream;
     switch (mt) {
-        case 1: return launch_generic(k_i2s<1>, prm, grid, smem, pdl, st);
-        case 2: return launch_generic(k_i2s<2>, prm, grid, smem, pdl, st);
-        case 4: return launch_generic(k_i2s<4>, prm, grid, smem, pdl, st);
-        case 8: return launch_generic(k_i2s<8>, prm, grid, smem, pdl, st);
+        case 1: return launch_generic<k_i2s<1>>(prm, grid, smem, pdl, st);
+        case 2: return launch_generic<k_i2s<2>>(prm, grid, smem, pdl, st);
+        case 4: return launch_generic<k_i2s<4>>(prm, grid, smem, pdl, st);
+        case 8: return launch_generic<k_i2s<8>>(prm, grid, smem, pdl, st);
     }
     return fail(SPTMM_ERR_INVALID, "internal: row tile %d", mt);
 }
-
-int kernels_init() { return SPTMM_OK; }
 
 }  // namespace sptmm

@@ -42,8 +42,10 @@ struct NativeParams {
     const uint32_t *blk_off;     // 2N+1
     const void *X;
     void *C;
+#ifdef SPTMM_TUNING
     unsigned long long *trace;   // optional: 8 timestamps per CTA for the first trace_ctas CTAs
     uint32_t trace_ctas;
+#endif
     uint32_t *status;            // device word: set non-zero if a bounded wait ran out
     uint32_t K, N, M;
     uint32_t max_cols;
@@ -56,6 +58,10 @@ struct NativeParams {
     uint32_t n_peers;
     uint32_t col_bound[9];
     void *Cp[8];
+    // de-quantising epilogue (int8 activations only): store float(sum) * (row_scale[m] * out_scale)
+    uint32_t scaled;
+    const float *row_scale;      // per row of X, or null for 1
+    float out_scale;
     uint32_t half_blocks;        // blocks per half of a warp's staging area
     uint32_t stage_blocks;       // blocks of staging area per warp (one or two halves)
     uint32_t stage_off;          // byte offset of the staging area in dynamic shared memory
@@ -63,12 +69,18 @@ struct NativeParams {
     uint32_t cta_col[kMaxGrid + 1];   // column boundaries: CTA i owns columns [cta_col[i], cta_col[i+1])
 };
 
+// Timestamps for kernel timelines exist only in the tuning build.
+#ifdef SPTMM_TUNING
 __device__ __forceinline__ unsigned long long global_ns()
 {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+#define SPTMM_STAMP(slot) do { if (tracing) p.trace[blockIdx.x * 8 + (slot)] = global_ns(); } while (0)
+#else
+#define SPTMM_STAMP(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint4 ld_weights16(const uint4 *p)
 {
@@ -130,8 +142,10 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     const uint32_t wb1 = b0 + (uint32_t)(((uint64_t)nb * (warp + 1)) / nwarps);
     const uint32_t n = wb1 - wb0;
     const uint32_t nbl = p.uniform_nbl;
+#ifdef SPTMM_TUNING
     const bool tracing = p.trace != nullptr && blockIdx.x < p.trace_ctas && blockIdx.y == 0 && tid == 33;   // a lane that issues no fences or copies
-    if (tracing) p.trace[blockIdx.x * 8 + 0] = global_ns();
+#endif
+    SPTMM_STAMP(0);
 
     // ---- list boundaries (only needed when lists differ in length): ask for them first, so the
     // answer is not queued behind the weight stream
@@ -211,7 +225,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
         for (uint32_t i = tid; i < nwarps * MT; i += blockDim.x) { head_s[i] = acc_t(0); tail_s[i] = acc_t(0); }
 
     pdl_wait_prior_grid();
-    if (tracing) p.trace[blockIdx.x * 8 + 1] = global_ns();
+    SPTMM_STAMP(1);
 
     if (x_regs) {
         if constexpr (MT == 1) {
@@ -224,7 +238,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     }
     if (x_first) request_weights();
     __syncthreads();
-    if (tracing) p.trace[blockIdx.x * 8 + 2] = global_ns();
+    SPTMM_STAMP(2);
 
     if (n) {
         // local index (relative to list 2*c0) of the list that holds block wb0, and of wb1-1
@@ -417,13 +431,15 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
                 }
             }
         }
-        if (!ok && lane == 0 && p.status) atomicOr(p.status, 1u);    // report, do not hang
+        // report, do not hang (a plain store: every writer stores the same 1, and the word may live
+        // in mapped host memory, where atomics are not available on every platform)
+        if (!ok && lane == 0 && p.status) *reinterpret_cast<volatile uint32_t *>(p.status) = 1u;
         if (dirty) flush();
     } else if (!kInt && lane == 0) {
         hcol_s[warp] = 0xffffffffu; tcol_s[warp] = 0xffffffffu;
     }
     __syncthreads();
-    if (tracing) p.trace[blockIdx.x * 8 + 3] = global_ns();
+    SPTMM_STAMP(3);
 
     // ---- write the CTA's columns; floats first fold the per-warp edge sums in warp order
     acc_t *C = reinterpret_cast<acc_t *>(p.C);
@@ -451,9 +467,16 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             continue;
         }
         const size_t o = p.c_colmajor ? (size_t)(c0 + col) * p.M + m0 + m : (size_t)(m0 + m) * p.N + c0 + col;
+        if constexpr (kInt) {
+            if (p.scaled) {          // the sum is exact in fp32 (|sum| <= 127 K < 2^23); one product of the two scales, one of the sum
+                const float sc = (p.row_scale ? __ldg(p.row_scale + m0 + m) : 1.0f) * p.out_scale;
+                reinterpret_cast<float *>(p.C)[o] = (float)v * sc;
+                continue;
+            }
+        }
         C[o] = v;
     }
-    if (tracing) p.trace[blockIdx.x * 8 + 4] = global_ns();
+    SPTMM_STAMP(4);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -535,8 +558,10 @@ static int launch_dtype(const NativeParams &prm, int mt, int pd, bool wide, dim3
     return fail(SPTMM_ERR_INVALID, "internal: row tile %d", mt);
 }
 
+#ifdef SPTMM_TUNING
 static unsigned long long *g_trace = nullptr;
 void set_trace_buffer(unsigned long long *dev_ptr) { g_trace = dev_ptr; }
+#endif
 
 static int launch_native(const GemvArgs &a, const bool delta)
 {
@@ -554,7 +579,7 @@ static int launch_native(const GemvArgs &a, const bool delta)
     }
     // A small tile leaves room for several CTAs per SM, whose stream and gather phases then
     // overlap (also across neighbouring calls); a tile of tens of KB gets the SM to itself.
-    static const size_t wide_kb = [] { const char *e = getenv("SPTMM_WIDE_KB"); return e ? (size_t)atoi(e) : (size_t)32; }();
+    static const size_t wide_kb = (size_t)tuning_knob("SPTMM_WIDE_KB", 32);
     const bool wide = xs_bytes(w.K, mt * es) > wide_kb * 1024;
     const LaunchPlan &plan = wide ? w.plan_wide : w.plan;
     const uint32_t threads = plan.threads, nwarps = threads / 32;
@@ -575,7 +600,7 @@ static int launch_native(const GemvArgs &a, const bool delta)
     // of two, so a neighbouring call's CTAs stream while this one gathers (6912x2560, 4 streams /
     // 1 stream: M=4 int8 6.1 -> 5.8 / 9.8 -> 8.5 us, M=1 fp32 5.9 -> 4.7 / 8.7 -> 7.6 us; the
     // one-row int8 tile wants the larger area: 3.35 against 3.5 us; 14 KB tiles are indifferent).
-    static const size_t stage_big_kb = [] { const char *e = getenv("SPTMM_STAGE_BIG_KB"); return e ? (size_t)atoi(e) : (size_t)30; }();
+    static const size_t stage_big_kb = (size_t)tuning_knob("SPTMM_STAGE_BIG_KB", 30);
     const size_t stage_kb = xs_bytes(w.K, mt * es) > 16 * 1024 ? std::min((size_t)tune().smem_kb, stage_big_kb) : (size_t)tune().smem_kb;
     const size_t budget = wide ? (size_t)225 * 1024
                                : std::min(base_smem + std::max(stage_kb * 1024, min_stage), (size_t)225 * 1024);
@@ -588,18 +613,18 @@ static int launch_native(const GemvArgs &a, const bool delta)
     prm.idx = (const uint4 *)a.arrays[0];
     prm.blk_off = (const uint32_t *)a.arrays[1];
     prm.X = a.X; prm.C = a.C;
+#ifdef SPTMM_TUNING
     prm.trace = g_trace;
-    static const uint32_t trace_ctas = [] { const char *e = getenv("SPTMM_TRACE_CTAS"); return e ? (uint32_t)atoi(e) : 8u; }();
-    prm.trace_ctas = trace_ctas;
-    prm.status = (uint32_t *)w.plan.d_status;
+    prm.trace_ctas = (uint32_t)tuning_knob("SPTMM_TRACE_CTAS", 8);
+#endif
+    prm.status = a.status ? a.status : (uint32_t *)w.plan.d_status;
     prm.K = w.K; prm.N = w.N; prm.M = a.M;
     prm.max_cols = plan.max_cols;
     prm.x_colmajor = (a.flags & SPTMM_X_COLMAJOR) ? 1 : 0;
     prm.c_colmajor = (a.flags & SPTMM_C_COLMAJOR) ? 1 : 0;
     prm.uniform_nbl = w.uniform_nbl;
     prm.one = 1;
-    static const int x_early_env = [] { const char *e = getenv("SPTMM_X_EARLY"); return e ? atoi(e) : 1; }();
-    prm.x_early = ((a.flags & SPTMM_LAUNCH_PDL) == 0 && x_early_env) ? 1 : 0;
+    prm.x_early = ((a.flags & SPTMM_LAUNCH_PDL) == 0 && tuning_knob("SPTMM_X_EARLY", 1)) ? 1 : 0;
     prm.n_peers = a.n_peers;
     for (uint32_t r = 0; r < 8; r++) {
         prm.Cp[r] = r < a.n_peers ? a.C_peers[r] : nullptr;
@@ -607,6 +632,7 @@ static int launch_native(const GemvArgs &a, const bool delta)
     }
     prm.col_bound[8] = a.n_peers ? w.N : 0;
     if (a.n_peers) prm.col_bound[a.n_peers] = w.N;
+    prm.scaled = a.scaled ? 1u : 0u; prm.row_scale = a.row_scale; prm.out_scale = a.out_scale;
     prm.half_blocks = half;
     prm.stage_blocks = halves * half;
     prm.stage_off = (uint32_t)base_smem;

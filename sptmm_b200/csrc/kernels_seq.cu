@@ -19,7 +19,9 @@
 //    quantise them on the fly to int8 with a per-row absmax scale, which fuses the activation
 //    quantiser between the layers of a stack into the matmul.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
+#include <mutex>
 
 #include "device_common.cuh"
 
@@ -51,7 +53,21 @@ struct SeqDesc {
     uint32_t release;                // 1: bump the step counter after the output is stored
     uint32_t c_kind;                 // 1: the output is the sum of each pair of neighbouring columns (N/2 values)
     uint32_t want_amax;              // 1: a later x_kind 3 step wants this step's row maxima recorded
+    // Producer-side quantiser (an x_kind 4 reader): this step turns its output columns
+    // [q_0, q_0 + q_n) -- counted from its first own column, so q_0 may be negative on a rank whose
+    // shard starts further right -- into int8 itself, in two hand-overs: every CTA publishes the row
+    // maxima of its own columns (amax1, then amax2 between GPUs), and once a CTA knows the rows'
+    // maxima over all columns it rounds ITS columns and stores them, three rows to a tagged word, in
+    // every rank's copy of the packed buffer.  The offsets count bytes from the start of a rank's
+    // synchronisation area (the same on every rank).
+    uint32_t q_n;                    // 0: off
+    int32_t q_0;
+    uint32_t q_off, amax1_off, amax2_off;
+    float *q_scale_out;              // optional: absmax/127 per row (the reader's scale_out)
 };
+
+constexpr uint32_t kAmaxStride = 256;            // row maxima: [16 rows][kAmaxStride CTAs] per step
+__host__ __device__ inline uint32_t packed_words(uint32_t M) { return (M + 2) / 3; }   // tagged words per column: three rows each
 
 constexpr uint32_t kPollLimit = 1u << 20;        // reloads of one stale word before giving up
 
@@ -104,7 +120,9 @@ struct SeqParams {
     unsigned long long *counter_peers[kMaxPeers];   // every rank's (peer-mapped); used when n_peers > 0
     uint32_t n_peers;            // 0: single GPU
     uint32_t *status;
-    unsigned long long *trace;   // optional, 4 timestamps per step (first 256 steps) from CTA 0
+#ifdef SPTMM_TUNING
+    unsigned long long *trace;   // optional timestamps for kernel timelines (tuning build only)
+#endif
     unsigned long long target;   // counters[s] >= target  <=>  step s finished in this run
     uint32_t nsteps, M, max_cols, ring_slots, xs_bytes, G;
     uint32_t slot_blocks;        // 512-byte blocks per ring slot
@@ -115,8 +133,16 @@ struct SeqParams {
     uint32_t *amax;
     uint32_t *amax_peers[kMaxPeers];
     uint32_t run_parity;
+    uint32_t my_rank;
+    // x_kind 5 (settled exchange): two local counters per step, and two buffers (by step parity) for
+    // the finished int8 tile every CTA then fetches with one bulk copy
+    unsigned long long *settle;
+    unsigned char *xq;
+    uint32_t xq_stride;
+    unsigned long long target_local;   // settle[i] >= target_local  <=>  every CTA of THIS GPU has arrived in this run
 };
 
+#ifdef SPTMM_TUNING
 // Timestamp for the optional trace.  A bare read of %globaltimer is hoisted by the assembler
 // (it was seen moving above barriers); guarding it with a predicate computed from a volatile
 // shared-memory load pins it behind whatever that load is ordered after.
@@ -128,6 +154,18 @@ __device__ __forceinline__ unsigned long long seq_ns(const volatile uint32_t *an
                  : "=l"(t) : "r"(v) : "memory");
     return t;
 }
+#endif
+
+// Every CTA's timestamp at a point inside the input stage, for steps 100..103 (tuning build only).
+#ifdef SPTMM_TUNING
+#define SEQ_MARK(prm, step, slot, anchor)                                                                   \
+    do {                                                                                                     \
+        if ((prm).trace != nullptr && threadIdx.x == 33 && (step) >= 100 && (step) < 104)                     \
+            (prm).trace[5120 + (slot) * 1024 + ((step) - 100) * 256 + blockIdx.x] = seq_ns(anchor);           \
+    } while (0)
+#else
+#define SEQ_MARK(prm, step, slot, anchor) do { } while (0)
+#endif
 
 __device__ __forceinline__ void seq_bulk_fetch(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar)
 {
@@ -544,10 +582,238 @@ __device__ __forceinline__ void stage_x_i8(unsigned char *xs, const SeqDesc &d, 
     if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);
 }
 
+// x_kind 4: X is the packed int8 copy of a step's output that the producing step made itself.
+// Word j*K + k holds rows 3j..3j+2 of column k in its low three bytes and the run's tag in the top
+// one (rows past M are zero); a thread takes whole columns, waits until their words carry `tag`
+// (bounded), and writes the column's MT tile bytes with one store.
+template <int MT>
+__device__ __forceinline__ void stage_x_packed(unsigned char *xs, const uint32_t *src, uint32_t K, uint32_t M, uint32_t tag,
+                                               bool sys, bool &ok)
+{
+    constexpr int W3 = (MT + 2) / 3;               // words per column at most
+    constexpr int U = MT == 16 ? 2 : 4;            // columns a thread has in flight
+    const uint32_t w3 = packed_words(M);
+    const uint32_t tid = threadIdx.x, nt = 512;    // consumer threads only
+    for (uint32_t k0 = tid; k0 < K; k0 += nt * U) {
+        uint32_t w[U][W3];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int j = 0; j < W3; j++) {
+                const uint32_t k = k0 + u * nt;
+                w[u][j] = (k < K && (uint32_t)j < w3) ? __ldcg(src + (size_t)j * K + k) : 0u;
+            }
+        for (uint32_t it = 0; ok; it++) {
+            bool stale = false;
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+                for (int j = 0; j < W3; j++) {
+                    const uint32_t k = k0 + u * nt;
+                    if (k < K && (uint32_t)j < w3 && (w[u][j] >> 24) != tag) {
+                        stale = true;
+                        w[u][j] = (uint32_t)ld_fresh(reinterpret_cast<const int32_t *>(src + (size_t)j * K + k), sys);
+                    }
+                }
+            if (!stale) break;
+            if (it >= kPollLimit) ok = false;
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint32_t k = k0 + u * nt;
+            if (k >= K) continue;
+            if constexpr (MT == 1) {
+                xs[k] = (unsigned char)(w[u][0] & 0xffu);
+            } else {
+                uint32_t o[MT / 4];
+#pragma unroll
+                for (int q = 0; q < MT / 4; q++) {
+                    o[q] = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int m = 4 * q + i;
+                        o[q] |= ((w[u][m / 3] >> (8 * (m % 3))) & 0xffu) << (8 * i);
+                    }
+                    o[q] ^= 0x80808080u;
+                }
+                if constexpr (MT == 4) *reinterpret_cast<uint32_t *>(xs + (size_t)k * 4) = o[0];
+                else *reinterpret_cast<uint4 *>(xs + (size_t)k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+    if (tid < (uint32_t)MT) reinterpret_cast<int8_t *>(xs)[(size_t)K * MT + tid] = tile_byte<MT>(0);      // the zero row
+}
+
 constexpr uint32_t kConsumers = 16;          // consumer warps; warp 16 is the producer
 constexpr uint32_t kConsumerThreads = kConsumers * 32;
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+
+// One arrival of this CTA at a local counter, then wait until every CTA of this GPU has arrived
+// (thread 0 polls, bounded; the others wait at the CTA barrier).  The release covers what the
+// CTA's threads wrote before the barrier in front of it.
+__device__ __forceinline__ void settle_barrier(unsigned long long *ctr, unsigned long long target, uint32_t *failed, uint32_t *status)
+{
+    consumer_sync();
+    if (threadIdx.x == 0) {
+        asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
+        if (!*failed) {
+            unsigned long long v = 0;
+            for (uint32_t it = 0; it < (1u << 21); it++) {
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
+                if (v >= target) break;
+            }
+            if (v < target) { *failed = 1; atomicOr(status, 16u); }
+        }
+    }
+    consumer_sync();
+}
+
+// x_kind 5, the settled exchange.  The producing step stored tagged int32 words (into every rank's
+// copy of the buffer, across GPUs).  Having all threads of all CTAs poll those words makes every CTA
+// hammer the same few cache lines, which is slow; here every word is watched by exactly ONE CTA of
+// each GPU: CTA c owns columns K*c/G .. K*(c+1)/G.  It waits for its columns' words (bounded), and
+//  - one row: arrives at a local counter; once all CTAs have, the row is complete in this GPU's L2
+//    and every CTA loads and quantises it without further checks;
+//  - several rows: adds its columns' row maxima to the step's maxima, arrives; once all have, it
+//    quantises ITS columns and writes them as finished tile bytes to a local buffer, arrives at a
+//    second counter, and every CTA then takes the whole tile with one bulk copy.
+// Only the tagged words cross NVLink; the counters and the tile buffer are local to each GPU.
+template <int MT>
+__device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc &d, const SeqParams &p, uint32_t s, int *red,
+                                                uint32_t xbar_a, uint32_t &xphase, uint32_t tag, bool sys, bool &ok,
+                                                uint32_t *failed, bool write_scale)
+{
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, cta = blockIdx.x, nt = kConsumerThreads;
+    const uint32_t k0 = (uint32_t)(((uint64_t)d.K * cta) / p.G), k1 = (uint32_t)(((uint64_t)d.K * (cta + 1)) / p.G), nk = k1 - k0;
+    const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
+    unsigned long long *c1 = p.settle + 2 * (size_t)s, *c2 = c1 + 1;
+    auto arrived = [&](const int32_t *w) {          // wait for one word to carry the tag; returns its value
+        int v = __ldcg(w);
+        for (uint32_t it = 0; ok && ((uint32_t)v >> 24) != tag; it++) {
+            if (it >= kPollLimit) { ok = false; break; }
+            v = ld_fresh(w, sys);
+        }
+        return untag(v);
+    };
+    if constexpr (MT == 1) {
+        for (uint32_t i = tid; i < nk; i += nt) (void)arrived(A + k0 + i);
+        if (!ok && !*failed) { *failed = 1; atomicOr(p.status, 2u); }
+        SEQ_MARK(p, s, 0, failed);
+        settle_barrier(c1, p.target_local, failed, p.status);
+        SEQ_MARK(p, s, 1, failed);
+        // the row is complete: 16-byte loads, values kept in registers between absmax and rounding
+        constexpr int V4 = 7;                              // covers K <= 14336
+        if ((d.K & 3) == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && d.K <= (uint32_t)V4 * 4 * nt) {
+            const uint32_t quads = d.K / 4;
+            int4 v[V4];
+            int amax = 0;
+#pragma unroll
+            for (int j = 0; j < V4; j++) {
+                const uint32_t q = tid + j * nt;
+                v[j] = q < quads ? __ldcg(reinterpret_cast<const int4 *>(A) + q) : make_int4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < V4; j++) {
+                v[j] = make_int4(untag(v[j].x), untag(v[j].y), untag(v[j].z), untag(v[j].w));
+                amax = max(amax, absmax4(v[j]));
+            }
+            amax = __reduce_max_sync(0xffffffffu, amax);
+            if (lane == 0) red[warp] = amax;
+            consumer_sync();
+            SEQ_MARK(p, s, 2, failed);
+            amax = 0;
+#pragma unroll
+            for (uint32_t w = 0; w < kConsumers; w++) amax = max(amax, red[w]);
+            const float scale = amax ? 127.0f / (float)amax : 0.0f;
+#pragma unroll
+            for (int j = 0; j < V4; j++) {
+                const uint32_t q = tid + j * nt;
+                if (q < quads)
+                    reinterpret_cast<uint32_t *>(xs)[q] = (uint32_t)(quant1(v[j].x, scale) & 0xff) | ((uint32_t)(quant1(v[j].y, scale) & 0xff) << 8) |
+                                                         ((uint32_t)(quant1(v[j].z, scale) & 0xff) << 16) | ((uint32_t)(quant1(v[j].w, scale) & 0xff) << 24);
+            }
+            if (tid == 0) xs[d.K] = 0;
+            if (write_scale && d.scale_out && tid == 0) d.scale_out[0] = (float)amax / 127.0f;
+        } else {
+            bool fine = true;                              // odd shapes: the general reader (every word carries the tag by now)
+            stage_x_quant<MT, true>(xs, d, p.M, red, write_scale, tag, sys, fine);
+        }
+    } else {
+        int *rowmax_s = red + 32;                          // [16]
+        uint32_t *amax_g = p.amax + ((size_t)p.run_parity * p.nsteps + s) * 16;
+        unsigned char *tile_g = p.xq + (size_t)(s & 1) * p.xq_stride;
+        if (tid < 16) rowmax_s[tid] = 0;
+        consumer_sync();
+        // my columns' words, row by row; up to VW of them stay in registers
+        constexpr int VW = 4;
+        const uint32_t words = p.M * nk;
+        int v[VW];
+#pragma unroll
+        for (int j = 0; j < VW; j++) {
+            const uint32_t i = tid + j * nt;
+            v[j] = 0;
+            if (i < words) {
+                const uint32_t m = i / nk, k = k0 + (i - m * nk);
+                v[j] = arrived(A + (size_t)m * d.ldx + k);
+                atomicMax(rowmax_s + m, abs(v[j]));
+            }
+        }
+        for (uint32_t i = tid + VW * nt; i < words; i += nt) {          // very wide slices: re-read later
+            const uint32_t m = i / nk, k = k0 + (i - m * nk);
+            atomicMax(rowmax_s + m, abs(arrived(A + (size_t)m * d.ldx + k)));
+        }
+        if (!ok && !*failed) { *failed = 1; atomicOr(p.status, 2u); }
+        consumer_sync();
+        SEQ_MARK(p, s, 0, failed);
+        if (tid < p.M && rowmax_s[tid]) atomicMax(amax_g + tid, (uint32_t)rowmax_s[tid]);
+        settle_barrier(c1, p.target_local, failed, p.status);
+        SEQ_MARK(p, s, 1, failed);
+        float *scale_s = reinterpret_cast<float *>(red);
+        if (tid < (uint32_t)MT) {
+            const uint32_t a = tid < p.M ? __ldcg(amax_g + tid) : 0u;
+            scale_s[tid] = a ? 127.0f / (float)a : 0.0f;
+            if (write_scale && d.scale_out && tid < p.M) d.scale_out[tid] = (float)a / 127.0f;
+        }
+        consumer_sync();
+        // round my columns and put them where the tile has them: byte k*MT + m, biased
+#pragma unroll
+        for (int j = 0; j < VW; j++) {
+            const uint32_t i = tid + j * nt;
+            if (i < words) {
+                const uint32_t m = i / nk, k = k0 + (i - m * nk);
+                tile_g[(size_t)k * MT + m] = (unsigned char)tile_byte<MT>(quant1(v[j], scale_s[m]));
+            }
+        }
+        for (uint32_t i = tid + VW * nt; i < words; i += nt) {
+            const uint32_t m = i / nk, k = k0 + (i - m * nk);
+            tile_g[(size_t)k * MT + m] = (unsigned char)tile_byte<MT>(quant1(untag(__ldcg(A + (size_t)m * d.ldx + k)), scale_s[m]));
+        }
+        for (uint32_t i = tid; i < ((uint32_t)MT - p.M) * nk; i += nt) {      // rows the tile has beyond M
+            const uint32_t m = p.M + i / nk, k = k0 + i % nk;
+            tile_g[(size_t)k * MT + m] = (unsigned char)tile_byte<MT>(0);
+        }
+        settle_barrier(c2, p.target_local, failed, p.status);
+        SEQ_MARK(p, s, 2, failed);
+        // the finished tile: one bulk copy (in pieces of at most 64 KB) into the tile's place
+        const uint32_t bytes = d.K * MT;
+        if (tid == 0) {
+            // the tile bytes were written by other CTAs' ordinary stores, and the tile's place in shared
+            // memory was last read by this CTA's gathers: order both before the bulk copy engine's accesses
+            asm volatile("fence.proxy.async;" ::: "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(xbar_a), "r"(bytes) : "memory");
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(xs);
+            for (uint32_t o = 0; o < bytes; o += 65536u) {
+                const uint32_t n = min(65536u, bytes - o);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(dst + o), "l"(tile_g + o), "r"(n), "r"(xbar_a) : "memory");
+            }
+        }
+        if (tid < (uint32_t)MT) xs[(size_t)d.K * MT + tid] = (unsigned char)tile_byte<MT>(0);      // the zero row
+        if (!seq_bounded_wait(xbar_a, xphase) && !*failed) { *failed = 1; atomicOr(p.status, 1u); }
+        xphase ^= 1;
+    }
+}
 
 template <int MT, bool TAGGED>
 __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_constant__ SeqParams p)
@@ -572,7 +838,13 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     __shared__ uint32_t failed;              // a bounded wait ran out somewhere in this CTA
     __shared__ __align__(16) uint32_t desc_s[2][(sizeof(SeqDesc) + 15) / 16 * 4];   // this and the next step's descriptor
     __shared__ uint32_t meta_s[2][4];        // their plan entries: b0, b1, c0, c1
-    if (tid == 0) failed = 0;
+    __shared__ __align__(8) unsigned long long xbar;        // completion of the activation tile's bulk copy (x_kind 5)
+    const uint32_t xbar_a = (uint32_t)__cvta_generic_to_shared(&xbar);
+    uint32_t xphase = 0;
+    if (tid == 0) {
+        failed = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(xbar_a) : "memory");
+    }
     if (!producer && lane == 0) {
         for (uint32_t i = 0; i < 2 * R; i++)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars_a + (warp * 2 * R + i) * 8) : "memory");
@@ -649,12 +921,15 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
 
     for (uint32_t s = 0; s < p.nsteps; s++) {
         // descriptor and plan entries of this step: put in shared memory during the previous step
-        const SeqDesc d = *reinterpret_cast<const SeqDesc *>(desc_s[s & 1]);
+        // (read in place: a private copy of the descriptor would live in local memory)
+        const SeqDesc &d = *reinterpret_cast<const SeqDesc *>(desc_s[s & 1]);
         const uint32_t b0 = meta_s[s & 1][0], b1 = meta_s[s & 1][1], c0 = meta_s[s & 1][2], c1 = meta_s[s & 1][3];
         int *c_s = c_base + (s & 1) * (size_t)p.max_cols * MT;
+#ifdef SPTMM_TUNING
         const bool tracing = p.trace != nullptr && cta == 0 && tid == 33 && s < 256;
+#endif
         // ---- wait until the step this one depends on has finished everywhere
-        if (d.dep >= 0 && !(TAGGED && d.x_kind == 2)) {     // tagged inputs are waited for word by word while staging
+        if (d.dep >= 0 && !(TAGGED && (d.x_kind == 2 || d.x_kind == 4 || d.x_kind == 5))) {     // tagged inputs are waited for word by word while staging
             if (tid == 0 && !failed) {
                 const unsigned long long *ctr = p.counters + d.dep;
                 unsigned long long v = 0;
@@ -667,8 +942,8 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             }
             consumer_sync();
         }
+#ifdef SPTMM_TUNING
         if (tracing) p.trace[s * 4 + 0] = seq_ns(&failed);
-#ifdef SPTMM_SEQ_PROFILE
         if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
             p.trace[1024 + 64 + (s - 100) * 16 + warp] = seq_ns(&failed);
         if (p.trace != nullptr && tid == 33 && s >= 100 && s < 104) p.trace[2048 + (s - 100) * 256 + cta] = seq_ns(&failed);   // every CTA: past the wait
@@ -685,6 +960,19 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         if (TAGGED && p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
             p.amax[((p.run_parity ^ 1u) * p.nsteps + s) * 16 + tid] = 0u;
         if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
+        else if (TAGGED && d.x_kind == 5) {
+            bool fresh = failed == 0;
+            const uint32_t tag = seq_tag(p.run_mod, d.in_tag_m, d.in_tag_j);
+            // odd shapes (a tile that is no whole number of 16-byte pieces) take the polling reader
+            if (MT > 1 && ((d.K * MT) & 15)) stage_x_quant<MT, TAGGED>(xs, d, p.M, red, cta == 0, tag, p.n_peers != 0, fresh);
+            else stage_x_settled<MT>(xs, d, p, s, red, xbar_a, xphase, tag, p.n_peers != 0, fresh, &failed, cta == 0);
+            if (!fresh && !failed) { failed = 1; atomicOr(p.status, 2u); }
+        }
+        else if (TAGGED && d.x_kind == 4) {
+            bool fresh = failed == 0;
+            stage_x_packed<MT>(xs, reinterpret_cast<const uint32_t *>(d.X), d.K, p.M, 1u + p.run_mod, p.n_peers != 0, fresh);
+            if (!fresh && !failed) { failed = 1; atomicOr(p.status, 2u); }
+        }
         else if (TAGGED && d.x_kind == 3) stage_x_scaled<MT>(xs, d, p.M, p.amax + ((size_t)p.run_parity * p.nsteps + (uint32_t)d.dep) * 16, cta == 0);
         else {
             bool fresh = failed == 0;          // after a failure nothing waits any more
@@ -692,7 +980,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             stage_x_quant<MT, TAGGED>(xs, d, p.M, red, cta == 0, tag, p.n_peers != 0, fresh);
             if (!fresh && !failed) { failed = 1; atomicOr(p.status, 2u); }      // a producer's word never arrived
         }
-#ifdef SPTMM_SEQ_PROFILE
+#ifdef SPTMM_TUNING
         if (p.trace != nullptr && cta == 0 && lane == 1 && s >= 100 && s < 104)
             p.trace[1024 + (s - 100) * 16 + warp] = seq_ns(&failed) + (xs[tid] == 77 && xs[tid + 1] == 78 && xs[tid + 2] == 99);
 #endif
@@ -702,8 +990,8 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_a + held_slot * 8) : "memory");
             held_slot = -1;
         }
+#ifdef SPTMM_TUNING
         if (tracing) p.trace[s * 4 + 1] = seq_ns(&failed);
-#ifdef SPTMM_SEQ_PROFILE
         if (p.trace != nullptr && tid == 33 && s >= 100 && s < 104) p.trace[3072 + (s - 100) * 256 + cta] = seq_ns(&failed);   // every CTA: X staged
 #endif
 
@@ -789,10 +1077,87 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         }
         if (s + 1 < p.nsteps) store_step_word(s + 1, nxt);
         consumer_sync();
+#ifdef SPTMM_TUNING
         if (tracing) p.trace[s * 4 + 2] = seq_ns(&failed);
-#ifdef SPTMM_SEQ_PROFILE
         if (p.trace != nullptr && tid == 33 && s >= 100 && s < 104) p.trace[4096 + (s - 100) * 256 + cta] = seq_ns(&failed);   // every CTA: gathered
 #endif
+
+        // what goes out: every column's sum, or (c_kind 1) the sums of neighbouring column pairs;
+        // the plan gives a pair-summing step even column boundaries
+        const uint32_t nout = d.c_kind ? ncols / 2 : ncols, o0 = d.c_kind ? c0 / 2 : c0;
+        auto value = [&](uint32_t j, uint32_t m) { return d.c_kind ? c_s[(2 * j) * MT + m] + c_s[(2 * j + 1) * MT + m] : c_s[j * MT + m]; };
+
+        // ---- producer-side quantiser (see SeqDesc::q_n): two hand-overs, all consumer warps
+        if (TAGGED && d.q_n) {
+            const uint32_t qtag = (1u + p.run_mod) << 24;
+            const uint32_t ranks = p.n_peers ? p.n_peers : 1u;
+            auto area = [&](uint32_t r) { return reinterpret_cast<unsigned char *>(p.n_peers ? p.counter_peers[r] : p.counters); };
+            unsigned char *own = reinterpret_cast<unsigned char *>(p.counters);
+            // own output columns inside the range, in this step's local column numbers
+            const int lo = max((int)o0, d.q_0), hi = min((int)(o0 + nout), d.q_0 + (int)d.q_n);
+            float *scale_s = reinterpret_cast<float *>(red);
+            if (warp < p.M) {                  // warp r looks after row r
+                uint32_t mx = 0;
+                for (int c = lo + (int)lane; c < hi; c += 32) mx = max(mx, (uint32_t)abs(value((uint32_t)c - o0, warp)));
+                mx = __reduce_max_sync(0xffffffffu, mx);
+                // every CTA's maximum of the row, as a tagged word of its own: no counter, no fence
+                uint32_t *amax1 = reinterpret_cast<uint32_t *>(own + d.amax1_off) + warp * kAmaxStride;
+                if (lane == 0) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(amax1 + cta), "r"(qtag | mx) : "memory");
+                bool okq = failed == 0;
+                uint32_t g = 0;
+                for (uint32_t c = lane; c < p.G; c += 32) {
+                    uint32_t v = (uint32_t)ld_fresh(reinterpret_cast<const int32_t *>(amax1 + c), false);
+                    for (uint32_t it = 0; okq && (v & 0xff000000u) != qtag; it++) {
+                        if (it >= kPollLimit) { okq = false; break; }
+                        v = (uint32_t)ld_fresh(reinterpret_cast<const int32_t *>(amax1 + c), false);
+                    }
+                    g = max(g, v & 0xffffffu);
+                }
+                g = __reduce_max_sync(0xffffffffu, g);
+                if (p.n_peers > 1) {
+                    // between GPUs: CTA r of every rank tells rank r this GPU's maxima; everybody then reads its
+                    // own rank's table of the n_peers GPUs' values
+                    if (cta < p.n_peers && lane == 0) {
+                        uint32_t *dst = reinterpret_cast<uint32_t *>(area(cta) + d.amax2_off) + warp * kMaxPeers + p.my_rank;
+                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(qtag | g) : "memory");
+                    }
+                    const uint32_t *amax2 = reinterpret_cast<const uint32_t *>(own + d.amax2_off) + warp * kMaxPeers;
+                    uint32_t v = qtag;
+                    if (lane < p.n_peers) {
+                        v = (uint32_t)ld_fresh(reinterpret_cast<const int32_t *>(amax2 + lane), true);
+                        for (uint32_t it = 0; okq && (v & 0xff000000u) != qtag; it++) {
+                            if (it >= kPollLimit) { okq = false; break; }
+                            v = (uint32_t)ld_fresh(reinterpret_cast<const int32_t *>(amax2 + lane), true);
+                        }
+                    }
+                    g = __reduce_max_sync(0xffffffffu, v & 0xffffffu);
+                }
+                if (!__all_sync(0xffffffffu, okq) && lane == 0 && !failed) { failed = 1; atomicOr(p.status, 8u); }
+                if (lane == 0) {
+                    scale_s[warp] = g ? 127.0f / (float)g : 0.0f;
+                    if (cta == 0 && d.q_scale_out) d.q_scale_out[warp] = (float)g / 127.0f;
+                }
+            }
+            consumer_sync();
+            // round this CTA's columns and hand them to every rank: three rows and the tag per word
+            const uint32_t w3 = packed_words(p.M);
+            const uint32_t nq = hi > lo ? (uint32_t)(hi - lo) : 0u;
+            for (uint32_t i = tid; i < nq * w3; i += kConsumerThreads) {
+                const uint32_t j = i / nq, c = (uint32_t)lo + (i - j * nq);
+                uint32_t word = qtag;
+#pragma unroll
+                for (uint32_t t = 0; t < 3; t++) {
+                    const uint32_t m = 3 * j + t;
+                    if (m < p.M) word |= ((uint32_t)quant1(value(c - o0, m), scale_s[m]) & 0xffu) << (8 * t);
+                }
+                const size_t at = (size_t)j * d.q_n + (uint32_t)((int)c - d.q_0);
+                for (uint32_t r = 0; r < ranks; r++) {
+                    uint32_t *dst = reinterpret_cast<uint32_t *>(area(r) + d.q_off) + at;
+                    if (p.n_peers) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(word) : "memory");
+                    else asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(dst), "r"(word) : "memory");
+                }
+            }
+        }
 
         // ---- results out, then tell the other CTAs this step is done here.  Warp 0 does it alone
         // while the others move on (the next step accumulates into the other buffer).
@@ -801,10 +1166,6 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             const bool tag_out = TAGGED && d.out_tag_m != 0;
             const uint32_t otag = tag_out ? seq_tag(p.run_mod, d.out_tag_m, d.out_tag_j) << 24 : 0u;
             auto out_word = [&](int v) { return tag_out ? (int)(otag | ((uint32_t)v & 0xffffffu)) : v; };
-            // what goes out: every column's sum, or (c_kind 1) the sums of neighbouring column pairs;
-            // the plan gives a pair-summing step even column boundaries
-            const uint32_t nout = d.c_kind ? ncols / 2 : ncols, o0 = d.c_kind ? c0 / 2 : c0;
-            auto value = [&](uint32_t j, uint32_t m) { return d.c_kind ? c_s[(2 * j) * MT + m] + c_s[(2 * j + 1) * MT + m] : c_s[j * MT + m]; };
             for (uint32_t i = lane; i < nout * p.M; i += 32) {
                 const uint32_t m = i / nout, j = i - m * nout;
                 const int wv = out_word(value(j, m));
@@ -835,7 +1196,9 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p.counter_peers[lane] + s) : "memory");
             }
         }
+#ifdef SPTMM_TUNING
         if (tracing) p.trace[s * 4 + 3] = seq_ns(&failed);
+#endif
     }
 }
 
@@ -852,6 +1215,8 @@ struct sptmm_seq {
     uint64_t epoch = 0;
     void *d_desc = nullptr, *d_blk = nullptr, *d_col = nullptr, *d_counters = nullptr, *d_status = nullptr;
     void *d_trace = nullptr;
+    void *d_xq = nullptr;            // x_kind 5: two local buffers for the finished int8 tile
+    uint32_t xq_stride = 0;
     uint32_t n_peers = 0, my_rank = 0;
     bool tagged = false;             // some step reads tagged words: run the kernel variant that knows them
     bool uses_amax = false;          // some step is x_kind 3: the row-maxima area is in use
@@ -861,9 +1226,7 @@ struct sptmm_seq {
 // Shallow rings stream best: three 4 KB slots per warp reach the HBM rate, deeper ones lose it.
 static size_t seq_ring_cap()
 {
-    const char *e = getenv("SPTMM_SEQ_RING");
-    const int v = e ? atoi(e) : 3;
-    return (size_t)std::max(2, std::min(v, 24));
+    return (size_t)std::max(2L, std::min(tuning_knob("SPTMM_SEQ_RING", 3), 24L));
 }
 
 static void seq_release(sptmm_seq *q)
@@ -873,10 +1236,37 @@ static void seq_release(sptmm_seq *q)
         int cur = 0;
         cudaGetDevice(&cur);
         cudaSetDevice(q->device);
-        for (void *p : {q->d_desc, q->d_blk, q->d_col, q->d_counters, q->d_status}) if (p) cudaFree(p);
+        for (void *p : {q->d_desc, q->d_blk, q->d_col, q->d_counters, q->d_status, q->d_xq}) if (p) cudaFree(p);
         cudaSetDevice(cur);
     }
     delete q;
+}
+
+// The synchronisation area of one rank: step counters (n x u64), the row maxima of x_kind 3
+// (2 halves x n steps x 16 rows x u32), then, for every step that quantises its own output for an
+// x_kind 4 reader, its tables of row maxima and its packed int8 output.  The same on every rank.
+struct SeqLayout {
+    std::vector<uint32_t> q_n, q_off, amax1_off, amax2_off;     // per producing step (q_n == 0: none)
+    uint64_t bytes = 0;
+};
+
+static SeqLayout seq_layout(const sptmm_seq_step *steps, uint32_t n, uint32_t M)
+{
+    SeqLayout L;
+    L.q_n.assign(n, 0); L.q_off.assign(n, 0); L.amax1_off.assign(n, 0); L.amax2_off.assign(n, 0);
+    uint64_t at = (uint64_t)n * 8 + (uint64_t)2 * n * 16 * 4 + (uint64_t)n * 16;      // = sptmm_seq_shared_bytes(n)
+    for (uint32_t s = 0; s < n; s++)
+        if (steps[s].x_kind == 4 && steps[s].dep >= 0 && (uint32_t)steps[s].dep < s && steps[s].w)
+            L.q_n[(uint32_t)steps[s].dep] = steps[s].w->K;
+    for (uint32_t s = 0; s < n; s++) {
+        if (!L.q_n[s]) continue;
+        at = (at + 255) & ~(uint64_t)255;
+        L.amax1_off[s] = (uint32_t)at; at += (uint64_t)16 * kAmaxStride * 4;
+        L.amax2_off[s] = (uint32_t)at; at += (uint64_t)16 * kMaxPeers * 4;
+        L.q_off[s] = (uint32_t)at; at += (uint64_t)packed_words(M) * L.q_n[s] * 4;
+    }
+    L.bytes = (at + 255) & ~(uint64_t)255;
+    return L;
 }
 
 static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, void *const *C_peers,
@@ -907,7 +1297,9 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         if (!w || !st.X || (!st.C && !n_peers)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u has a null pointer", s);
         else if (w->format != SPTMM_FMT_U16_V256) rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u is not in the native u16 format", s);
         else if (w->device != dev || st.replica >= w->dev.size()) rc = fail(SPTMM_ERR_STATE, "seq_create: step %u weights are not uploaded to device %d (replica %u)", s, dev, st.replica);
-        else if (st.x_kind > 3) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
+        else if (st.x_kind > 5) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
+        else if (st.x_kind == 5 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 5) needs a producer (dep) and takes no X2", s);
+        else if (st.x_kind == 4 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 4) needs a producer (dep) and takes no X2", s);
         else if (st.x_kind == 3 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 3) needs a producer (dep) and takes no X2", s);
         else if (st.c_kind > 1 || (st.c_kind == 1 && (w->N & 1))) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u c_kind %u (pair sums need an even N)", s, st.c_kind);
         else if (st.x_kind == 2 && st.dep < 0) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u reads tagged words but names no producer (dep)", s);
@@ -942,15 +1334,15 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
     {
         std::vector<char> tagged(n, 0);
         for (uint32_t s = 0; s < n; s++)
-            if (steps[s].x_kind == 2) { tagged[(uint32_t)steps[s].dep] = 1; q->tagged = true; }
+            if (steps[s].x_kind == 2 || steps[s].x_kind == 5) { tagged[(uint32_t)steps[s].dep] = 1; q->tagged = true; }
         int rc = SPTMM_OK;
         for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++) {
             desc[s].release = tagged[s] ? 0 : 1;
             if (steps[s].x_kind == 3) { desc[(uint32_t)steps[s].dep].want_amax = 1; q->uses_amax = true; }
             if (tagged[s] && desc[s].c_kind && desc[s].K > 33000)
                 rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u: pair sums over K=%u rows do not fit a tagged word", s, desc[s].K);
-            if (steps[s].x_kind != 2 && steps[s].dep >= 0 && tagged[(uint32_t)steps[s].dep])
-                rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u waits for step %d, whose output is tagged for an x_kind 2 reader", s, steps[s].dep);
+            if (steps[s].x_kind != 2 && steps[s].x_kind != 5 && steps[s].x_kind != 4 && steps[s].dep >= 0 && tagged[(uint32_t)steps[s].dep])
+                rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u waits for step %d, whose output is tagged for an x_kind 2 or 5 reader", s, steps[s].dep);
             if (!tagged[s]) continue;
             uint32_t m = 0, j = 0;
             for (uint32_t t = 0; t < n; t++)
@@ -962,7 +1354,7 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
             desc[s].out_tag_m = m; desc[s].out_tag_j = j;
         }
         for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++)
-            if (steps[s].x_kind == 2) {
+            if (steps[s].x_kind == 2 || steps[s].x_kind == 5) {
                 const SeqDesc &pd = desc[(uint32_t)steps[s].dep];
                 desc[s].in_tag_m = pd.out_tag_m; desc[s].in_tag_j = pd.out_tag_j;
                 // the producer's rows are ldc wide and its columns (one shard of them, on several
@@ -972,6 +1364,46 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
                 if (x < lo || x >= hi || (x2 && (x2 < lo || x2 >= hi)))
                     rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u reads tagged words outside the output of step %d", s, steps[s].dep);
             }
+        if (rc != SPTMM_OK) { seq_release(q); return rc; }
+    }
+
+    // Producer-side quantiser: an x_kind 4 step makes the step it names in `dep` quantise the
+    // columns it reads.  Its X names those columns inside the producer's output (that is how the
+    // range is given); what the kernel reads instead is the producer's packed copy in the
+    // synchronisation area, patched in below once that area's address is known.
+    const SeqLayout layout = seq_layout(steps, n, M);
+    {
+        int rc = SPTMM_OK;
+        bool any_q = false;
+        for (uint32_t s = 0; s < n; s++) any_q = any_q || layout.q_n[s] != 0;
+        if (any_q && (uint32_t)sms > kAmaxStride)
+            rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: %d SMs, the row-maxima tables plan for at most %u", sms, kAmaxStride);
+        for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++) {
+            if (steps[s].x_kind != 4) continue;
+            const uint32_t pr = (uint32_t)steps[s].dep;
+            SeqDesc &pd = desc[pr];
+            const long long diff = (const char *)steps[s].X - (const char *)pd.C;
+            if (diff % 4 || diff / 4 < -(1 << 24) || diff / 4 > (1 << 24))
+                rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 4) does not read inside the output of step %u", s, pr);
+            else if (pd.q_n && (pd.q_n != desc[s].K || pd.q_0 != (int32_t)(diff / 4)))
+                rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: steps reading step %u quantised must read the same columns", pr);
+            else if (2ull * 127 * pd.K >= (1ull << 24))
+                rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u: K=%u is too long for 24-bit row maxima", pr, pd.K);
+            else {
+                pd.q_n = desc[s].K; pd.q_0 = (int32_t)(diff / 4);
+                pd.q_off = layout.q_off[pr]; pd.amax1_off = layout.amax1_off[pr]; pd.amax2_off = layout.amax2_off[pr];
+                pd.q_scale_out = steps[s].scale_out;
+                q->tagged = true;                       // the kernel variant that knows the exchanges
+            }
+        }
+        // a step bumps its counter only if somebody waits for it there (the release stalls warp 0
+        // until its stores have landed, on every rank)
+        for (uint32_t s = 0; s < n; s++) {
+            bool waited = false;
+            for (uint32_t t = s + 1; t < n; t++)
+                if (steps[t].dep == (int32_t)s && steps[t].x_kind != 2 && steps[t].x_kind != 4 && steps[t].x_kind != 5) waited = true;
+            if (!waited) desc[s].release = 0;
+        }
         if (rc != SPTMM_OK) { seq_release(q); return rc; }
     }
 
@@ -996,31 +1428,53 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
     o = (o + 127) & ~(size_t)127;
     q->smem = 1024 + o + (size_t)nwarps * q->ring_slots * slot_bytes;
 
-    cudaError_t e = cudaMalloc(&q->d_desc, n * sizeof(SeqDesc));
-    if (e == cudaSuccess) e = cudaMemcpy(q->d_desc, desc.data(), n * sizeof(SeqDesc), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMalloc(&q->d_blk, blk.size() * 4);
-    if (e == cudaSuccess) e = cudaMemcpy(q->d_blk, blk.data(), blk.size() * 4, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMalloc(&q->d_col, col.size() * 4);
-    if (e == cudaSuccess) e = cudaMemcpy(q->d_col, col.data(), col.size() * 4, cudaMemcpyHostToDevice);
     q->n_peers = n_peers; q->my_rank = my_rank;
+    cudaError_t e = cudaSuccess;
     if (n_peers) {                    // counters live in peer-mapped memory the caller owns and zeroed
         for (uint32_t r = 0; r < n_peers; r++) {
             if (!counter_peers[r]) { seq_release(q); return fail(SPTMM_ERR_INVALID, "seq_create: no counters for rank %u", r); }
             q->counter_peers[r] = counter_peers[r];
         }
     } else {
-        if (e == cudaSuccess) e = cudaMalloc(&q->d_counters, sptmm_seq_shared_bytes(n));
-        if (e == cudaSuccess) e = cudaMemset(q->d_counters, 0, sptmm_seq_shared_bytes(n));
+        e = cudaMalloc(&q->d_counters, layout.bytes);
+        if (e == cudaSuccess) e = cudaMemset(q->d_counters, 0, layout.bytes);
     }
+    const char *own_area = (const char *)(n_peers ? counter_peers[my_rank] : q->d_counters);
+    for (uint32_t s = 0; s < n; s++)
+        if (steps[s].x_kind == 4) desc[s].X = own_area + desc[(uint32_t)steps[s].dep].q_off;
+    if (e == cudaSuccess) e = cudaMalloc(&q->d_desc, n * sizeof(SeqDesc));
+    if (e == cudaSuccess) e = cudaMemcpy(q->d_desc, desc.data(), n * sizeof(SeqDesc), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&q->d_blk, blk.size() * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(q->d_blk, blk.data(), blk.size() * 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMalloc(&q->d_col, col.size() * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(q->d_col, col.data(), col.size() * 4, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMalloc(&q->d_status, 16);
     if (e == cudaSuccess) e = cudaMemset(q->d_status, 0, 16);
+    {
+        uint32_t k5 = 0;                                     // longest row any settled-exchange step reads
+        for (uint32_t s = 0; s < n; s++)
+            if (steps[s].x_kind == 5) k5 = std::max(k5, desc[s].K);
+        if (k5) {
+            if (q->mt > 1) q->uses_amax = true;              // the steps' row maxima live in that area
+            q->xq_stride = (uint32_t)(((size_t)k5 * q->mt + 255) & ~(size_t)255);
+            if (e == cudaSuccess) e = cudaMalloc(&q->d_xq, 2 * (size_t)q->xq_stride);
+        }
+    }
     if (e != cudaSuccess) { seq_release(q); return fail(SPTMM_ERR_CUDA, "seq_create: %s", cudaGetErrorString(e)); }
     *out = q;
     return SPTMM_OK;
 }
 
 // step counters (n x u64), then the row maxima (2 halves x n steps x 16 rows x u32)
-extern "C" uint64_t sptmm_seq_shared_bytes(uint32_t n_steps) { return (uint64_t)n_steps * 8 + (uint64_t)2 * n_steps * 16 * 4; }
+// and two local arrival counters per step (x_kind 5)
+static uint64_t seq_settle_offset(uint32_t n_steps) { return (uint64_t)n_steps * 8 + (uint64_t)2 * n_steps * 16 * 4; }
+extern "C" uint64_t sptmm_seq_shared_bytes(uint32_t n_steps) { return seq_settle_offset(n_steps) + (uint64_t)n_steps * 16; }
+
+extern "C" uint64_t sptmm_seq_shared_bytes_for(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M)
+{
+    if (!steps || n_steps == 0 || M == 0 || M > 16) return 0;
+    return seq_layout(steps, n_steps, M).bytes;
+}
 
 extern "C" int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n, uint32_t M, sptmm_seq **out)
 {
@@ -1048,10 +1502,10 @@ static int seq_launch(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
 template <int MT, bool TAGGED>
 static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
 {
-    static int configured_device = -1;
-    if (configured_device != q->device) {
+    static std::atomic<int> configured_device{-1};     // host threads may launch concurrently
+    if (configured_device.load(std::memory_order_acquire) != q->device) {
         SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_seq<MT, TAGGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-        configured_device = q->device;
+        configured_device.store(q->device, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(q->G); cfg.blockDim = dim3(q->threads); cfg.dynamicSmemBytes = q->smem; cfg.stream = st;
@@ -1076,7 +1530,9 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     prm.cta_col = (const uint32_t *)q->d_col;
     prm.counters = (unsigned long long *)q->d_counters;
     prm.status = (uint32_t *)q->d_status;
+#ifdef SPTMM_TUNING
     prm.trace = (unsigned long long *)q->d_trace;
+#endif
     prm.n_peers = q->n_peers;
     for (uint32_t r = 0; r < kMaxPeers; r++) prm.counter_peers[r] = (unsigned long long *)q->counter_peers[r];
     if (q->n_peers) prm.counters = prm.counter_peers[q->my_rank];
@@ -1086,6 +1542,10 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     prm.xs_bytes = q->xs_bytes; prm.G = q->G; prm.slot_blocks = q->slot_blocks; prm.one = 1;
     prm.run_mod = (uint32_t)(q->epoch % 255);
     prm.run_parity = (uint32_t)(q->epoch & 1);
+    prm.my_rank = q->my_rank;
+    prm.settle = (unsigned long long *)((char *)prm.counters + seq_settle_offset(q->nsteps));
+    prm.xq = (unsigned char *)q->d_xq; prm.xq_stride = q->xq_stride;
+    prm.target_local = (unsigned long long)q->G * q->epoch;
     // the row maxima sit behind the counters; a sequence without x_kind 3 steps never touches them
     for (uint32_t r = 0; r < kMaxPeers; r++)
         prm.amax_peers[r] = q->uses_amax && q->counter_peers[r] ? (uint32_t *)((char *)q->counter_peers[r] + (size_t)q->nsteps * 8) : nullptr;
@@ -1110,12 +1570,14 @@ extern "C" int sptmm_seq_status(sptmm_seq *q, uint32_t *status, uint64_t *stream
     return SPTMM_OK;
 }
 
+#ifdef SPTMM_TUNING
 extern "C" int sptmm_seq_set_trace(sptmm_seq *q, void *dev_ptr)
 {
     if (!q) return fail(SPTMM_ERR_INVALID, "seq_set_trace: null handle");
     q->d_trace = dev_ptr;
     return SPTMM_OK;
 }
+#endif
 
 extern "C" int sptmm_seq_free(sptmm_seq *q)
 {
@@ -1158,16 +1620,21 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
     // the address a kernel can use has to be asked for.
     static unsigned char *scratch_of[64] = {};
     static int sms_of[64] = {};
-    if (!scratch_of[dev]) {
-        void *p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_seq_static_scratch);
-        if (e != cudaSuccess || !p) return fail(SPTMM_ERR_CUDA, "seq_run_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        SPTMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        sms_of[dev] = sms;
-        scratch_of[dev] = (unsigned char *)p;
+    static std::mutex setup_lock;                  // host threads may make their first calls at the same time
+    unsigned char *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(setup_lock);
+        if (!scratch_of[dev]) {
+            void *p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_seq_static_scratch);
+            if (e != cudaSuccess || !p) return fail(SPTMM_ERR_CUDA, "seq_run_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            SPTMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            sms_of[dev] = sms;
+            scratch_of[dev] = (unsigned char *)p;
+        }
+        sms = sms_of[dev];
+        scratch = scratch_of[dev];
     }
-    sms = sms_of[dev];
-    unsigned char *scratch = scratch_of[dev];
     if ((uint32_t)sms > kStaticMaxCtas)
         return fail(SPTMM_ERR_UNSUPPORTED, "seq_run_static: %d SMs, the fixed scratch plans for at most %u", sms, kStaticMaxCtas);
 
@@ -1219,6 +1686,12 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
 
     // tables in, and what must start at zero cleared: the array keeps the previous call's contents
     cudaStream_t st = (cudaStream_t)stream;
+    // The table copies below read host vectors that die with this call, and a status request waits
+    // for the stream: neither survives being recorded into a graph, so a capturing stream is refused.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    SPTMM_CUDA_TRY(cudaStreamIsCapturing(st, &capturing));
+    if (capturing != cudaStreamCaptureStatusNone)
+        return fail(SPTMM_ERR_STATE, "seq_run_static: the stream is being captured; this call copies per-call tables from host memory and cannot be recorded");
     SPTMM_CUDA_TRY(cudaMemcpyAsync(scratch + kStaticDescOff, desc.data(), n * sizeof(SeqDesc), cudaMemcpyHostToDevice, st));
     SPTMM_CUDA_TRY(cudaMemcpyAsync(scratch + kStaticBlkOff, blk.data(), blk.size() * 4, cudaMemcpyHostToDevice, st));
     SPTMM_CUDA_TRY(cudaMemcpyAsync(scratch + kStaticColOff, col.data(), col.size() * 4, cudaMemcpyHostToDevice, st));
@@ -1232,10 +1705,13 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
     for (uint32_t r = 0; r < kMaxPeers; r++) prm.counter_peers[r] = nullptr;
     prm.n_peers = 0;
     prm.status = (uint32_t *)(scratch + kStaticStatusOff);
+#ifdef SPTMM_TUNING
     prm.trace = nullptr;
+#endif
     prm.target = q.G;                              // counters were just cleared: one run's worth
     prm.nsteps = n; prm.M = M; prm.max_cols = q.max_cols; prm.ring_slots = q.ring_slots;
-    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1; prm.run_mod = 0; prm.run_parity = 0; prm.amax = nullptr;
+    prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1; prm.run_mod = 0; prm.run_parity = 0; prm.amax = nullptr; prm.my_rank = 0;
+    prm.settle = nullptr; prm.xq = nullptr; prm.xq_stride = 0; prm.target_local = 0;
     for (uint32_t r = 0; r < kMaxPeers; r++) prm.amax_peers[r] = nullptr;
     int rc = SPTMM_OK;
     switch (q.mt) {

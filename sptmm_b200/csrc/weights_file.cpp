@@ -157,6 +157,14 @@ extern "C" int sptmm_weights_load(const char *path, sptmm_weights **out)
             for (size_t l = 0; good && l < 2 * (size_t)w->N; l++) good = off[l] <= off[l + 1];
         }
         if (!good) return fail(SPTMM_ERR_INVALID, "weights_load: the block table of %s does not match its arrays", path);
+        // The kernels divide block numbers by uniform_nbl to find a column, so it is never taken from
+        // the file: it follows from the block table exactly as the encoder derives it.
+        const uint32_t *off = reinterpret_cast<const uint32_t *>(w->arrays[1].data.data());
+        uint32_t nbl = off[1] - off[0];
+        for (size_t l = 0; l < 2 * (size_t)w->N; l++)
+            if (off[l + 1] - off[l] != nbl) { nbl = 0; break; }
+        if (w->uniform_nbl != nbl || w->entries_per_block != 256)
+            return fail(SPTMM_ERR_INVALID, "weights_load: the header of %s disagrees with its block table", path);
     } else {
         const size_t half = w->S / 2;
         size_t want = 0, count = 2;

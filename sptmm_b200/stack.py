@@ -49,17 +49,32 @@ def stack_weights(layers: int, hidden: int, ffn: int, kv: int, p_zero: float, se
 
 class TernaryStack:
     def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, M=1, p_zero=1 / 3, seed=0,
-                 rank=0, world=1, group=None, keep_dense=False, tagged=None, row_maxima=False):
+                 rank=0, world=1, group=None, keep_dense=False, tagged=None, row_maxima=False, producer_quant=None,
+                 settled=None):
         import torch
         self.torch = torch
         self.layers, self.hidden, self.ffn, self.kv, self.M = layers, hidden, ffn, kv, M
         self.rank, self.world = rank, world
-        # Steps can hand their outputs on as tagged words (x_kind 2: no counters, no fences).  Measured
-        # on B200: across GPUs that beats the step counters for M <= 4 (2 GPUs, M=1: 1.20 ms per
-        # pass against 1.51 ms), on one GPU and for M=16 it does not; None picks accordingly.
-        if tagged is None:
-            tagged = world > 1 and M <= 4
-        self.tagged = tagged
+        # How a step's int32 output becomes the next step's int8 input:
+        #  - producer_quant (x_kind 4): the producing step quantises its own columns after a small
+        #    exchange of row maxima and stores int8; readers fetch M*K bytes.  For M >= 4 (None picks
+        #    it there), where every CTA quantising all M rows for itself is what a step costs.
+        #  - tagged (x_kind 2): readers quantise; outputs travel as tagged words, no counters, no
+        #    fences.  Measured on B200: across GPUs that beats the step counters for M <= 4 (2 GPUs,
+        #    M=1: 1.20 ms per pass against 1.51 ms), on one GPU it does not; None picks accordingly.
+        #  - settled (x_kind 5): tagged words as above, but every word is watched by one CTA per GPU,
+        #    the CTAs of a GPU meet at local counters, and for M > 1 each CTA quantises only its own
+        #    columns into a local int8 tile that all fetch with one bulk copy.
+        explicit = tagged is not None or producer_quant is not None or row_maxima
+        if settled is None:
+            settled = not explicit
+        if producer_quant is None:
+            producer_quant = False
+        if settled:
+            tagged, producer_quant = True, False         # the producers store tagged words
+        elif tagged is None:
+            tagged = world > 1 and M <= 4 and not producer_quant
+        self.tagged, self.producer_quant, self.settled = tagged, producer_quant, settled
         self.dense = [] if keep_dense else None
         shapes = layer_shapes(hidden, ffn, kv)
         widths = {name: N for name, _, N in shapes}
@@ -81,7 +96,11 @@ class TernaryStack:
         # ---- activation buffers (full width on every rank) and step counters in one arena
         n_steps = 4 * layers
         off, cur = {}, 0
-        off["counters"] = cur; cur += int(sp.lib.sptmm_seq_shared_bytes(n_steps))      # step counters + row maxima
+        # step counters + row maxima (+ the producers' packed int8 outputs): the size depends on the
+        # step kinds and shapes only, so a list without buffer addresses gives it
+        xk = 5 if settled else (4 if producer_quant else (2 if tagged else 1))
+        sizing = [{"w": self.weights[s], "X": 1, "C": 1, "dep": s - 1, "x_kind": (0 if s == 0 else xk)} for s in range(n_steps)]
+        off["counters"] = cur; cur += int(sp.seq_shared_bytes(sizing, M))
         widths["gu"] = ffn                       # stored as pair sums
         widths["out"] = widths["down"]           # the last step's result: never tagged, no reader inside the kernel
         for name in ("qkv", "o", "gu", "down", "out"):
@@ -106,8 +125,8 @@ class TernaryStack:
 
         # ---- the step list
         steps = []
-        xk = 2 if tagged else 1                  # a reader of part of a row finds the row's absmax itself
-        xw = 2 if tagged else (3 if row_maxima else 1)    # row_maxima: a reader of a whole row gets its absmax from the producer
+        xk = 5 if settled else (4 if producer_quant else (2 if tagged else 1))       # a reader of part of a row finds the row's absmax itself
+        xw = 5 if settled else (4 if producer_quant else (2 if tagged else (3 if row_maxima else 1)))    # row_maxima: a reader of a whole row gets its absmax from the producer
         for l in range(layers):
             for i, (name, K, N) in enumerate(shapes):
                 s = 4 * l + i

@@ -48,9 +48,11 @@ def gpu_parity():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
     layers, hidden, ffn, kv = 3, 256, 512, 64
-    for M, tagged, row_maxima in ((1, False, False), (4, False, True), (1, True, False), (4, True, False)):
+    for M, tagged, row_maxima, pq in ((1, False, False, False), (4, False, True, False), (1, True, False, False), (4, True, False, False),
+                                      (1, False, False, True), (4, False, False, True), (16, False, False, True),
+                                      (1, None, False, None), (3, None, False, None), (4, None, False, None), (16, None, False, None)):
         st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, rank=rank, world=world, keep_dense=True,
-                            tagged=tagged, row_maxima=row_maxima)
+                            tagged=tagged, row_maxima=row_maxima, producer_quant=pq)
         x = O.gen_x_i8(M * hidden, 9).reshape(M, hidden)
         st.set_input(x)
         want = S.reference_forward(st.dense, layers, hidden, ffn, kv, x, O.gemv_i8_dense, O.quant_absmax_i8)
@@ -61,7 +63,7 @@ def gpu_parity():
             assert st.status() == 0, "a bounded wait ran out on rank %d" % rank
             dist.barrier()
             for name in ("qkv", "o", "gu", "down"):
-                assert (st.buffer(name) == want[name]).all(), (rank, M, tagged, name)
+                assert (st.buffer(name) == want[name]).all(), (rank, M, tagged, row_maxima, pq, name)
         del st
     dist.barrier()
     if rank == 0:

@@ -170,6 +170,118 @@ def test_pair_sums_and_producer_side_row_maxima(M):
         sp.Sequence([{"w": w1, "X": dev(X), "C": c1}, {"w": w2, "X": c1, "X2": c1, "C": c2, "x_kind": 3, "dep": 0}], M=M)
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 13, 16])
+def test_producer_side_quantiser(M):
+    """x_kind 4: the producing step quantises the columns its reader names (a part of its row, or
+    the pair sums of a fused gate|up step) and hands them on as packed int8; the reader fetches
+    bytes.  Same numbers as the reader-side quantiser and the oracle chain; several runs (the
+    packed words carry a tag that changes every run); the int32 outputs stay plain."""
+    K1, N1, off, K2, H, N3 = 512, 448, 64, 320, 288, 200
+    W1 = sp.gen_ternary_iid(K1, N1, 0.4, 1)
+    W2 = sp.gen_ternary_iid(K2, 2 * H, 0.5, 2)                                  # gate | up, reads columns off..off+K2 of step 0
+    W2i = np.ascontiguousarray(W2.reshape(2, H, K2).transpose(1, 0, 2).reshape(2 * H, K2))    # g0 u0 g1 u1 ...
+    W3 = sp.gen_ternary_iid(H, N3, 1 / 3, 3)
+    w1, w2, w3 = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (W1, W2i, W3))
+    X = O.gen_x_i8(M * K1, 4)
+    c1 = torch.zeros((M, N1), dtype=torch.int32, device="cuda")
+    c2 = torch.zeros((M, H), dtype=torch.int32, device="cuda")
+    c3 = torch.zeros((M, N3), dtype=torch.int32, device="cuda")
+    s2 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    s3 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    seq = sp.Sequence([
+        {"w": w1, "X": dev(X), "C": c1},
+        {"w": w2, "X": c1[:, off:], "C": c2, "x_kind": 4, "dep": 0, "scale_out": s2, "c_kind": 1},
+        {"w": w3, "X": c2, "C": c3, "x_kind": 4, "dep": 1, "scale_out": s3},
+    ], M=M)
+    r1 = O.gemv_i8_dense(X, W1)
+    q1, sc1 = O.quant_absmax_i8(np.ascontiguousarray(r1[:, off:off + K2]))
+    r2 = O.gemv_i8_dense(q1.reshape(-1), W2)
+    q2, sc2 = O.quant_absmax_i8(r2[:, :H], r2[:, H:])
+    r3 = O.gemv_i8_dense(q2.reshape(-1), W3)
+    for run in range(4):
+        seq.run()
+        assert seq.status() == 0
+        assert (c1.cpu().numpy() == r1).all()
+        assert (c2.cpu().numpy() == r2[:, :H] + r2[:, H:]).all()
+        assert (c3.cpu().numpy() == r3).all(), "run %d" % run
+        assert (s2.cpu().numpy() == sc1).all() and (s3.cpu().numpy() == sc2).all()
+    with pytest.raises(sp.SptmmError):          # the producer must be named
+        sp.Sequence([{"w": w1, "X": dev(X), "C": c1}, {"w": w2, "X": c1, "C": c2, "x_kind": 4, "c_kind": 1}], M=M)
+    with pytest.raises(sp.SptmmError):          # two readers of one producer must read the same columns
+        sp.Sequence([{"w": w1, "X": dev(X), "C": c1}, {"w": w2, "X": c1[:, off:], "C": c2, "x_kind": 4, "dep": 0, "c_kind": 1},
+                     {"w": w2, "X": c1, "C": c2, "x_kind": 4, "dep": 0, "c_kind": 1}], M=M)
+
+
+def test_producer_side_quantiser_full_width_rows():
+    """The layer shapes of the 2B stack at M=16 (K up to 6912: more columns than one pass of the
+    CTA's threads covers), one layer, against the oracle chain."""
+    M, hidden, ffn = 16, 2560, 6912
+    Wgu = sp.gen_ternary_iid(hidden, 2 * ffn, 1 / 3, 11)
+    Wgui = np.ascontiguousarray(Wgu.reshape(2, ffn, hidden).transpose(1, 0, 2).reshape(2 * ffn, hidden))
+    Wd = sp.gen_ternary_iid(ffn, hidden, 1 / 3, 12)
+    Wq = sp.gen_ternary_iid(hidden, 512, 1 / 3, 13)
+    wgu, wd, wq = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (Wgui, Wd, Wq))
+    X = O.gen_x_i8(M * hidden, 5)
+    cg = torch.zeros((M, ffn), dtype=torch.int32, device="cuda")
+    cd = torch.zeros((M, hidden), dtype=torch.int32, device="cuda")
+    cq = torch.zeros((M, 512), dtype=torch.int32, device="cuda")
+    seq = sp.Sequence([
+        {"w": wgu, "X": dev(X), "C": cg, "c_kind": 1},
+        {"w": wd, "X": cg, "C": cd, "x_kind": 4, "dep": 0},
+        {"w": wq, "X": cd, "C": cq, "x_kind": 4, "dep": 1},
+    ], M=M)
+    r1 = O.gemv_i8_dense(X, Wgu)
+    q1, _ = O.quant_absmax_i8(r1[:, :ffn], r1[:, ffn:])
+    r2 = O.gemv_i8_dense(q1.reshape(-1), Wd)
+    q2, _ = O.quant_absmax_i8(r2)
+    r3 = O.gemv_i8_dense(q2.reshape(-1), Wq)
+    for _ in range(2):
+        seq.run()
+        assert seq.status() == 0
+        assert (cd.cpu().numpy() == r2).all()
+        assert (cq.cpu().numpy() == r3).all()
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 5, 16])
+def test_settled_exchange(M):
+    """x_kind 5: tagged words watched by one CTA each, local counters, and (M > 1) a local int8 tile
+    fetched by bulk copy.  Parts of rows, pair sums, a buffer written twice in a run, odd widths
+    that fall back to the polling reader, several runs; bit-exact against the oracle chain."""
+    K1, N1, off, K2, H, N3 = 512, 448, 64, 320, 288, 200
+    W1 = sp.gen_ternary_iid(K1, N1, 0.4, 1)
+    W2 = sp.gen_ternary_iid(K2, 2 * H, 0.5, 2)
+    W2i = np.ascontiguousarray(W2.reshape(2, H, K2).transpose(1, 0, 2).reshape(2 * H, K2))
+    W3 = sp.gen_ternary_iid(H, N1, 1 / 3, 3)            # back to width N1: its output reuses W1's buffer
+    W4 = sp.gen_ternary_iid(N1 - 3, N3, 0.6, 4)         # an odd row length (445 columns)
+    w1, w2, w3, w4 = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (W1, W2i, W3, W4))
+    X = O.gen_x_i8(M * K1, 4)
+    c1 = torch.zeros((M, N1), dtype=torch.int32, device="cuda")      # written by steps 0 and 2
+    c2 = torch.zeros((M, H), dtype=torch.int32, device="cuda")
+    c4 = torch.zeros((M, N3), dtype=torch.int32, device="cuda")
+    s2 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    s3 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    seq = sp.Sequence([
+        {"w": w1, "X": dev(X), "C": c1},
+        {"w": w2, "X": c1[:, off:], "ldx": N1, "C": c2, "x_kind": 5, "dep": 0, "c_kind": 1, "scale_out": s2},
+        {"w": w3, "X": c2, "C": c1, "x_kind": 5, "dep": 1, "scale_out": s3},
+        {"w": w4, "X": c1, "ldx": N1, "C": c4, "x_kind": 5, "dep": 2},
+    ], M=M)
+    r1 = O.gemv_i8_dense(X, W1)
+    q1, sc1 = O.quant_absmax_i8(np.ascontiguousarray(r1[:, off:off + K2]))
+    r2 = O.gemv_i8_dense(q1.reshape(-1), W2)
+    q2, sc2 = O.quant_absmax_i8(r2[:, :H], r2[:, H:])
+    r3 = O.gemv_i8_dense(q2.reshape(-1), W3)
+    q3, _ = O.quant_absmax_i8(np.ascontiguousarray(r3[:, :N1 - 3]))
+    r4 = O.gemv_i8_dense(q3.reshape(-1), W4)
+    for run in range(5):
+        seq.run()
+        assert seq.status() == 0
+        assert (c4.cpu().numpy() == r4).all(), "run %d" % run
+        assert (((c1.cpu().numpy() << 8) >> 8) == r3).all()
+        assert (((c2.cpu().numpy() << 8) >> 8) == r2[:, :H] + r2[:, H:]).all()
+        assert (s2.cpu().numpy() == sc1).all() and (s3.cpu().numpy() == sc2).all()
+
+
 def test_tagged_exchange_is_validated():
     W = sp.gen_ternary_iid(256, 256, 0.5, 0)
     w = sp.Weights(W, sp.FMT_U16_V256).upload()

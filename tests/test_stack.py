@@ -53,13 +53,15 @@ def _oracle_chain(dense, layers, hidden, ffn, kv, x):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("tagged,row_maxima", [(False, False), (True, False), (False, True)])
-@pytest.mark.parametrize("M", [1, 4, 16])
-def test_small_stack_single_gpu(M, tagged, row_maxima):
+@pytest.mark.parametrize("tagged,row_maxima,producer_quant", [(False, False, False), (True, False, False), (False, True, False),
+                                                              (False, False, True), (None, False, None)])
+@pytest.mark.parametrize("M", [1, 2, 4, 11, 16])
+def test_small_stack_single_gpu(M, tagged, row_maxima, producer_quant):
     import torch
     torch.cuda.set_device(0)
     layers, hidden, ffn, kv = 3, 256, 512, 64
-    st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, keep_dense=True, tagged=tagged, row_maxima=row_maxima)
+    st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, keep_dense=True, tagged=tagged, row_maxima=row_maxima,
+                        producer_quant=producer_quant)
     x = O.gen_x_i8(M * hidden, 9).reshape(M, hidden)
     st.set_input(x)
     for _ in range(2):

@@ -82,6 +82,12 @@ def test_load_rejects_consistent_looking_but_wrong_files(tmp_path):
     open(p, "wb").write(bytes(_rehash(bad)))
     with pytest.raises(sp.SptmmError):
         sp.Weights.load(p)
+    for at_, v in ((48, 7), (44, 128)):                                  # blocks per list / entries per block the table does not bear out
+        bad = bytearray(blob); bad[at_:at_ + 4] = struct.pack("<I", v)
+        open(p, "wb").write(bytes(_rehash(bad)))
+        with pytest.raises(sp.SptmmError) as e:
+            sp.Weights.load(p)
+        assert "disagrees" in e.value.message
     bad = bytearray(blob); bad[8:12] = struct.pack("<I", 9)             # a future file version
     open(p, "wb").write(bytes(_rehash(bad)))
     with pytest.raises(sp.SptmmError) as e:
