@@ -34,6 +34,13 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 K, N, S, M = 6912, 2560, 4096, 1
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "effective_hbm_GBps_ternary_gemv_6912x2560_M1"
+WORKLOAD = "C1 ternary GEMV M=1 K=6912 N=2560, reference generator -S=4096, int8 activations, int32 sums"
+# DRAM bytes (read + write) per launch of the GEMV kernel on exactly this workload, from one ncu
+# capture of two launches (21.0092 MB each); not measured by the run that prints it.
+NCU_TRAFFIC_BYTES = 21009200
+# the same in both arms of the bench (the GPU arm's copy count and launch mode, and each arm's weight layout, are in "detail")
+CONFIG = {"workload": WORKLOAD,
+          "l2": "GPU arm: cold, the calls rotate over weight copies totalling more than the 126 MB L2; host arm: one 21 MB copy"}
 
 
 def algorithmic_bytes(stream_bytes: int, m: int, act_size: int) -> int:
@@ -95,8 +102,10 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": n}
 
 
-def cpu_baseline(budget_s: float = 8.0):
-    """Scalar add/sub loop over the reference's chunk-interleaved u16 layout on the host cores."""
+def cpu_baseline(budget_s: float = 8.0, blocks: int = 7):
+    """Scalar add/sub loop over the reference's chunk-interleaved u16 layout on the host cores.
+    The budget is split into `blocks` equal parts and the MEDIAN block is reported: other work on
+    the box moves single timings by tens of per cent."""
     import oracle_lib as O
     W = O.gen_fixed(K, N, S)
     X = O.gen_x_i8(M * K, 1)
@@ -105,14 +114,18 @@ def cpu_baseline(budget_s: float = 8.0):
     cores = os.cpu_count() or 1
     nbytes = algorithmic_bytes(2 * S * N, M, 1)
     O.gemv_i8_div_mt(X, wp, wn, M, K, N, S, 32, cores)
-    calls, t0 = 0, time.perf_counter()
-    while time.perf_counter() - t0 < budget_s:
-        O.gemv_i8_div_mt(X, wp, wn, M, K, N, S, 32, cores)
-        calls += 1
-    dt = (time.perf_counter() - t0) / calls
+    per_call, calls = [], 0
+    for _ in range(blocks):
+        n, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < budget_s / blocks:
+            O.gemv_i8_div_mt(X, wp, wn, M, K, N, S, 32, cores)
+            n += 1
+        per_call.append((time.perf_counter() - t0) / n)
+        calls += n
+    dt = statistics.median(per_call)
     return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "us_per_call": dt * 1e6,
-            "sample": "%d calls of the same M=1 6912x2560 S=4096 GEMV over ~%.0f s, %d threads" % (calls, budget_s, cores)}, (X, wp, wn)
+            "us_per_call": dt * 1e6, "us_per_call_min_max": [min(per_call) * 1e6, max(per_call) * 1e6],
+            "sample": "%d calls of the same M=1 6912x2560 S=4096 GEMV in %d blocks over ~%.0f s, %d threads; median block" % (calls, blocks, budget_s, cores)}, (X, wp, wn)
 
 
 def run_reference(args):
@@ -138,8 +151,8 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "us_per_call": dt / (args.steps * per_step) * 1e6, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "i8", "data": "synthetic",
-        "config": {"workload": "C1 ternary GEMV M=1 K=6912 N=2560, reference generator -S=4096, u16 lists split 32",
-                   "calls_per_step": per_step},
+        "config": CONFIG,
+        "detail": {"layout": "reference u16 lists, split 32 (W_map_32_div)", "calls_per_step": per_step},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": "%d steps x %d calls, scalar add/sub loop over W_map_32_div, %d threads" % (args.steps, per_step, cores)},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -376,69 +389,10 @@ def run_ours(args):
     # pass, column-sharded over all ranks with the fused peer-store exchange when world > 1
     stack_info = {}
     if not args.no_stack:
-        from sptmm_b200 import stack as stack_mod
         w.close()                                   # free the GEMV replicas first
         del out
         torch.cuda.empty_cache()
-        for m_rows in (1, 4, 16):
-            stk = stack_mod.TernaryStack(args.stack_layers, 2560, 6912, 640, M=m_rows, p_zero=1 / 3, seed=0, rank=rank, world=world,
-                                          tagged=True if args.stack_tagged else None)
-            stk.set_input(O.gen_x_i8(m_rows * 2560, 5).reshape(m_rows, 2560))
-            with torch.cuda.stream(st):
-                for _ in range(3):
-                    if world > 1:
-                        dist.barrier()
-                    stk.forward(st.cuda_stream)
-                    st.synchronize()
-                ok = stk.status() == 0
-                if world > 1:
-                    dist.barrier()
-                passes = 20
-                s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s0.record(st)
-                for _ in range(passes):
-                    stk.forward(st.cuda_stream)
-                s1.record(st)
-                st.synchronize()
-            sms = s0.elapsed_time(s1) / passes
-            total_bytes = float(stk.stream_bytes)
-            if world > 1:
-                t = torch.tensor([sms, -total_bytes, 0.0 if ok else 1.0], dtype=torch.float64, device="cuda")
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                sms = float(t[0].item()); ok = ok and float(t[2].item()) == 0.0
-                tb = torch.tensor([total_bytes], dtype=torch.float64, device="cuda")
-                dist.all_reduce(tb)
-                total_bytes = float(tb.item())
-            stack_info["M%d" % m_rows] = {"us_per_pass": sms * 1e3, "tokens_per_s": m_rows / (sms * 1e-3),
-                                          "encoded_GB": total_bytes / 1e9, "GBps_all_gpus": total_bytes / (sms * 1e-3) / 1e9,
-                                          "status_ok": ok, "layers": args.stack_layers, "steps_per_pass": stk.n_steps,
-                                          "exchange": "tagged words" if stk.tagged else "step counters"}
-            del stk
-            torch.cuda.empty_cache()
-            if world > 1:
-                # the same hardware used as replicas: every rank runs the whole stack on its own M
-                # rows, nothing is exchanged (world x M tokens per pass)
-                rep = stack_mod.TernaryStack(args.stack_layers, 2560, 6912, 640, M=m_rows, p_zero=1 / 3, seed=0, rank=0, world=1)
-                rep.set_input(O.gen_x_i8(m_rows * 2560, 5 + rank).reshape(m_rows, 2560))
-                with torch.cuda.stream(st):
-                    for _ in range(3):
-                        rep.forward(st.cuda_stream)
-                    st.synchronize()
-                    ok_r = rep.status() == 0
-                    dist.barrier()
-                    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    s0.record(st)
-                    for _ in range(passes):
-                        rep.forward(st.cuda_stream)
-                    s1.record(st)
-                    st.synchronize()
-                t = torch.tensor([s0.elapsed_time(s1) / passes, 0.0 if ok_r else 1.0], dtype=torch.float64, device="cuda")
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                rms = float(t[0].item())
-                stack_info["M%d" % m_rows]["replicas"] = {"us_per_pass": rms * 1e3, "tokens_per_s_all_gpus": world * m_rows / (rms * 1e-3),
-                                                           "status_ok": float(t[1].item()) == 0.0}
-                del rep
-                torch.cuda.empty_cache()
+        stack_info = stack_leg(args, sp, O, torch, dist, st, rank, world)
 
     large_info = large_sweep(args, sp, O, torch, dist, rank, world) if args.large else None
 
@@ -450,14 +404,15 @@ def run_ours(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "us_per_call": us_per_call,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "i8", "data": "synthetic",
             "pct_of_8000GBps": per_gpu / 8000.0 * 100.0,
-            "config": {"workload": "C1 ternary GEMV M=1 K=6912 N=2560, reference generator -S=4096, native u16 lists",
-                       "calls_per_step": calls, "weight_copies": replicas,
+            "config": CONFIG,
+            "detail": {"layout": "native u16 lists (256-entry blocks)", "calls_per_step": calls, "weight_copies": replicas,
                        "l2": "cold: rotating %d weight copies (%.0f MB) > 126 MB L2" % (replicas, replicas * per_copy / 1e6),
                        "launch": mode + ", %d concurrent streams (independent calls, round-robin), programmatic dependent launch inside a stream" % nstreams,
-                       "per_rank": "each GPU runs the same independent 2560-column shard",
-                       "tune": os.environ.get("SPTMM_TUNE", "")},
+                       "per_rank": "each GPU runs the same independent 2560-column shard"},
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                         "peak_kind": peak_kind, "algorithmic_bytes_per_launch": nbytes, "traffic": NCU_TRAFFIC_BYTES},
+                         "peak_kind": peak_kind, "algorithmic_bytes_per_launch": nbytes, "traffic": NCU_TRAFFIC_BYTES,
+                         "traffic_source": "ncu capture of this kernel on this workload (two launches); a constant here, not measured by this run",
+                         "single_stream_frac": (single["GBps"] / peak) if single and "GBps" in single else None},
             "e2e": {"value": e2e_value, "unit": "GB/s", "us_per_call": e2e_us,
                     "h2d_bytes_per_step": M * K * calls, "d2h_bytes_per_step": M * N * 4 * calls,
                     "calls_timed": e2e_calls, "calls_in_flight": e2e_slots, "host_threads": e2e_threads,
@@ -471,6 +426,9 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"], _ = cpu_baseline()
+        if world == 1 and not args.no_reference_gpu:
+            torch.cuda.synchronize()
+            line["reference_gpu"] = reference_gpu_leg()
         if args.extra:
             line["extra"] = extra_workloads(sp, O, torch, st)
         if large_info is not None:
@@ -481,10 +439,158 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of k_u16_v256 from the committed ncu
-# summary under profiles/ (k_u16_v256_gemv_6912x2560_M1.md: 21.0066 and 21.0063 MB on two launches).
-NCU_TRAFFIC_BYTES = 21009152
 
+README_COMMANDS = [          # the reference's README.md:23-27 (cu_blas is broken as shipped: it passes a null W)
+    ("rcr", ["-row_split3_small", "32", "-M=1", "-K=6912", "-N=2560", "-S=4096"]),
+    ("rcr", ["-row_split3_small", "32", "-M=4", "-K=6912", "-N=2560", "-S=4096"]),
+    ("rcr", ["-row_split_delta2", "32", "-M=1", "-K=6912", "-N=2560", "-S=4096"]),
+    ("rcr", ["-i2s", "-M=1", "-K=6912", "-N=2560", "-S=4096"]),       # M=1 only: the reference's M>1 launch writes out of bounds when K>N
+]
+
+
+def reference_gpu_leg(iters: int = 20000):
+    """Not part of the timed metric: where the reference's own GPU program was built beside the
+    oracle, run its README commands (launch + device synchronise per iteration, its own protocol)
+    and this library's drop-in for the same commands, alternately, and record both ms/iter."""
+    harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
+    ours = os.path.join(ROOT, "sptmm_b200", "bin")
+    if not os.path.exists(harness):
+        return {"unavailable": "the reference program is not built here"}
+
+    def last_number(cmd):
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=180)
+        except (OSError, subprocess.TimeoutExpired) as e:
+            return None, str(e)[:100]
+        lines = [l.strip() for l in r.stdout.splitlines() if l.strip()]
+        try:
+            return float(lines[-1]), None
+        except (IndexError, ValueError):
+            return None, ("rc %d: " % r.returncode) + (r.stdout + r.stderr)[-120:]
+
+    rows = []
+    for prog, flags in README_COMMANDS:
+        flags = flags + ["-iter=%d" % iters]
+        row = {"command": prog + " " + " ".join(flags), "protocol": "launch + device synchronise per iteration, weights stay in L2"}
+        ref, ours_t = [], []
+        for _ in range(3):                                        # alternate, keep the best of three
+            v, err = last_number([harness, "readme"] + flags)
+            if v is None:
+                row["reference_error"] = err
+                break
+            ref.append(v)
+            v, err = last_number([os.path.join(ours, prog)] + flags)
+            if v is None:
+                row["ours_error"] = err
+                break
+            ours_t.append(v)
+        if ref:
+            row["reference_us_per_iter"] = min(ref) * 1e3
+        if ours_t:
+            row["ours_us_per_iter"] = min(ours_t) * 1e3
+        rows.append(row)
+    return {"rows": rows, "iterations": iters}
+
+
+def stack_leg(args, sp, O, torch, dist, st, rank, world):
+    """The 30-layer stack at M = 1, 4, 16: one persistent kernel per pass, every matrix sharded by
+    columns over the ranks (fused exchange).  With several ranks also, per M: a parity pass against
+    the single-GPU stack on the same input (every rank, the last layer's four buffers, bit for bit
+    -- a mismatch ends the run), the same GPUs as independent replicas, and the NCCL variant
+    (per-call kernels + ncclAllGather + quantiser kernel in one CUDA graph)."""
+    from sptmm_b200 import stack as SM
+    shape = (args.stack_layers, 2560, 6912, 640)
+    wts = SM.StackWeights(*shape, p_zero=1 / 3, seed=0, rank=rank, world=world)
+    wts1 = wts if world == 1 else SM.StackWeights(*shape, p_zero=1 / 3, seed=0, rank=0, world=1)
+    passes = 20
+    names = ("qkv", "o", "gu", "down")
+    info = {}
+
+    def timed(forward, sync_ranks=True):
+        with torch.cuda.stream(st):
+            for _ in range(3):
+                if world > 1 and sync_ranks:
+                    dist.barrier()
+                forward()
+                st.synchronize()
+            if world > 1:
+                dist.barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(st)
+            for _ in range(passes):
+                forward()
+            s1.record(st)
+            st.synchronize()
+        ms = s0.elapsed_time(s1) / passes
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms * 1e3
+
+    def all_ranks(flag: bool) -> bool:
+        if world == 1:
+            return flag
+        t = torch.tensor([0.0 if flag else 1.0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) == 0.0
+
+    for m_rows in (1, 4, 16):
+        x = O.gen_x_i8(m_rows * 2560, 5).reshape(m_rows, 2560)
+        stk = SM.TernaryStack(*shape, M=m_rows, rank=rank, world=world, weights=wts, settled=True if args.stack_settled else None,
+                              tagged=True if args.stack_tagged else None)
+        stk.set_input(x)
+        us = timed(lambda: stk.forward(st.cuda_stream))
+        ok = all_ranks(stk.status() == 0)
+        total_bytes = float(stk.stream_bytes)
+        if world > 1:
+            tb = torch.tensor([total_bytes], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tb)
+            total_bytes = float(tb.item())
+        entry = {"us_per_pass": us, "tokens_per_s": m_rows / (us * 1e-6), "encoded_GB": total_bytes / 1e9,
+                 "GBps_all_gpus": total_bytes / (us * 1e-6) / 1e9, "status_ok": ok, "layers": args.stack_layers,
+                 "steps_per_pass": stk.n_steps,
+                 "exchange": "settled (one watcher per word, local counters)" if stk.settled else ("tagged words" if stk.tagged else "step counters")}
+        info["M%d" % m_rows] = entry
+        # the same weights as launch-per-matmul: per-call kernels + (NCCL all-gather) + quantiser kernel, one CUDA graph per pass
+        ns = SM.NcclStack(wts, M=m_rows)
+        ns.set_input(x)
+        with torch.cuda.stream(st):
+            nccl_us = timed(ns.forward)
+        nccl_out = ns.result()
+        if world > 1:
+            # ---- parity, visible in this record: the 1-GPU stack on the SAME input
+            rep = SM.TernaryStack(*shape, M=m_rows, rank=0, world=1, weights=wts1)
+            rep.set_input(x)
+            with torch.cuda.stream(st):
+                dist.barrier()
+                stk.forward(st.cuda_stream)
+                rep.forward(st.cuda_stream)
+                st.synchronize()
+                dist.barrier()
+            same = all(np.array_equal(stk.buffer(n), rep.buffer(n)) for n in names) and stk.status() == 0 and rep.status() == 0
+            if not all_ranks(same):
+                raise SystemExit("parity failure: the sharded stack (M=%d, %d GPUs) differs from the single-GPU stack" % (m_rows, world))
+            entry["parity"] = "bit-exact vs 1 GPU: qkv, o, gu, down of the last layer, on every rank"
+            if not all_ranks(np.array_equal(nccl_out, rep.buffer("down"))):
+                raise SystemExit("parity failure: the NCCL stack (M=%d, %d GPUs) differs from the single-GPU stack" % (m_rows, world))
+            # ---- the same hardware used as replicas: every rank runs the whole stack on its own M rows
+            rep.set_input(O.gen_x_i8(m_rows * 2560, 5 + rank).reshape(m_rows, 2560))
+            rus = timed(lambda: rep.forward(st.cuda_stream), sync_ranks=False)
+            entry["replicas"] = {"us_per_pass": rus, "tokens_per_s_all_gpus": world * m_rows / (rus * 1e-6), "status_ok": all_ranks(rep.status() == 0)}
+            entry["sharded_speedup"] = rus / us
+            entry["nccl"] = {"us_per_pass": nccl_us, "sharded_speedup": rus / nccl_us, "parity": "bit-exact vs 1 GPU (final output)",
+                             "how": "per step: sptmm_gemv on the rank's columns, ncclAllGather of the int32 results, sptmm_quantize_absmax; one CUDA graph per pass"}
+            del rep
+        else:
+            same = np.array_equal(nccl_out, stk.buffer("down"))
+            if not same:
+                raise SystemExit("parity failure: launch-per-matmul stack (M=%d) differs from the persistent kernel" % m_rows)
+            entry["launch_per_matmul"] = {"us_per_pass": nccl_us, "parity": "bit-exact vs the persistent kernel (final output)",
+                                          "how": "per step: sptmm_gemv + sptmm_quantize_absmax; one CUDA graph per pass"}
+        del stk, ns
+        torch.cuda.empty_cache()
+    return info
 
 def extra_workloads(sp, O, torch, st, nstreams=4):
     """The same matrix at M=1/4/16 (int8, fp16) in the native format, the reference layouts and the
@@ -657,8 +763,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-seq", action="store_true", help="skip the persistent-sequence measurement")
     ap.add_argument("--no-stack", action="store_true", help="skip the layer-stack measurement")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip running the reference's own GPU program (README commands)")
     ap.add_argument("--stack-layers", type=int, default=30)
     ap.add_argument("--stack-tagged", action="store_true", help="layer stack hands activations on as tagged words (x_kind 2)")
+    ap.add_argument("--stack-settled", action="store_true", help="layer stack uses the settled exchange (x_kind 5) at every M and GPU count")
     ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
     ap.add_argument("--large", nargs="?", const="one", default=None, choices=["one", "all"],
                     help="also run the large-matrix sweep (column-sharded and split-K over all ranks); 'all' = three shapes")

@@ -337,6 +337,10 @@ int sptmm_dev_free(void *ptr);
 int sptmm_memcpy_h2d(void *dst, const void *src, uint64_t bytes);
 int sptmm_memcpy_d2h(void *dst, const void *src, uint64_t bytes);
 int sptmm_device_sync(void);
+/* Wait until `stream` (NULL = the default stream) has finished: polls first, which returns sooner
+ * than the blocking wait for work of a few microseconds (the reference waits with
+ * cudaDeviceSynchronize after every launch, main.cu:1456). */
+int sptmm_stream_wait(void *stream);
 
 #ifdef __cplusplus
 }

@@ -91,6 +91,7 @@ def _load() -> C.CDLL:
         "sptmm_memcpy_h2d": (i32, [vp, vp, u64]),
         "sptmm_memcpy_d2h": (i32, [vp, vp, u64]),
         "sptmm_device_sync": (i32, []),
+        "sptmm_stream_wait": (i32, [vp]),
     }
     if TUNING:                           # csrc/tuning.h
         sigs["sptmm_seq_set_trace"] = (i32, [vp, vp])
@@ -109,7 +110,7 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_shared_bytes_for", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_free",
            "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
-           "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync"]
+           "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync", "sptmm_stream_wait"]
 
 
 def check(rc: int) -> None:

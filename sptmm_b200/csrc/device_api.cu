@@ -400,3 +400,15 @@ extern "C" int sptmm_memcpy_d2h(void *dst, const void *src, uint64_t bytes)
     return SPTMM_OK;
 }
 extern "C" int sptmm_device_sync(void) { SPTMM_CUDA_TRY(cudaDeviceSynchronize()); return SPTMM_OK; }
+
+extern "C" int sptmm_stream_wait(void *stream)
+{
+    // for work of a few microseconds, asking whether the stream is done returns sooner than the
+    // blocking wait does; after a while fall back to it
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaErrorNotReady;
+    for (int spin = 0; spin < 20000 && e == cudaErrorNotReady; spin++) e = cudaStreamQuery(st);
+    if (e == cudaErrorNotReady) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(SPTMM_ERR_CUDA, "stream_wait: %s", cudaGetErrorString(e));
+    return SPTMM_OK;
+}

@@ -60,7 +60,7 @@ extern "C" int sptmm_quantize_absmax(const int32_t *X, uint32_t M, uint32_t K, u
     if (!X || !Xq) return fail(SPTMM_ERR_INVALID, "quantize_absmax: null pointer");
     if (M == 0 || K == 0) return fail(SPTMM_ERR_INVALID, "quantize_absmax: M=%u K=%u", M, K);
     const uint32_t width = pair ? 2 * K : K;
-    if (shard && width % shard) return fail(SPTMM_ERR_INVALID, "quantize_absmax: %u source columns are not whole shards of %u", width, shard);
+    if (shard && pair && (shard & 1)) return fail(SPTMM_ERR_INVALID, "quantize_absmax: pair sums need shards of an even number of columns (%u)", shard);
     if (!shard && ldx && ldx < width) return fail(SPTMM_ERR_INVALID, "quantize_absmax: ldx=%u is less than the %u source columns", ldx, width);
     QuantParams prm{X, Xq, scale, M, K, ldx ? ldx : width, shard, pair ? 1u : 0u};
     cudaLaunchConfig_t cfg = {};

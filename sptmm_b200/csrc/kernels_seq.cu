@@ -347,6 +347,53 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
     if (tid < (uint32_t)MT) xs[(size_t)d.K * MT + tid] = 0x80;        // the zero row
 }
 
+// One complete int32 row -> int8 tile, 16 bytes per load, the values kept in registers between
+// the absmax and the rounding; `tagged`: the words carry a tag byte to strip.  The trip count is
+// uniform over the CTA, so rows far shorter than the register budget cost no idle instructions.
+// Needs K % 4 == 0, A 16-byte aligned, K <= 14336.
+__device__ __forceinline__ bool row_fits_vec(const void *A, uint32_t K)
+{
+    return (K & 3) == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && K <= 7u * 4u * 512u;
+}
+__device__ __forceinline__ void quant_row_vec(unsigned char *xs, const int32_t *A, uint32_t K, int *red, bool tagged, float *scale_out)
+{
+    constexpr int V4 = 7;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nt = 512;
+    const uint32_t quads = K / 4, nv = (quads + nt - 1) / nt;
+    int4 v[V4];
+    int amax = 0;
+#pragma unroll
+    for (int j = 0; j < V4; j++) {
+        if ((uint32_t)j < nv) {
+            const uint32_t q = tid + j * nt;
+            v[j] = q < quads ? __ldcg(reinterpret_cast<const int4 *>(A) + q) : make_int4(0, 0, 0, 0);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < V4; j++) {
+        if ((uint32_t)j < nv) {
+            if (tagged) v[j] = make_int4((v[j].x << 8) >> 8, (v[j].y << 8) >> 8, (v[j].z << 8) >> 8, (v[j].w << 8) >> 8);
+            amax = max(amax, max(max(abs(v[j].x), abs(v[j].y)), max(abs(v[j].z), abs(v[j].w))));
+        }
+    }
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    if (lane == 0) red[warp] = amax;
+    asm volatile("bar.sync 1, 512;" ::: "memory");
+    amax = lane < 16 ? red[lane] : 0;
+    amax = __reduce_max_sync(0xffffffffu, amax);
+    const float scale = amax ? 127.0f / (float)amax : 0.0f;
+    auto q1 = [&](int x) { return (uint32_t)max(-127, min(127, __float2int_rn((float)x * scale))) & 0xffu; };
+#pragma unroll
+    for (int j = 0; j < V4; j++) {
+        if ((uint32_t)j < nv) {
+            const uint32_t q = tid + j * nt;
+            if (q < quads) reinterpret_cast<uint32_t *>(xs)[q] = q1(v[j].x) | (q1(v[j].y) << 8) | (q1(v[j].z) << 16) | (q1(v[j].w) << 24);
+        }
+    }
+    if (tid == 0) xs[K] = 0;
+    if (scale_out && tid == 0) scale_out[0] = (float)amax / 127.0f;
+}
+
 // int32 rows (optionally the sum of two sources) -> int8 with a per-row absmax scale:
 // q = clamp(rint(v * (127 / amax)), -127, 127), all in fp32; amax == 0 gives zeros.
 template <int MT, bool TAGGED>
@@ -376,6 +423,12 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
     }
     const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
     const int32_t *B = reinterpret_cast<const int32_t *>(d.X2);
+    if constexpr (MT == 1) {
+        if (!tag && !B && M >= 1 && row_fits_vec(A, d.K)) {          // the common case: one finished row
+            quant_row_vec(xs, A, d.K, red, false, (write_scale && d.scale_out) ? d.scale_out : nullptr);
+            return;
+        }
+    }
     int8_t *dst = reinterpret_cast<int8_t *>(xs);
     const uint32_t tid = threadIdx.x, nt = 512, lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;   // consumer threads only
     constexpr int V = 28;                      // values a thread keeps per row: covers K <= 14336
@@ -703,65 +756,37 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
         settle_barrier(c1, p.target_local, failed, p.status);
         SEQ_MARK(p, s, 1, failed);
         // the row is complete: 16-byte loads, values kept in registers between absmax and rounding
-        constexpr int V4 = 7;                              // covers K <= 14336
-        if ((d.K & 3) == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && d.K <= (uint32_t)V4 * 4 * nt) {
-            const uint32_t quads = d.K / 4;
-            int4 v[V4];
-            int amax = 0;
-#pragma unroll
-            for (int j = 0; j < V4; j++) {
-                const uint32_t q = tid + j * nt;
-                v[j] = q < quads ? __ldcg(reinterpret_cast<const int4 *>(A) + q) : make_int4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int j = 0; j < V4; j++) {
-                v[j] = make_int4(untag(v[j].x), untag(v[j].y), untag(v[j].z), untag(v[j].w));
-                amax = max(amax, absmax4(v[j]));
-            }
-            amax = __reduce_max_sync(0xffffffffu, amax);
-            if (lane == 0) red[warp] = amax;
-            consumer_sync();
-            SEQ_MARK(p, s, 2, failed);
-            amax = 0;
-#pragma unroll
-            for (uint32_t w = 0; w < kConsumers; w++) amax = max(amax, red[w]);
-            const float scale = amax ? 127.0f / (float)amax : 0.0f;
-#pragma unroll
-            for (int j = 0; j < V4; j++) {
-                const uint32_t q = tid + j * nt;
-                if (q < quads)
-                    reinterpret_cast<uint32_t *>(xs)[q] = (uint32_t)(quant1(v[j].x, scale) & 0xff) | ((uint32_t)(quant1(v[j].y, scale) & 0xff) << 8) |
-                                                         ((uint32_t)(quant1(v[j].z, scale) & 0xff) << 16) | ((uint32_t)(quant1(v[j].w, scale) & 0xff) << 24);
-            }
-            if (tid == 0) xs[d.K] = 0;
-            if (write_scale && d.scale_out && tid == 0) d.scale_out[0] = (float)amax / 127.0f;
-        } else {
-            bool fine = true;                              // odd shapes: the general reader (every word carries the tag by now)
-            stage_x_quant<MT, true>(xs, d, p.M, red, write_scale, tag, sys, fine);
-        }
+        // (the host admits only rows that fit: K a multiple of 4, at most 14336, 16-byte aligned)
+        quant_row_vec(xs, A, d.K, red, true, (write_scale && d.scale_out) ? d.scale_out : nullptr);
+        SEQ_MARK(p, s, 2, failed);
     } else {
         int *rowmax_s = red + 32;                          // [16]
         uint32_t *amax_g = p.amax + ((size_t)p.run_parity * p.nsteps + s) * 16;
         unsigned char *tile_g = p.xq + (size_t)(s & 1) * p.xq_stride;
         if (tid < 16) rowmax_s[tid] = 0;
         consumer_sync();
-        // my columns' words, row by row; up to VW of them stay in registers
-        constexpr int VW = 4;
-        const uint32_t words = p.M * nk;
-        int v[VW];
+        // thread t owns column k0 + t (a CTA has fewer columns than threads): all rows' loads in flight
+        // together, then the stale ones again until they carry the tag
+        const bool mine = tid < nk;
+        const uint32_t k = k0 + tid;
+        int v[MT];
 #pragma unroll
-        for (int j = 0; j < VW; j++) {
-            const uint32_t i = tid + j * nt;
-            v[j] = 0;
-            if (i < words) {
-                const uint32_t m = i / nk, k = k0 + (i - m * nk);
-                v[j] = arrived(A + (size_t)m * d.ldx + k);
-                atomicMax(rowmax_s + m, abs(v[j]));
-            }
+        for (int m = 0; m < MT; m++) v[m] = (mine && (uint32_t)m < p.M) ? __ldcg(A + (size_t)m * d.ldx + k) : (int)(tag << 24);
+        for (uint32_t it = 0; ok; it++) {
+            bool stale = false;
+#pragma unroll
+            for (int m = 0; m < MT; m++)
+                if (((uint32_t)v[m] >> 24) != tag) { stale = true; v[m] = ld_fresh(A + (size_t)m * d.ldx + k, sys); }
+            if (!stale) break;
+            if (it >= kPollLimit) ok = false;
         }
-        for (uint32_t i = tid + VW * nt; i < words; i += nt) {          // very wide slices: re-read later
-            const uint32_t m = i / nk, k = k0 + (i - m * nk);
-            atomicMax(rowmax_s + m, abs(arrived(A + (size_t)m * d.ldx + k)));
+        if (warp * 32 < nk) {
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                v[m] = untag(v[m]);
+                const int a = __reduce_max_sync(0xffffffffu, abs(v[m]));
+                if (lane == 0 && a) atomicMax(rowmax_s + m, a);
+            }
         }
         if (!ok && !*failed) { *failed = 1; atomicOr(p.status, 2u); }
         consumer_sync();
@@ -776,22 +801,18 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
             if (write_scale && d.scale_out && tid < p.M) d.scale_out[tid] = (float)a / 127.0f;
         }
         consumer_sync();
-        // round my columns and put them where the tile has them: byte k*MT + m, biased
+        // round my column and put it where the tile has it: bytes k*MT .. k*MT + MT-1, biased, one store
+        if (mine) {
+            uint32_t o[MT / 4];
 #pragma unroll
-        for (int j = 0; j < VW; j++) {
-            const uint32_t i = tid + j * nt;
-            if (i < words) {
-                const uint32_t m = i / nk, k = k0 + (i - m * nk);
-                tile_g[(size_t)k * MT + m] = (unsigned char)tile_byte<MT>(quant1(v[j], scale_s[m]));
+            for (int q = 0; q < MT / 4; q++) {
+                o[q] = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) o[q] |= ((uint32_t)quant1(v[4 * q + i], scale_s[4 * q + i]) & 0xffu) << (8 * i);
+                o[q] ^= 0x80808080u;
             }
-        }
-        for (uint32_t i = tid + VW * nt; i < words; i += nt) {
-            const uint32_t m = i / nk, k = k0 + (i - m * nk);
-            tile_g[(size_t)k * MT + m] = (unsigned char)tile_byte<MT>(quant1(untag(__ldcg(A + (size_t)m * d.ldx + k)), scale_s[m]));
-        }
-        for (uint32_t i = tid; i < ((uint32_t)MT - p.M) * nk; i += nt) {      // rows the tile has beyond M
-            const uint32_t m = p.M + i / nk, k = k0 + i % nk;
-            tile_g[(size_t)k * MT + m] = (unsigned char)tile_byte<MT>(0);
+            if constexpr (MT == 4) *reinterpret_cast<uint32_t *>(tile_g + (size_t)k * 4) = o[0];
+            else *reinterpret_cast<uint4 *>(tile_g + (size_t)k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
         }
         settle_barrier(c2, p.target_local, failed, p.status);
         SEQ_MARK(p, s, 2, failed);
@@ -815,9 +836,17 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
     }
 }
 
-template <int MT, bool TAGGED>
+// XV selects what a kernel variant knows about (each carries only its own code, which keeps the
+// registers of the input stages it does not need out of the gather loop's way):
+//   0  int8 inputs and the counter hand-over (x_kind 0, 1)
+//   1  also tagged words polled by every reader, row maxima, the producer-side quantiser (x_kind 2, 3, 4)
+//   2  int8 inputs and the settled exchange (x_kind 0, 5)
+template <int MT, int XV>
 __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_constant__ SeqParams p)
 {
+    constexpr bool TAGGED = XV == 1;          // the polling exchanges
+    constexpr bool SETTLED = XV == 2;
+    constexpr bool TAGS = XV != 0;            // outputs may carry tags
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     unsigned char *smem = tile_base(dyn_smem);     // the tile's fixed address; all offsets count from it
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -929,7 +958,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         const bool tracing = p.trace != nullptr && cta == 0 && tid == 33 && s < 256;
 #endif
         // ---- wait until the step this one depends on has finished everywhere
-        if (d.dep >= 0 && !(TAGGED && (d.x_kind == 2 || d.x_kind == 4 || d.x_kind == 5))) {     // tagged inputs are waited for word by word while staging
+        if (d.dep >= 0 && !(TAGGED && (d.x_kind == 2 || d.x_kind == 4)) && !(SETTLED && d.x_kind == 5)) {     // tagged inputs are waited for word by word while staging
             if (tid == 0 && !failed) {
                 const unsigned long long *ctr = p.counters + d.dep;
                 unsigned long long v = 0;
@@ -957,15 +986,13 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         uint32_t nxt = 0;
         if (s + 1 < p.nsteps) nxt = load_step_word(s + 1);
         // (TAGGED kernels are the ones that also know row maxima: plain sequences carry neither)
-        if (TAGGED && p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
+        if (TAGS && p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
             p.amax[((p.run_parity ^ 1u) * p.nsteps + s) * 16 + tid] = 0u;
         if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
-        else if (TAGGED && d.x_kind == 5) {
+        else if constexpr (SETTLED) {               // x_kind 5 (the host admits no other kind here)
             bool fresh = failed == 0;
             const uint32_t tag = seq_tag(p.run_mod, d.in_tag_m, d.in_tag_j);
-            // odd shapes (a tile that is no whole number of 16-byte pieces) take the polling reader
-            if (MT > 1 && ((d.K * MT) & 15)) stage_x_quant<MT, TAGGED>(xs, d, p.M, red, cta == 0, tag, p.n_peers != 0, fresh);
-            else stage_x_settled<MT>(xs, d, p, s, red, xbar_a, xphase, tag, p.n_peers != 0, fresh, &failed, cta == 0);
+            stage_x_settled<MT>(xs, d, p, s, red, xbar_a, xphase, tag, p.n_peers != 0, fresh, &failed, cta == 0);
             if (!fresh && !failed) { failed = 1; atomicOr(p.status, 2u); }
         }
         else if (TAGGED && d.x_kind == 4) {
@@ -1159,20 +1186,30 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             }
         }
 
-        // ---- results out, then tell the other CTAs this step is done here.  Warp 0 does it alone
-        // while the others move on (the next step accumulates into the other buffer).
-        if (warp == 0) {
-            // a tagged output carries its tag in the top byte (|value| < 2^23 because K < 65536)
-            const bool tag_out = TAGGED && d.out_tag_m != 0;
-            const uint32_t otag = tag_out ? seq_tag(p.run_mod, d.out_tag_m, d.out_tag_j) << 24 : 0u;
-            auto out_word = [&](int v) { return tag_out ? (int)(otag | ((uint32_t)v & 0xffffffu)) : v; };
-            for (uint32_t i = lane; i < nout * p.M; i += 32) {
+        // ---- results out, then tell the other CTAs this step is done here.  A handful of values
+        // that a counter bump has to follow are stored by warp 0 alone while the others move on (the
+        // next step accumulates into the other buffer); otherwise all warps store.
+        // A tagged output carries its tag in the top byte (|value| < 2^23 because K < 65536).
+        const bool tag_out = TAGS && d.out_tag_m != 0;
+        const uint32_t otag = tag_out ? seq_tag(p.run_mod, d.out_tag_m, d.out_tag_j) << 24 : 0u;
+        const bool tail = (TAGGED && d.want_amax) || d.release;      // something follows the stores
+        const bool solo = tail && nout * p.M <= 64;
+        auto store_out = [&](uint32_t first, uint32_t step) {
+            for (uint32_t i = first; i < nout * p.M; i += step) {
                 const uint32_t m = i / nout, j = i - m * nout;
-                const int wv = out_word(value(j, m));
+                const int val = value(j, m);
+                const int wv = tag_out ? (int)(otag | ((uint32_t)val & 0xffffffu)) : val;
                 if (p.n_peers == 0) d.C[(size_t)m * d.ldc + o0 + j] = wv;
                 else                  // the exchange: straight into every rank's buffer over NVLink (plain peer stores)
                     for (uint32_t r = 0; r < p.n_peers; r++) d.Cp[r][(size_t)m * d.ldc + o0 + j] = wv;
             }
+        };
+        if (!solo) {
+            store_out(tid, kConsumerThreads);
+            if (tail) consumer_sync();
+        }
+        if (warp == 0 && (solo || tail)) {
+            if (solo) store_out(lane, 32);
             if (TAGGED && d.want_amax) {        // every row's largest magnitude, for the x_kind 3 reader: lane m reports row m
                 uint32_t mine = 0;
                 for (uint32_t m = 0; m < p.M; m++) {
@@ -1191,8 +1228,8 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             __syncwarp();
             // the release orders this warp's stores and reductions (seen through __syncwarp) before the count
             if (p.n_peers == 0) {
-                if (lane == 0 && (!TAGGED || d.release)) asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
-            } else if (lane < p.n_peers && (!TAGGED || d.release)) {
+                if (lane == 0 && d.release) asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.counters + s) : "memory");
+            } else if (lane < p.n_peers && d.release) {
                 asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(p.counter_peers[lane] + s) : "memory");
             }
         }
@@ -1220,6 +1257,7 @@ struct sptmm_seq {
     uint32_t n_peers = 0, my_rank = 0;
     bool tagged = false;             // some step reads tagged words: run the kernel variant that knows them
     bool uses_amax = false;          // some step is x_kind 3: the row-maxima area is in use
+    bool settled = false;            // the steps with a producer are all x_kind 5: the kernel variant for that exchange
     void *counter_peers[kMaxPeers] = {};
 };
 
@@ -1299,6 +1337,9 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         else if (w->device != dev || st.replica >= w->dev.size()) rc = fail(SPTMM_ERR_STATE, "seq_create: step %u weights are not uploaded to device %d (replica %u)", s, dev, st.replica);
         else if (st.x_kind > 5) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u x_kind %u", s, st.x_kind);
         else if (st.x_kind == 5 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 5) needs a producer (dep) and takes no X2", s);
+        else if (st.x_kind == 5 && ((w->K & 3) || (reinterpret_cast<uintptr_t>(st.X) & 15) || (st.ldx & 3) || (M == 1 && w->K > 14336) ||
+                                    (w->K + (uint32_t)sms - 1) / (uint32_t)sms > 512))
+            rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u (x_kind 5) needs K a multiple of 4 (at most 14336 for one row), X 16-byte aligned and ldx a multiple of 4", s);
         else if (st.x_kind == 4 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 4) needs a producer (dep) and takes no X2", s);
         else if (st.x_kind == 3 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 3) needs a producer (dep) and takes no X2", s);
         else if (st.c_kind > 1 || (st.c_kind == 1 && (w->N & 1))) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u c_kind %u (pair sums need an even N)", s, st.c_kind);
@@ -1454,7 +1495,17 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         uint32_t k5 = 0;                                     // longest row any settled-exchange step reads
         for (uint32_t s = 0; s < n; s++)
             if (steps[s].x_kind == 5) k5 = std::max(k5, desc[s].K);
+        if (k5 && q->mt > 1 && q->uses_amax) {
+            seq_release(q);
+            return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: x_kind 3 and x_kind 5 steps of several rows cannot share a sequence (both keep row maxima per step)");
+        }
         if (k5) {
+            for (uint32_t s = 0; s < n; s++)
+                if (steps[s].x_kind != 0 && steps[s].x_kind != 5) {
+                    seq_release(q);
+                    return fail(SPTMM_ERR_UNSUPPORTED, "seq_create: a sequence with x_kind 5 steps takes x_kind 0 and 5 only (step %u is %u)", s, steps[s].x_kind);
+                }
+            q->settled = true;
             if (q->mt > 1) q->uses_amax = true;              // the steps' row maxima live in that area
             q->xq_stride = (uint32_t)(((size_t)k5 * q->mt + 255) & ~(size_t)255);
             if (e == cudaSuccess) e = cudaMalloc(&q->d_xq, 2 * (size_t)q->xq_stride);
@@ -1488,23 +1539,24 @@ extern "C" int sptmm_seq_create_shared(const sptmm_seq_step *steps, uint32_t n, 
     return seq_create_impl(steps, n, M, C_peers, counter_peers, n_peers, my_rank, out);
 }
 
-template <int MT, bool TAGGED>
+template <int MT, int XV>
 static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st);
 
 template <int MT>
 static int seq_launch(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
 {
-    // one kernel variant knows tagged words and row maxima, the other neither (and is smaller, which
-    // shows: 0.7 us per step on the 6912x2560 sequence)
-    return (q->tagged || q->uses_amax) ? seq_launch_as<MT, true>(q, prm, st) : seq_launch_as<MT, false>(q, prm, st);
+    // every kernel variant carries only the exchanges its sequence uses (see k_seq); the plain one is
+    // 0.7 us per step faster on the 6912x2560 sequence than one that knows them all
+    if (q->settled) return seq_launch_as<MT, 2>(q, prm, st);
+    return (q->tagged || q->uses_amax) ? seq_launch_as<MT, 1>(q, prm, st) : seq_launch_as<MT, 0>(q, prm, st);
 }
 
-template <int MT, bool TAGGED>
+template <int MT, int XV>
 static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
 {
     static std::atomic<int> configured_device{-1};     // host threads may launch concurrently
     if (configured_device.load(std::memory_order_acquire) != q->device) {
-        SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_seq<MT, TAGGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        SPTMM_CUDA_TRY(cudaFuncSetAttribute(k_seq<MT, XV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured_device.store(q->device, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
@@ -1513,7 +1565,7 @@ static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t 
     attr[0].id = cudaLaunchAttributeCooperative;      // all CTAs resident at once, or the launch fails
     attr[0].val.cooperative = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    SPTMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, k_seq<MT, TAGGED>, prm));
+    SPTMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, k_seq<MT, XV>, prm));
     return SPTMM_OK;
 }
 

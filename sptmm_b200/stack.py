@@ -47,10 +47,38 @@ def stack_weights(layers: int, hidden: int, ffn: int, kv: int, p_zero: float, se
             yield l, name, sp.gen_ternary_iid(K, N, p_zero, matrix_seed(seed, l, i))
 
 
+class StackWeights:
+    """This rank's column shard of every matrix of the stack, encoded and uploaded; independent of M,
+    so stacks for several batch sizes can share one set."""
+
+    def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, p_zero=1 / 3, seed=0, rank=0, world=1, keep_dense=False):
+        self.shape = (layers, hidden, ffn, kv)
+        self.rank, self.world = rank, world
+        self.dense = [] if keep_dense else None
+        self.weights, self.stream_bytes, self.params = [], 0, 0
+        for l, name, W in stack_weights(layers, hidden, ffn, kv, p_zero, seed):
+            if keep_dense:
+                self.dense.append(W)
+            if name == "gu":                    # columns g0,u0,g1,u1,...: a pair-summing step adds gate_j and up_j
+                W = np.ascontiguousarray(W.reshape(2, ffn, W.shape[1]).transpose(1, 0, 2).reshape(2 * ffn, W.shape[1]))
+            c0, c1 = shard_range(W.shape[0], rank, world)
+            assert name != "gu" or (c0 % 2 == 0 and c1 % 2 == 0), "pair sums need even shard boundaries"
+            w = sp.Weights(W[c0:c1], sp.FMT_U16_V256).upload()
+            self.weights.append(w)
+            self.stream_bytes += w.stream_bytes
+            self.params += W.shape[0] * W.shape[1]
+
+    def close(self):
+        for w in self.weights:
+            w.close()
+        self.weights = []
+
+
 class TernaryStack:
     def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, M=1, p_zero=1 / 3, seed=0,
                  rank=0, world=1, group=None, keep_dense=False, tagged=None, row_maxima=False, producer_quant=None,
-                 settled=None):
+                 settled=None, weights=None):
+        """weights: a StackWeights built for the same shapes, rank and world (else one is built here)."""
         import torch
         self.torch = torch
         self.layers, self.hidden, self.ffn, self.kv, self.M = layers, hidden, ffn, kv, M
@@ -65,9 +93,12 @@ class TernaryStack:
         #  - settled (x_kind 5): tagged words as above, but every word is watched by one CTA per GPU,
         #    the CTAs of a GPU meet at local counters, and for M > 1 each CTA quantises only its own
         #    columns into a local int8 tile that all fetch with one bulk copy.
+        #    Measured on B200 (30 layers, us per pass; counters / settled): one GPU M=1 1 240 / 1 380,
+        #    M=4 1 890 / 1 900, M=16 4 280 / 3 350; two GPUs M=1 950 (polled tags) / 930, M=4 1 510 / 1 420,
+        #    M=16 3 540 / 2 420.  None picks it across GPUs and, on one GPU, from eight rows upward.
         explicit = tagged is not None or producer_quant is not None or row_maxima
         if settled is None:
-            settled = not explicit
+            settled = not explicit and (world > 1 or M >= 8)
         if producer_quant is None:
             producer_quant = False
         if settled:
@@ -75,23 +106,15 @@ class TernaryStack:
         elif tagged is None:
             tagged = world > 1 and M <= 4 and not producer_quant
         self.tagged, self.producer_quant, self.settled = tagged, producer_quant, settled
-        self.dense = [] if keep_dense else None
         shapes = layer_shapes(hidden, ffn, kv)
         widths = {name: N for name, _, N in shapes}
 
         # ---- weights: this rank's columns of every matrix
-        self.weights, self.stream_bytes, self.params = [], 0, 0
-        for l, name, W in stack_weights(layers, hidden, ffn, kv, p_zero, seed):
-            if keep_dense:
-                self.dense.append(W)
-            if name == "gu":                    # columns g0,u0,g1,u1,...: a pair-summing step adds gate_j and up_j
-                W = np.ascontiguousarray(W.reshape(2, ffn, W.shape[1]).transpose(1, 0, 2).reshape(2 * ffn, W.shape[1]))
-            c0, c1 = shard_range(W.shape[0], rank, world)
-            assert name != "gu" or (c0 % 2 == 0 and c1 % 2 == 0), "pair sums need even shard boundaries"
-            w = sp.Weights(W[c0:c1], sp.FMT_U16_V256).upload()
-            self.weights.append(w)
-            self.stream_bytes += w.stream_bytes
-            self.params += W.shape[0] * W.shape[1]
+        if weights is None:
+            weights = StackWeights(layers, hidden, ffn, kv, p_zero, seed, rank, world, keep_dense)
+        assert weights.shape == (layers, hidden, ffn, kv) and (weights.rank, weights.world) == (rank, world)
+        self.shared_weights = weights
+        self.weights, self.stream_bytes, self.params, self.dense = weights.weights, weights.stream_bytes, weights.params, weights.dense
 
         # ---- activation buffers (full width on every rank) and step counters in one arena
         n_steps = 4 * layers
@@ -194,3 +217,72 @@ def reference_forward(dense, layers, hidden, ffn, kv, x_i8, gemv_dense, quant):
         xg, _ = quant(np.ascontiguousarray(out["gu"]))
         out["down"] = gemv_dense(xg.reshape(-1), Wd).reshape(M, -1)
     return out
+
+
+class NcclStack:
+    """The same column-sharded stack with NCCL between the steps instead of the fused exchange: per
+    step one per-call matmul on this rank's columns (sptmm_gemv), an all-gather of the int32
+    results (ncclAllGather through torch.distributed) and the quantiser kernel
+    (sptmm_quantize_absmax) on what arrived; a whole pass is captured in one CUDA graph.  It is the
+    comparator the fused exchange is measured against, and a second implementation of the same
+    numbers (bit-exact with TernaryStack).  NCCL's buffers stay NCCL's: nothing of this library
+    touches peer memory here."""
+
+    def __init__(self, weights: StackWeights, M=1, group=None):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.group = torch, dist, group
+        self.layers, self.hidden, self.ffn, self.kv = weights.shape
+        self.M, self.rank, self.world, self.w = M, weights.rank, weights.world, weights.weights
+        self.stream_bytes = weights.stream_bytes
+        hidden, ffn, kv = self.hidden, self.ffn, self.kv
+        # (output columns of the step, columns the next step reads, pair sums?)
+        self.plan = [(hidden + 2 * kv, hidden, False), (hidden, hidden, False), (2 * ffn, ffn, True), (hidden, hidden, False)]
+        self.x_in = torch.zeros(M, hidden, dtype=torch.int8, device="cuda")
+        self.xq = [torch.zeros(M, max(hidden, ffn), dtype=torch.int8, device="cuda") for _ in range(2)]
+        self.part = {n: torch.zeros(M, (n * (self.rank + 1)) // self.world - (n * self.rank) // self.world, dtype=torch.int32, device="cuda")
+                     for n in {p[0] for p in self.plan}}
+        self.full = {n: torch.zeros(self.world, M, n // self.world, dtype=torch.int32, device="cuda") for n in {p[0] for p in self.plan}}
+        for n in self.full:
+            assert n % self.world == 0, "the NCCL variant needs equal shards"
+        self.scales = torch.zeros(4 * self.layers, M, dtype=torch.float32, device="cuda")
+        self.graph = None
+
+    def set_input(self, x_i8: np.ndarray) -> None:
+        self.x_in.copy_(self.torch.from_numpy(np.ascontiguousarray(x_i8, dtype=np.int8).reshape(self.M, self.hidden)))
+
+    def _pass(self, stream: int) -> None:
+        x = self.x_in
+        for s in range(4 * self.layers):
+            n_out, k_next, pair = self.plan[s % 4]
+            part, full = self.part[n_out], self.full[n_out]
+            self.w[s].gemv(x, self.M, part, sp.I8, stream=stream)
+            if self.world > 1:
+                self.dist.all_gather_into_tensor(full, part, group=self.group)
+            else:
+                full.copy_(part.view(1, self.M, n_out))
+            if s + 1 < 4 * self.layers:
+                x = self.xq[s & 1]
+                sp.quantize_absmax(full, self.M, k_next, x, self.scales[s + 1], shard=n_out // self.world, pair=pair, stream=stream)
+        self.last = full
+
+    def forward(self) -> None:
+        """One pass on the current stream: the first call runs eagerly (NCCL sets itself up), the
+        second captures the pass in a CUDA graph, later calls replay it."""
+        torch = self.torch
+        st = torch.cuda.current_stream()
+        if self.graph is not None:
+            self.graph.replay()
+        elif getattr(self, "_warm", False):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st if st != torch.cuda.default_stream() else None):
+                self._pass(torch.cuda.current_stream().cuda_stream)
+            self.graph = g
+            g.replay()
+        else:
+            self._pass(st.cuda_stream)
+            self._warm = True
+
+    def result(self) -> np.ndarray:
+        """The last step's int32 output (M x hidden), after a synchronise."""
+        return self.last.cpu().numpy().transpose(1, 0, 2).reshape(self.M, -1)

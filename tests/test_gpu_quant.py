@@ -62,8 +62,14 @@ def test_quantize_absmax_row_stride_pairs_and_shards():
     torch.cuda.synchronize()
     want_q, want_s = O.quant_absmax_i8(rows)
     assert (q.cpu().numpy() == want_q).all() and (s.cpu().numpy() == want_s).all()
+    # the leading columns only (a reader of part of the gathered row)
+    sp.quantize_absmax(dev(gathered), M, K - 100, q[:, :K - 100].contiguous(), None, shard=shard)
+    qq = torch.zeros((M, K - 100), dtype=torch.int8, device="cuda")
+    sp.quantize_absmax(dev(gathered), M, K - 100, qq, None, shard=shard)
+    torch.cuda.synchronize()
+    assert (qq.cpu().numpy() == O.quant_absmax_i8(np.ascontiguousarray(rows[:, :K - 100]))[0]).all()
     with pytest.raises(sp.SptmmError):
-        sp.quantize_absmax(dev(gathered), M, K, q, None, shard=7)
+        sp.quantize_absmax(dev(gathered), M, K // 2, q, None, shard=7, pair=True)
 
 
 @pytest.mark.parametrize("fmt", [sp.FMT_U16_V256, sp.FMT_DELTA_LANE])

@@ -245,14 +245,14 @@ def test_producer_side_quantiser_full_width_rows():
 @pytest.mark.parametrize("M", [1, 2, 4, 5, 16])
 def test_settled_exchange(M):
     """x_kind 5: tagged words watched by one CTA each, local counters, and (M > 1) a local int8 tile
-    fetched by bulk copy.  Parts of rows, pair sums, a buffer written twice in a run, odd widths
-    that fall back to the polling reader, several runs; bit-exact against the oracle chain."""
+    fetched by bulk copy.  Parts of rows, pair sums, a buffer written twice in a run, several runs;
+    bit-exact against the oracle chain.  Row lengths that are no multiple of 4 are refused."""
     K1, N1, off, K2, H, N3 = 512, 448, 64, 320, 288, 200
     W1 = sp.gen_ternary_iid(K1, N1, 0.4, 1)
     W2 = sp.gen_ternary_iid(K2, 2 * H, 0.5, 2)
     W2i = np.ascontiguousarray(W2.reshape(2, H, K2).transpose(1, 0, 2).reshape(2 * H, K2))
     W3 = sp.gen_ternary_iid(H, N1, 1 / 3, 3)            # back to width N1: its output reuses W1's buffer
-    W4 = sp.gen_ternary_iid(N1 - 3, N3, 0.6, 4)         # an odd row length (445 columns)
+    W4 = sp.gen_ternary_iid(N1 - 4, N3, 0.6, 4)         # part of a row again (444 columns)
     w1, w2, w3, w4 = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (W1, W2i, W3, W4))
     X = O.gen_x_i8(M * K1, 4)
     c1 = torch.zeros((M, N1), dtype=torch.int32, device="cuda")      # written by steps 0 and 2
@@ -271,7 +271,7 @@ def test_settled_exchange(M):
     r2 = O.gemv_i8_dense(q1.reshape(-1), W2)
     q2, sc2 = O.quant_absmax_i8(r2[:, :H], r2[:, H:])
     r3 = O.gemv_i8_dense(q2.reshape(-1), W3)
-    q3, _ = O.quant_absmax_i8(np.ascontiguousarray(r3[:, :N1 - 3]))
+    q3, _ = O.quant_absmax_i8(np.ascontiguousarray(r3[:, :N1 - 4]))
     r4 = O.gemv_i8_dense(q3.reshape(-1), W4)
     for run in range(5):
         seq.run()
@@ -280,6 +280,12 @@ def test_settled_exchange(M):
         assert (((c1.cpu().numpy() << 8) >> 8) == r3).all()
         assert (((c2.cpu().numpy() << 8) >> 8) == r2[:, :H] + r2[:, H:]).all()
         assert (s2.cpu().numpy() == sc1).all() and (s3.cpu().numpy() == sc2).all()
+    wodd = sp.Weights(sp.gen_ternary_iid(N1 - 3, N3, 0.6, 4), sp.FMT_U16_V256).upload()
+    with pytest.raises(sp.SptmmError):
+        sp.Sequence([{"w": w1, "X": dev(X), "C": c1}, {"w": wodd, "X": c1, "ldx": N1, "C": c4, "x_kind": 5, "dep": 0}], M=M)
+    with pytest.raises(sp.SptmmError):          # the settled exchange does not mix with the polling ones
+        sp.Sequence([{"w": w1, "X": dev(X), "C": c1}, {"w": w3, "X": c2, "C": c1, "x_kind": 5, "dep": 0},
+                     {"w": w4, "X": c1, "ldx": N1, "C": c4, "x_kind": 1, "dep": 1}], M=M)
 
 
 def test_tagged_exchange_is_validated():
