@@ -306,6 +306,13 @@ int sptmm_seq_run(sptmm_seq *seq, void *stream);
 /* status (if not NULL): waits for the device, then reads the error word a run raises when one of
  * its bounded waits ran out (0 = all good).  stream_bytes (if not NULL): encoded bytes per run. */
 int sptmm_seq_status(sptmm_seq *seq, uint32_t *status, uint64_t *stream_bytes);
+/* How often a waiting thread reloads a step counter (or a word of the settled exchange) before it
+ * gives up, raises the status word and lets the run finish without further waiting.  0 restores
+ * the default of 2^21 reloads (seconds).  A host that supervises several GPUs sets this to what
+ * its own timeout allows; the status word tells it that a peer never delivered:
+ * bit 0 a weight copy never arrived, bit 1 a producer's output never arrived, bit 2 a ring slot
+ * was never freed, bit 3 row maxima never arrived, bit 4 a local arrival counter never filled. */
+int sptmm_seq_set_wait_limit(sptmm_seq *seq, uint32_t polls);
 /* No counterpart in the reference.  Runs a sequence of at most 16 steps WITHOUT allocating any
  * device memory: for callers that cannot call cudaMalloc when they need the result -- code inside
  * a closed, pre-sized memory pool, a real-time loop that may not block on the allocator, a host

@@ -83,6 +83,7 @@ def _load() -> C.CDLL:
         "sptmm_seq_run": (i32, [vp, vp]),
         "sptmm_seq_run_static": (i32, [vp, u32, u32, vp, C.POINTER(u32)]),
         "sptmm_seq_status": (i32, [vp, C.POINTER(u32), C.POINTER(u64)]),
+        "sptmm_seq_set_wait_limit": (i32, [vp, u32]),
         "sptmm_seq_free": (i32, [vp]),
         "sptmm_device_count": (i32, [C.POINTER(C.c_int)]),
         "sptmm_set_device": (i32, [C.c_int]),
@@ -108,7 +109,7 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_status", "sptmm_quantize_absmax", "sptmm_gemv_scaled", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait", "sptmm_gemv_host_batch",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
-           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_shared_bytes_for", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_free",
+           "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_shared_bytes_for", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_wait_limit", "sptmm_seq_free",
            "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync", "sptmm_stream_wait"]
 
@@ -339,6 +340,10 @@ class Sequence:
         nb = C.c_uint64(0)
         check(lib.sptmm_seq_status(self._h, None, C.byref(nb)))
         return nb.value
+
+    def set_wait_limit(self, polls: int) -> None:
+        """Reloads before a device-side wait gives up and raises the status word (0 = default)."""
+        check(lib.sptmm_seq_set_wait_limit(self._h, polls))
 
     def set_trace(self, dev_tensor) -> None:
         """Tuning build only (SPTMM_B200_TUNING=1)."""

@@ -233,7 +233,7 @@ __global__ void __launch_bounds__(256) k_i2s(const I2sParams p)
 
 // --------------------------------------------------------------------------------------------
 template <auto kern, typename Prm>
-static int launch_generic(const Prm &prm, dim3 grid, size_t smem, bool pdl, cudaStream_t st)
+static int launch_generic(const Prm &prm, dim3 grid, size_t smem, bool pdl, cudaStream_t st, uint32_t threads = 256)
 {
     if (smem > 48 * 1024) {          // opt in to large dynamic shared memory once per kernel and device
         static std::atomic<int> configured_device{-1};     // one instance per kernel (the kernel is a template argument)
@@ -245,7 +245,7 @@ static int launch_generic(const Prm &prm, dim3 grid, size_t smem, bool pdl, cuda
         }
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.gridDim = grid; cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -353,14 +353,18 @@ int launch_i2s(const GemvArgs &a)
     if (smem > 227 * 1024) return fail(SPTMM_ERR_UNSUPPORTED, "i2s: K=%u does not fit shared memory", w.K);
     I2sParams prm{(const uint32_t *)a.arrays[0], (const int8_t *)a.X, (int32_t *)a.C, w.K, w.N, a.M,
                   (a.flags & SPTMM_X_COLMAJOR) ? 1u : 0u, (a.flags & SPTMM_C_COLMAJOR) ? 1u : 0u};
-    const dim3 grid((w.N + 31) / 32, (a.M + mt - 1) / mt, 1);
+    // Four columns per warp.  Small matrices get small CTAs so that every SM has one (the 2560
+    // columns of the 2B shapes: 160 CTAs of 128 threads, the reference's own launch shape,
+    // bitnet_kernels.cuh:75-111); wide ones keep 256 threads, i.e. fewer copies of X per column.
+    const uint32_t threads = w.N <= 8192 ? 128u : 256u, cols_per_cta = threads / 8;
+    const dim3 grid((w.N + cols_per_cta - 1) / cols_per_cta, (a.M + mt - 1) / mt, 1);
     const bool pdl = (a.flags & SPTMM_LAUNCH_PDL) != 0;
     cudaStream_t st = (cudaStream_t)a.stream;
     switch (mt) {
-        case 1: return launch_generic<k_i2s<1>>(prm, grid, smem, pdl, st);
-        case 2: return launch_generic<k_i2s<2>>(prm, grid, smem, pdl, st);
-        case 4: return launch_generic<k_i2s<4>>(prm, grid, smem, pdl, st);
-        case 8: return launch_generic<k_i2s<8>>(prm, grid, smem, pdl, st);
+        case 1: return launch_generic<k_i2s<1>>(prm, grid, smem, pdl, st, threads);
+        case 2: return launch_generic<k_i2s<2>>(prm, grid, smem, pdl, st, threads);
+        case 4: return launch_generic<k_i2s<4>>(prm, grid, smem, pdl, st, threads);
+        case 8: return launch_generic<k_i2s<8>>(prm, grid, smem, pdl, st, threads);
     }
     return fail(SPTMM_ERR_INVALID, "internal: row tile %d", mt);
 }

@@ -140,6 +140,7 @@ struct SeqParams {
     unsigned char *xq;
     uint32_t xq_stride;
     unsigned long long target_local;   // settle[i] >= target_local  <=>  every CTA of THIS GPU has arrived in this run
+    uint32_t poll_limit;               // reloads of a counter (or of a settled-exchange word) before a wait gives up
 };
 
 #ifdef SPTMM_TUNING
@@ -705,14 +706,15 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;
 // One arrival of this CTA at a local counter, then wait until every CTA of this GPU has arrived
 // (thread 0 polls, bounded; the others wait at the CTA barrier).  The release covers what the
 // CTA's threads wrote before the barrier in front of it.
-__device__ __forceinline__ void settle_barrier(unsigned long long *ctr, unsigned long long target, uint32_t *failed, uint32_t *status)
+__device__ __forceinline__ void settle_barrier(unsigned long long *ctr, unsigned long long target, uint32_t *failed, uint32_t *status,
+                                               uint32_t poll_limit)
 {
     consumer_sync();
     if (threadIdx.x == 0) {
         asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
         if (!*failed) {
             unsigned long long v = 0;
-            for (uint32_t it = 0; it < (1u << 21); it++) {
+            for (uint32_t it = 0; it < poll_limit; it++) {
                 asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
                 if (v >= target) break;
             }
@@ -744,7 +746,7 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
     auto arrived = [&](const int32_t *w) {          // wait for one word to carry the tag; returns its value
         int v = __ldcg(w);
         for (uint32_t it = 0; ok && ((uint32_t)v >> 24) != tag; it++) {
-            if (it >= kPollLimit) { ok = false; break; }
+            if (it >= p.poll_limit) { ok = false; break; }
             v = ld_fresh(w, sys);
         }
         return untag(v);
@@ -753,7 +755,7 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
         for (uint32_t i = tid; i < nk; i += nt) (void)arrived(A + k0 + i);
         if (!ok && !*failed) { *failed = 1; atomicOr(p.status, 2u); }
         SEQ_MARK(p, s, 0, failed);
-        settle_barrier(c1, p.target_local, failed, p.status);
+        settle_barrier(c1, p.target_local, failed, p.status, p.poll_limit);
         SEQ_MARK(p, s, 1, failed);
         // the row is complete: 16-byte loads, values kept in registers between absmax and rounding
         // (the host admits only rows that fit: K a multiple of 4, at most 14336, 16-byte aligned)
@@ -778,7 +780,7 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
             for (int m = 0; m < MT; m++)
                 if (((uint32_t)v[m] >> 24) != tag) { stale = true; v[m] = ld_fresh(A + (size_t)m * d.ldx + k, sys); }
             if (!stale) break;
-            if (it >= kPollLimit) ok = false;
+            if (it >= p.poll_limit) ok = false;
         }
         if (warp * 32 < nk) {
 #pragma unroll
@@ -792,7 +794,7 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
         consumer_sync();
         SEQ_MARK(p, s, 0, failed);
         if (tid < p.M && rowmax_s[tid]) atomicMax(amax_g + tid, (uint32_t)rowmax_s[tid]);
-        settle_barrier(c1, p.target_local, failed, p.status);
+        settle_barrier(c1, p.target_local, failed, p.status, p.poll_limit);
         SEQ_MARK(p, s, 1, failed);
         float *scale_s = reinterpret_cast<float *>(red);
         if (tid < (uint32_t)MT) {
@@ -814,7 +816,7 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
             if constexpr (MT == 4) *reinterpret_cast<uint32_t *>(tile_g + (size_t)k * 4) = o[0];
             else *reinterpret_cast<uint4 *>(tile_g + (size_t)k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        settle_barrier(c2, p.target_local, failed, p.status);
+        settle_barrier(c2, p.target_local, failed, p.status, p.poll_limit);
         SEQ_MARK(p, s, 2, failed);
         // the finished tile: one bulk copy (in pieces of at most 64 KB) into the tile's place
         const uint32_t bytes = d.K * MT;
@@ -962,7 +964,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             if (tid == 0 && !failed) {
                 const unsigned long long *ctr = p.counters + d.dep;
                 unsigned long long v = 0;
-                for (uint32_t it = 0; it < (1u << 21); it++) {
+                for (uint32_t it = 0; it < p.poll_limit; it++) {
                     if (p.n_peers) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
                     else asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
                     if (v >= p.target) break;
@@ -1258,6 +1260,7 @@ struct sptmm_seq {
     bool tagged = false;             // some step reads tagged words: run the kernel variant that knows them
     bool uses_amax = false;          // some step is x_kind 3: the row-maxima area is in use
     bool settled = false;            // the steps with a producer are all x_kind 5: the kernel variant for that exchange
+    uint32_t poll_limit = 1u << 21;  // see sptmm_seq_set_wait_limit
     void *counter_peers[kMaxPeers] = {};
 };
 
@@ -1598,6 +1601,7 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     prm.settle = (unsigned long long *)((char *)prm.counters + seq_settle_offset(q->nsteps));
     prm.xq = (unsigned char *)q->d_xq; prm.xq_stride = q->xq_stride;
     prm.target_local = (unsigned long long)q->G * q->epoch;
+    prm.poll_limit = q->poll_limit;
     // the row maxima sit behind the counters; a sequence without x_kind 3 steps never touches them
     for (uint32_t r = 0; r < kMaxPeers; r++)
         prm.amax_peers[r] = q->uses_amax && q->counter_peers[r] ? (uint32_t *)((char *)q->counter_peers[r] + (size_t)q->nsteps * 8) : nullptr;
@@ -1630,6 +1634,13 @@ extern "C" int sptmm_seq_set_trace(sptmm_seq *q, void *dev_ptr)
     return SPTMM_OK;
 }
 #endif
+
+extern "C" int sptmm_seq_set_wait_limit(sptmm_seq *q, uint32_t polls)
+{
+    if (!q) return fail(SPTMM_ERR_INVALID, "seq_set_wait_limit: null handle");
+    q->poll_limit = polls ? polls : 1u << 21;
+    return SPTMM_OK;
+}
 
 extern "C" int sptmm_seq_free(sptmm_seq *q)
 {
@@ -1763,7 +1774,7 @@ extern "C" int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n, uin
     prm.target = q.G;                              // counters were just cleared: one run's worth
     prm.nsteps = n; prm.M = M; prm.max_cols = q.max_cols; prm.ring_slots = q.ring_slots;
     prm.xs_bytes = q.xs_bytes; prm.G = q.G; prm.slot_blocks = q.slot_blocks; prm.one = 1; prm.run_mod = 0; prm.run_parity = 0; prm.amax = nullptr; prm.my_rank = 0;
-    prm.settle = nullptr; prm.xq = nullptr; prm.xq_stride = 0; prm.target_local = 0;
+    prm.settle = nullptr; prm.xq = nullptr; prm.xq_stride = 0; prm.target_local = 0; prm.poll_limit = 1u << 21;
     for (uint32_t r = 0; r < kMaxPeers; r++) prm.amax_peers[r] = nullptr;
     int rc = SPTMM_OK;
     switch (q.mt) {

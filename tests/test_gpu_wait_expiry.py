@@ -1,0 +1,78 @@
+"""What a sequence does when a peer never delivers: every device-side wait is bounded, so the run
+ends by itself, the status word says which kind of wait ran out, and the device stays usable.
+
+The missing peer is made on the host, without a second GPU and without any fault: the sequence is
+created as rank 0 of TWO ranks (sptmm_seq_create_shared), the second rank's output and counter
+areas are ordinary local buffers, and no second rank ever runs.  Its arrivals (half of every step
+counter's target) and its columns of every output therefore never come; with the wait limit set
+to a few thousand reloads the run returns within milliseconds."""
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import sptmm_b200 as sp
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    torch.cuda.set_device(0)
+    yield
+    torch.cuda.synchronize()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("x_kind,M", [(1, 1), (1, 4), (5, 1), (5, 4)])
+def test_missing_peer_ends_the_run_with_a_status(x_kind, M):
+    K, N = 256, 128                                     # the full layer; this "rank" owns columns 0..63
+    W1 = sp.gen_ternary_iid(K, N, 0.4, 1)
+    W2 = sp.gen_ternary_iid(N, N, 0.5, 2)
+    w1 = sp.Weights(W1[: N // 2], sp.FMT_U16_V256).upload()
+    w2 = sp.Weights(W2[: N // 2], sp.FMT_U16_V256).upload()
+    X = O.gen_x_i8(M * K, 3)
+    steps = [{"w": w1, "X": dev(X), "dep": -1, "ldc": N}, {"w": w2, "X": 0, "x_kind": x_kind, "dep": 0, "ldx": N, "ldc": N},
+             {"w": w2, "X": 0, "x_kind": x_kind, "dep": 1, "ldx": N, "ldc": N}]
+    # rank 0's buffers and the never-running rank 1's: plain local memory, zeroed
+    bufs = [[torch.zeros((M, N), dtype=torch.int32, device="cuda") for _ in range(2)] for _ in range(3)]
+    steps[1]["X"], steps[2]["X"] = bufs[0][0], bufs[1][0]
+    for s, st in enumerate(steps):
+        st["C_peers"] = [b.data_ptr() for b in bufs[s]]          # this rank's shard starts at column 0 of both
+    nbytes = sp.seq_shared_bytes([dict(st, C=1) for st in steps], M)
+    areas = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    seq = sp.Sequence(steps, M=M, counter_peers=[a.data_ptr() for a in areas], rank=0)
+    seq.set_wait_limit(1 << 12)
+    seq.run()
+    status = seq.status()                               # waits for the device: the run came back by itself
+    assert status & 2, "the wait for the producer's output must have run out (status %d)" % status
+    assert status & ~(2 | 16) == 0, status
+    # the first step has no dependency and is complete: this rank's columns, in both copies
+    want = O.gemv_i8_dense(X, W1[: N // 2]).reshape(M, N // 2)
+    for b in bufs[0]:
+        got = b.cpu().numpy()[:, : N // 2]
+        got = (got << 8) >> 8 if x_kind == 5 else got   # the settled exchange stores tagged words
+        assert (got == want).all()
+    seq.close()
+
+    # the device is as usable as before: a complete sequence on the same weights is exact
+    c1 = torch.zeros((M, N // 2), dtype=torch.int32, device="cuda")
+    ok = sp.Sequence([{"w": w1, "X": dev(X), "C": c1}], M=M)
+    ok.run()
+    assert ok.status() == 0
+    assert (c1.cpu().numpy() == want).all()
+
+
+def test_wait_limit_rejects_a_null_handle_and_restores_the_default():
+    W = sp.gen_ternary_iid(64, 32, 0.5, 1)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload()
+    c = torch.zeros(32, dtype=torch.int32, device="cuda")
+    seq = sp.Sequence([{"w": w, "X": dev(O.gen_x_i8(64, 1)), "C": c}])
+    seq.set_wait_limit(0)                                # back to the default
+    seq.run()
+    assert seq.status() == 0
+    assert sp.lib.sptmm_seq_set_wait_limit(None, 5) != 0
