@@ -88,6 +88,14 @@ int sptmm_gen_ternary_fixed(uint32_t K, uint32_t N, uint32_t S, int8_t *W);
 /* No counterpart in the reference: i.i.d. entries, P(0)=p_zero, P(+1)=P(-1), splitmix64 per column. */
 int sptmm_gen_ternary_iid(uint32_t K, uint32_t N, double p_zero, uint64_t seed, int8_t *W);
 
+/* Real-valued weights -> ternary, the absmean rule of BitNet b1.58 (no counterpart in the reference,
+ * whose matrices are synthetic, main.cu:248-265): scale = mean(|W|) over the matrix,
+ * W_t = clamp(round_half_even(W / (scale + 1e-5)), -1, +1), so that W ~ scale * W_t.
+ * W: K x N column-major like every matrix here, `dtype` SPTMM_F16 or SPTMM_F32 (host memory);
+ * W_ternary: K x N int8 ready for sptmm_encode; *scale (optional): the factor a de-quantising
+ * epilogue multiplies by (sptmm_gemv_scaled's w_scale). */
+int sptmm_ternarise_absmean(const void *W, uint32_t dtype, uint32_t K, uint32_t N, int8_t *W_ternary, float *scale);
+
 /* ---- encoding (host).  Replaces the device-side encoder prepareW_map (main.cu:202-489).    */
 
 /* S = 0 derives the per-sign capacity from the longest list (rounded up as the format needs);
@@ -335,6 +343,64 @@ int sptmm_seq_run_static(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t
                          uint32_t *status_out);
 
 int sptmm_seq_free(sptmm_seq *seq);
+
+/* ---- a stack of ternary layers over the GPUs of one node ----------------------------------------- */
+
+/* No counterpart in the reference (one matmul per launch on one GPU, main.cu:994-1458, 1861); the
+ * layer shapes are the ones its dispatch ladders hard-code (main.cu:1107-1190).  `layers` layers of
+ * four dependent steps -- qkv (hidden -> hidden + 2 kv), o (hidden -> hidden, on the q part of
+ * qkv), gate|up fused (hidden -> 2 ffn, stored as gate_j + up_j) and down (ffn -> hidden) -- on
+ * int8 activations with int32 results and the per-row absmax quantiser between the steps.  Every
+ * matrix is sharded by contiguous column ranges over `world` ranks (one process or host thread per
+ * GPU); a forward pass is one persistent kernel per rank.  Weights are synthetic: i.i.d. ternary
+ * with P(0) = p_zero, a seed per matrix derived from `seed`, identical on every rank. */
+typedef struct sptmm_stack_config {
+    uint32_t layers, hidden, ffn, kv;
+    double p_zero;
+    uint64_t seed;
+    uint32_t rank, world;
+} sptmm_stack_config;
+
+/* how a step's int32 output becomes the next step's int8 input (sptmm_seq_step::x_kind) */
+enum {
+    SPTMM_STACK_AUTO = 0,            /* settled across GPUs and from eight rows upward, else counters */
+    SPTMM_STACK_COUNTERS = 1,        /* x_kind 1: step counters, readers quantise                    */
+    SPTMM_STACK_TAGGED = 2,          /* x_kind 2: tagged words polled by every reader                */
+    SPTMM_STACK_ROW_MAXIMA = 3,      /* x_kind 3 for readers of whole rows (1 otherwise)             */
+    SPTMM_STACK_PRODUCER_QUANT = 4,  /* x_kind 4: producers quantise, packed int8 travels            */
+    SPTMM_STACK_SETTLED = 5          /* x_kind 5: one watcher per word, local counters, int8 tile    */
+};
+
+typedef struct sptmm_stack_weights sptmm_stack_weights;   /* this rank's shard of every matrix, uploaded */
+typedef struct sptmm_stack sptmm_stack;
+
+/* Generates, shards, encodes and uploads (to the current device) this rank's columns of every
+ * matrix.  Independent of the batch size: stacks for several M may share one set. */
+int sptmm_stack_weights_create(const sptmm_stack_config *cfg, sptmm_stack_weights **out);
+int sptmm_stack_weights_info(const sptmm_stack_weights *w, uint64_t *stream_bytes, uint64_t *params);
+/* matrix `index` (4 per layer: qkv, o, gate|up interleaved, down) as an encoded, uploaded handle */
+int sptmm_stack_weights_matrix(const sptmm_stack_weights *w, uint32_t index, const sptmm_weights **out);
+int sptmm_stack_weights_free(sptmm_stack_weights *w);
+
+/* Bytes of one rank's arena (activation buffers, synchronisation area, input, scales) for M rows.
+ * With several ranks the caller allocates one arena per rank, zeroes it, maps every rank's arena
+ * into every rank's address space (CUDA IPC, the virtual memory API, a symmetric-memory
+ * allocator) and passes the `world` base addresses, valid in THIS process, as arena_peers; only
+ * the library's own kernels touch peer memory, with plain stores.  With one rank arena_peers may
+ * be NULL and the library allocates. */
+uint64_t sptmm_stack_arena_bytes(const sptmm_stack_weights *w, uint32_t M, uint32_t exchange);
+int sptmm_stack_create(sptmm_stack_weights *w, uint32_t M, uint32_t exchange, void *const *arena_peers,
+                       sptmm_stack **out);
+int sptmm_stack_set_input(sptmm_stack *st, const int8_t *x_host);        /* M x hidden int8, host memory */
+int sptmm_stack_forward(sptmm_stack *st, void *stream);                   /* asynchronous, one launch */
+/* This rank's copy of "qkv", "o", "gu" (pair sums) or "down" (the final result) of the last layer,
+ * int32 M x *width, after waiting for the device; host_out may be NULL to ask for the width. */
+int sptmm_stack_buffer(sptmm_stack *st, const char *name, int32_t *host_out, uint32_t *width);
+int sptmm_stack_status(sptmm_stack *st, uint32_t *status);                /* see sptmm_seq_status */
+int sptmm_stack_exchange(const sptmm_stack *st, uint32_t *exchange);      /* the exchange in use */
+int sptmm_stack_sequence(sptmm_stack *st, sptmm_seq **seq);               /* the stack's sequence (not to be freed) */
+int sptmm_stack_wait_limit(sptmm_stack *st, uint32_t polls);              /* see sptmm_seq_set_wait_limit */
+int sptmm_stack_free(sptmm_stack *st);
 
 /* ---- small device helpers so a C caller needs no CUDA headers ------------------------------ */
 int sptmm_device_count(int *count);

@@ -410,3 +410,26 @@ void oracle_quant_absmax_i8(const int32_t *A, uint32_t lda, const int32_t *B, ui
         if (scale) scale[m] = (float)amax / 127.0f;
     }
 }
+
+/* Absmean ternarisation of real-valued weights (BitNet b1.58): scale = mean(|W|) over the matrix,
+ * W_t = clamp(round_half_even(W / (scale + 1e-5)), -1, +1).  The reference has no such step (its
+ * matrices are synthetic, main.cu:248-265); this restates the rule the library's
+ * sptmm_ternarise_absmean implements, for the tests.  W: K x N fp32, column-major; the mean is a
+ * double-precision sum per column, the columns added in order. */
+void oracle_ternarise_absmean(const float *W, uint32_t K, uint32_t N, int8_t *out, float *scale)
+{
+    double total = 0.0;
+    for (uint32_t c = 0; c < N; c++) {
+        double s = 0.0;
+        for (uint32_t k = 0; k < K; k++) s += fabs((double)W[(uint64_t)c * K + k]);
+        total += s;
+    }
+    volatile float mean = (float)(total / ((double)K * N));
+    volatile float inv = 1.0f / (mean + 1e-5f);
+    for (uint64_t i = 0; i < (uint64_t)K * N; i++) {
+        volatile float prod = W[i] * inv;
+        float q = rintf(prod);
+        out[i] = (int8_t)(q > 1.0f ? 1 : (q < -1.0f ? -1 : (int)q));
+    }
+    if (scale) *scale = mean;
+}

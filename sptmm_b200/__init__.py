@@ -55,6 +55,7 @@ def _load() -> C.CDLL:
         "sptmm_version": (i32, []),
         "sptmm_gen_ternary_fixed": (i32, [u32, u32, u32, vp]),
         "sptmm_gen_ternary_iid": (i32, [u32, u32, C.c_double, u64, vp]),
+        "sptmm_ternarise_absmean": (i32, [vp, u32, u32, u32, vp, C.POINTER(C.c_float)]),
         "sptmm_encode": (i32, [vp, u32, u32, u32, u32, u32, C.POINTER(vp)]),
         "sptmm_weights_info_get": (i32, [vp, C.POINTER(WeightsInfo)]),
         "sptmm_weights_array": (i32, [vp, u32, C.POINTER(vp), C.POINTER(vp), C.POINTER(u64), C.POINTER(C.c_char_p)]),
@@ -85,6 +86,20 @@ def _load() -> C.CDLL:
         "sptmm_seq_status": (i32, [vp, C.POINTER(u32), C.POINTER(u64)]),
         "sptmm_seq_set_wait_limit": (i32, [vp, u32]),
         "sptmm_seq_free": (i32, [vp]),
+        "sptmm_stack_weights_create": (i32, [vp, C.POINTER(vp)]),
+        "sptmm_stack_weights_info": (i32, [vp, C.POINTER(u64), C.POINTER(u64)]),
+        "sptmm_stack_weights_matrix": (i32, [vp, u32, C.POINTER(vp)]),
+        "sptmm_stack_weights_free": (i32, [vp]),
+        "sptmm_stack_arena_bytes": (u64, [vp, u32, u32]),
+        "sptmm_stack_create": (i32, [vp, u32, u32, vp, C.POINTER(vp)]),
+        "sptmm_stack_set_input": (i32, [vp, vp]),
+        "sptmm_stack_forward": (i32, [vp, vp]),
+        "sptmm_stack_buffer": (i32, [vp, C.c_char_p, vp, C.POINTER(u32)]),
+        "sptmm_stack_status": (i32, [vp, C.POINTER(u32)]),
+        "sptmm_stack_exchange": (i32, [vp, C.POINTER(u32)]),
+        "sptmm_stack_sequence": (i32, [vp, C.POINTER(vp)]),
+        "sptmm_stack_wait_limit": (i32, [vp, u32]),
+        "sptmm_stack_free": (i32, [vp]),
         "sptmm_device_count": (i32, [C.POINTER(C.c_int)]),
         "sptmm_set_device": (i32, [C.c_int]),
         "sptmm_dev_alloc": (i32, [C.POINTER(vp), u64]),
@@ -105,11 +120,14 @@ def _load() -> C.CDLL:
 
 
 lib = _load()
-EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid",
+EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid", "sptmm_ternarise_absmean",
            "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_status", "sptmm_quantize_absmax", "sptmm_gemv_scaled", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait", "sptmm_gemv_host_batch",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_shared_bytes_for", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_wait_limit", "sptmm_seq_free",
+           "sptmm_stack_weights_create", "sptmm_stack_weights_info", "sptmm_stack_weights_matrix", "sptmm_stack_weights_free",
+           "sptmm_stack_arena_bytes", "sptmm_stack_create", "sptmm_stack_set_input", "sptmm_stack_forward", "sptmm_stack_buffer",
+           "sptmm_stack_status", "sptmm_stack_exchange", "sptmm_stack_sequence", "sptmm_stack_wait_limit", "sptmm_stack_free",
            "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync", "sptmm_stream_wait"]
 
@@ -150,6 +168,19 @@ def gen_ternary_iid(K: int, N: int, p_zero: float, seed: int) -> np.ndarray:
     return W
 
 
+def ternarise_absmean(W: np.ndarray) -> tuple[np.ndarray, float]:
+    """fp16 / fp32 weights of shape (N, K) (column c of the K x N matrix is row c) -> (int8 ternary
+    matrix of the same shape, scale): the absmean rule of BitNet b1.58 (sptmm_ternarise_absmean)."""
+    if W.dtype not in (np.float16, np.float32) or W.ndim != 2:
+        raise ValueError("W must be a 2-D float16 or float32 array")
+    W = np.ascontiguousarray(W)
+    N, K = W.shape
+    out = np.empty((N, K), dtype=np.int8)
+    scale = C.c_float(0)
+    check(lib.sptmm_ternarise_absmean(W.ctypes.data, F16 if W.dtype == np.float16 else F32, K, N, out.ctypes.data, C.byref(scale)))
+    return out, scale.value
+
+
 class Weights:
     """An encoded ternary matrix (host-owned handle; optionally uploaded to the current device)."""
 
@@ -162,6 +193,15 @@ class Weights:
         check(lib.sptmm_encode(W.ctypes.data, K, N, fmt, split, S, C.byref(h)))
         self._h = h
         self.info = self._info()
+
+    @classmethod
+    def borrow(cls, handle) -> "Weights":
+        """A view of a handle somebody else owns (it is not freed with this object)."""
+        self = cls.__new__(cls)
+        self._h = handle
+        self._borrowed = True
+        self.info = self._info()
+        return self
 
     @classmethod
     def load(cls, path: str) -> "Weights":
@@ -264,7 +304,8 @@ class Weights:
 
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:
-            lib.sptmm_weights_free(self._h)
+            if not getattr(self, "_borrowed", False):
+                lib.sptmm_weights_free(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):
@@ -327,6 +368,13 @@ class Sequence:
                                               C.cast(kp, C.c_void_p), n, rank, C.byref(h)))
         self._h = h
 
+    @classmethod
+    def borrow(cls, handle) -> "Sequence":
+        """A view of a sequence somebody else owns (it is not freed with this object)."""
+        self = cls.__new__(cls)
+        self._h, self._keep, self._borrowed = handle, [], True
+        return self
+
     def run(self, stream: int = 0) -> None:
         check(lib.sptmm_seq_run(self._h, stream))
 
@@ -351,7 +399,8 @@ class Sequence:
 
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:
-            lib.sptmm_seq_free(self._h)
+            if not getattr(self, "_borrowed", False):
+                lib.sptmm_seq_free(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):

@@ -1,8 +1,8 @@
 """A BitNet-b1.58-shaped stack of ternary layers run as one persistent sequence per forward pass.
 
-Plumbing only: this module generates seeded weights, encodes and uploads this rank's column
-shard of every matrix, lays out the activation buffers and builds the step list; all compute is
-the C ABI's sequence kernel (sptmm_seq_*).  The reference has no layer stack, no quantiser and no
+Plumbing only: the stack itself -- weight generation, this rank's column shard of every matrix,
+the buffer layout, the step list -- is the C ABI's sptmm_stack_* (host C++, csrc/stack.cpp) over
+its sequence kernel; this module allocates the peer-visible arena and marshals arguments.  The reference has no layer stack, no quantiser and no
 multi-GPU path; the shapes are the ones its dispatch ladders hard-code (main.cu:1107-1190: fused
 qkv N=3840 and gate|up N=13824 at K=2560, down 6912x2560).
 
@@ -20,6 +20,8 @@ counters live in the same peer-mapped arena (torch symmetric memory), so a forwa
 one kernel launch per rank with no collective call inside.
 """
 from __future__ import annotations
+
+import ctypes as C
 
 import numpy as np
 
@@ -47,155 +49,143 @@ def stack_weights(layers: int, hidden: int, ffn: int, kv: int, p_zero: float, se
             yield l, name, sp.gen_ternary_iid(K, N, p_zero, matrix_seed(seed, l, i))
 
 
+class StackConfig(C.Structure):
+    _fields_ = [("layers", C.c_uint32), ("hidden", C.c_uint32), ("ffn", C.c_uint32), ("kv", C.c_uint32),
+                ("p_zero", C.c_double), ("seed", C.c_uint64), ("rank", C.c_uint32), ("world", C.c_uint32)]
+
+
+AUTO, COUNTERS, TAGGED, ROW_MAXIMA, PRODUCER_QUANT, SETTLED = 0, 1, 2, 3, 4, 5      # sptmm.h: SPTMM_STACK_*
+
+
 class StackWeights:
-    """This rank's column shard of every matrix of the stack, encoded and uploaded; independent of M,
-    so stacks for several batch sizes can share one set."""
+    """This rank's column shard of every matrix of the stack, generated, encoded and uploaded by
+    sptmm_stack_weights_create; independent of M, so stacks for several batch sizes share one set."""
 
     def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, p_zero=1 / 3, seed=0, rank=0, world=1, keep_dense=False):
         self.shape = (layers, hidden, ffn, kv)
         self.rank, self.world = rank, world
-        self.dense = [] if keep_dense else None
-        self.weights, self.stream_bytes, self.params = [], 0, 0
-        for l, name, W in stack_weights(layers, hidden, ffn, kv, p_zero, seed):
-            if keep_dense:
-                self.dense.append(W)
-            if name == "gu":                    # columns g0,u0,g1,u1,...: a pair-summing step adds gate_j and up_j
-                W = np.ascontiguousarray(W.reshape(2, ffn, W.shape[1]).transpose(1, 0, 2).reshape(2 * ffn, W.shape[1]))
-            c0, c1 = shard_range(W.shape[0], rank, world)
-            assert name != "gu" or (c0 % 2 == 0 and c1 % 2 == 0), "pair sums need even shard boundaries"
-            w = sp.Weights(W[c0:c1], sp.FMT_U16_V256).upload()
-            self.weights.append(w)
-            self.stream_bytes += w.stream_bytes
-            self.params += W.shape[0] * W.shape[1]
+        cfg = StackConfig(layers, hidden, ffn, kv, float(p_zero), int(seed) & 0xFFFFFFFFFFFFFFFF, rank, world)
+        h = C.c_void_p()
+        sp.check(sp.lib.sptmm_stack_weights_create(C.byref(cfg), C.byref(h)))
+        self._h = h
+        nb, npar = C.c_uint64(), C.c_uint64()
+        sp.check(sp.lib.sptmm_stack_weights_info(h, C.byref(nb), C.byref(npar)))
+        self.stream_bytes, self.params = nb.value, npar.value
+        self.weights = []
+        for i in range(4 * layers):
+            wh = C.c_void_p()
+            sp.check(sp.lib.sptmm_stack_weights_matrix(h, i, C.byref(wh)))
+            self.weights.append(sp.Weights.borrow(wh))
+        # the dense matrices, for tests that compare with the oracle chain (the same seeds)
+        self.dense = [W for _, _, W in stack_weights(layers, hidden, ffn, kv, p_zero, seed)] if keep_dense else None
 
     def close(self):
-        for w in self.weights:
-            w.close()
-        self.weights = []
+        if getattr(self, "_h", None) is not None and self._h.value:
+            sp.lib.sptmm_stack_weights_free(self._h)
+            self._h = C.c_void_p()
+            self.weights = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class TernaryStack:
+    """sptmm_stack_* behind a Python face: this class allocates the arena (torch symmetric memory
+    across GPUs, so that every rank can address every rank's copy) and marshals arguments; weight
+    generation, sharding, the buffer layout and the step list are the library's."""
+
     def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, M=1, p_zero=1 / 3, seed=0,
                  rank=0, world=1, group=None, keep_dense=False, tagged=None, row_maxima=False, producer_quant=None,
-                 settled=None, weights=None):
-        """weights: a StackWeights built for the same shapes, rank and world (else one is built here)."""
+                 settled=None, weights=None, exchange=None):
+        """weights: a StackWeights built for the same shapes, rank and world (else one is built here).
+        exchange: one of AUTO, COUNTERS, TAGGED, ROW_MAXIMA, PRODUCER_QUANT, SETTLED; the boolean
+        arguments are the older way of naming the same choice."""
         import torch
         self.torch = torch
         self.layers, self.hidden, self.ffn, self.kv, self.M = layers, hidden, ffn, kv, M
         self.rank, self.world = rank, world
-        # How a step's int32 output becomes the next step's int8 input:
-        #  - producer_quant (x_kind 4): the producing step quantises its own columns after a small
-        #    exchange of row maxima and stores int8; readers fetch M*K bytes.  For M >= 4 (None picks
-        #    it there), where every CTA quantising all M rows for itself is what a step costs.
-        #  - tagged (x_kind 2): readers quantise; outputs travel as tagged words, no counters, no
-        #    fences.  Measured on B200: across GPUs that beats the step counters for M <= 4 (2 GPUs,
-        #    M=1: 1.20 ms per pass against 1.51 ms), on one GPU it does not; None picks accordingly.
-        #  - settled (x_kind 5): tagged words as above, but every word is watched by one CTA per GPU,
-        #    the CTAs of a GPU meet at local counters, and for M > 1 each CTA quantises only its own
-        #    columns into a local int8 tile that all fetch with one bulk copy.
-        #    Measured on B200 (30 layers, us per pass; counters / settled): one GPU M=1 1 240 / 1 380,
-        #    M=4 1 890 / 1 900, M=16 4 280 / 3 350; two GPUs M=1 950 (polled tags) / 930, M=4 1 510 / 1 420,
-        #    M=16 3 540 / 2 420.  None picks it across GPUs and, on one GPU, from eight rows upward.
-        explicit = tagged is not None or producer_quant is not None or row_maxima
-        if settled is None:
-            settled = not explicit and (world > 1 or M >= 8)
-        if producer_quant is None:
-            producer_quant = False
-        if settled:
-            tagged, producer_quant = True, False         # the producers store tagged words
-        elif tagged is None:
-            tagged = world > 1 and M <= 4 and not producer_quant
-        self.tagged, self.producer_quant, self.settled = tagged, producer_quant, settled
-        shapes = layer_shapes(hidden, ffn, kv)
-        widths = {name: N for name, _, N in shapes}
-
-        # ---- weights: this rank's columns of every matrix
+        if exchange is None:
+            if settled:
+                exchange = SETTLED
+            elif producer_quant:
+                exchange = PRODUCER_QUANT
+            elif row_maxima:
+                exchange = ROW_MAXIMA
+            elif tagged:
+                exchange = TAGGED
+            elif tagged is False or producer_quant is False or settled is False:
+                exchange = COUNTERS              # the newer exchanges were declined by name
+            else:
+                exchange = AUTO
         if weights is None:
             weights = StackWeights(layers, hidden, ffn, kv, p_zero, seed, rank, world, keep_dense)
         assert weights.shape == (layers, hidden, ffn, kv) and (weights.rank, weights.world) == (rank, world)
         self.shared_weights = weights
         self.weights, self.stream_bytes, self.params, self.dense = weights.weights, weights.stream_bytes, weights.params, weights.dense
-
-        # ---- activation buffers (full width on every rank) and step counters in one arena
-        n_steps = 4 * layers
-        off, cur = {}, 0
-        # step counters + row maxima (+ the producers' packed int8 outputs): the size depends on the
-        # step kinds and shapes only, so a list without buffer addresses gives it
-        xk = 5 if settled else (4 if producer_quant else (2 if tagged else 1))
-        sizing = [{"w": self.weights[s], "X": 1, "C": 1, "dep": s - 1, "x_kind": (0 if s == 0 else xk)} for s in range(n_steps)]
-        off["counters"] = cur; cur += int(sp.seq_shared_bytes(sizing, M))
-        widths["gu"] = ffn                       # stored as pair sums
-        widths["out"] = widths["down"]           # the last step's result: never tagged, no reader inside the kernel
-        for name in ("qkv", "o", "gu", "down", "out"):
-            cur = (cur + 255) & ~255
-            off[name] = cur; cur += M * widths[name] * 4
-        cur = (cur + 255) & ~255
+        nbytes = int(sp.lib.sptmm_stack_arena_bytes(weights._h, M, exchange))
+        if nbytes == 0:
+            raise ValueError("sptmm_stack_arena_bytes: bad M or exchange")
+        h = C.c_void_p()
         if world > 1:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm
-            self.arena = symm.empty(cur, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+            self.arena = symm.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
             self.arena.zero_()
             self.handle = symm.rendezvous(self.arena, group=group if group is not None else dist.group.WORLD)
-            bases = [int(p) for p in self.handle.buffer_ptrs]
+            bases = (C.c_void_p * world)(*[int(p) for p in self.handle.buffer_ptrs])
+            torch.cuda.synchronize()
             dist.barrier()
+            sp.check(sp.lib.sptmm_stack_create(weights._h, M, exchange, bases, C.byref(h)))
         else:
-            self.arena = torch.zeros(cur, dtype=torch.uint8, device="cuda")
-            bases = [self.arena.data_ptr()]
-        self.bases, self.off = bases, off
-        mine = bases[rank]
-        self.x_in = torch.zeros(M, hidden, dtype=torch.int8, device="cuda")
-        self.scales = torch.zeros(n_steps, M, dtype=torch.float32, device="cuda")
-
-        # ---- the step list
-        steps = []
-        xk = 5 if settled else (4 if producer_quant else (2 if tagged else 1))       # a reader of part of a row finds the row's absmax itself
-        xw = 5 if settled else (4 if producer_quant else (2 if tagged else (3 if row_maxima else 1)))    # row_maxima: a reader of a whole row gets its absmax from the producer
-        for l in range(layers):
-            for i, (name, K, N) in enumerate(shapes):
-                s = 4 * l + i
-                c0, _ = shard_range(N, rank, world)
-                st = {"w": self.weights[s], "dep": s - 1, "ldc": widths[name], "scale_out": self.scales[s]}
-                if name == "qkv":
-                    if l == 0:
-                        st.update(X=self.x_in, x_kind=0)
-                    else:
-                        st.update(X=mine + off["down"], x_kind=xw, ldx=hidden)
-                elif name == "o":
-                    st.update(X=mine + off["qkv"], x_kind=xk, ldx=widths["qkv"])
-                elif name == "gu":
-                    st.update(X=mine + off["o"], x_kind=xw, ldx=hidden, c_kind=1)
-                else:
-                    st.update(X=mine + off["gu"], x_kind=xw, ldx=ffn)
-                dst = "out" if s == n_steps - 1 else name
-                o0 = c0 // 2 if name == "gu" else c0      # where this rank's first output column lands
-                if world > 1:
-                    st["C_peers"] = [b + off[dst] + o0 * 4 for b in bases]
-                else:
-                    st["C"] = mine + off[dst] + o0 * 4
-                steps.append(st)
-        counter_peers = [b + off["counters"] for b in bases] if world > 1 else None
-        self.seq = sp.Sequence(steps, M=M, counter_peers=counter_peers, rank=rank)
-        self.n_steps = n_steps
+            self.arena = None
+            sp.check(sp.lib.sptmm_stack_create(weights._h, M, exchange, None, C.byref(h)))
+        self._h = h
+        ex = C.c_uint32()
+        sp.check(sp.lib.sptmm_stack_exchange(h, C.byref(ex)))
+        self.exchange = ex.value
+        self.tagged, self.settled, self.producer_quant = ex.value in (TAGGED, SETTLED), ex.value == SETTLED, ex.value == PRODUCER_QUANT
+        self.n_steps = 4 * layers
+        sh = C.c_void_p()
+        sp.check(sp.lib.sptmm_stack_sequence(h, C.byref(sh)))
+        self.seq = sp.Sequence.borrow(sh)
 
     def set_input(self, x_i8: np.ndarray) -> None:
-        self.x_in.copy_(self.torch.from_numpy(np.ascontiguousarray(x_i8, dtype=np.int8).reshape(self.M, self.hidden)))
+        x = np.ascontiguousarray(x_i8, dtype=np.int8).reshape(self.M, self.hidden)
+        sp.check(sp.lib.sptmm_stack_set_input(self._h, x.ctypes.data))
 
     def forward(self, stream: int = 0) -> None:
-        self.seq.run(stream)
+        sp.check(sp.lib.sptmm_stack_forward(self._h, stream))
 
     def buffer(self, name: str) -> np.ndarray:
         """This rank's copy of an activation buffer (int32, M x width), after a synchronise: the
         last values written to "qkv", "o", "gu" and, as "down", the stack's final result."""
-        width = self.ffn if name == "gu" else dict((n, N) for n, _, N in layer_shapes(self.hidden, self.ffn, self.kv))[name]
-        src = "out" if name == "down" else name
-        t = self.arena[self.off[src]: self.off[src] + self.M * width * 4].view(self.torch.int32)
-        v = t.cpu().numpy().reshape(self.M, width)
-        if self.tagged and src != "out":
-            v = (v << 8) >> 8                    # drop the tag byte, sign-extend the 24-bit value
-        return v
+        width = C.c_uint32()
+        sp.check(sp.lib.sptmm_stack_buffer(self._h, name.encode(), None, C.byref(width)))
+        out = np.empty((self.M, width.value), dtype=np.int32)
+        sp.check(sp.lib.sptmm_stack_buffer(self._h, name.encode(), out.ctypes.data, None))
+        return out
 
     def status(self) -> int:
-        return self.seq.status()
+        st = C.c_uint32()
+        sp.check(sp.lib.sptmm_stack_status(self._h, C.byref(st)))
+        return st.value
+
+    def set_wait_limit(self, polls: int) -> None:
+        sp.check(sp.lib.sptmm_stack_wait_limit(self._h, polls))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            sp.lib.sptmm_stack_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def reference_forward(dense, layers, hidden, ffn, kv, x_i8, gemv_dense, quant):

@@ -146,6 +146,19 @@ _lib.oracle_fnv1a64.argtypes = [vp, u64]
 _lib.oracle_fnv1a64.restype = u64
 
 
+_lib.oracle_ternarise_absmean.argtypes = [vp, u32, u32, vp, vp]
+
+
+def ternarise_absmean(W: np.ndarray):
+    """fp32 weights of shape (N, K) -> (int8 ternary, scale): the oracle's absmean rule."""
+    W = np.ascontiguousarray(W, dtype=np.float32)
+    N, K = W.shape
+    out = np.empty((N, K), dtype=np.int8)
+    scale = np.zeros(1, dtype=np.float32)
+    _lib.oracle_ternarise_absmean(_p(W), K, N, _p(out), _p(scale))
+    return out, float(scale[0])
+
+
 def fnv1a64(a) -> str:
     a = np.ascontiguousarray(a)
     return "%016x" % _lib.oracle_fnv1a64(_p(a), a.nbytes)
