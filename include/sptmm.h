@@ -74,6 +74,8 @@ typedef struct sptmm_weights_info {
     uint64_t lossy_entries; /* DELTA_DIV256: entries whose 8-bit store lost information      */
     uint32_t n_arrays;      /* number of encoded arrays, see sptmm_weights_array             */
     int32_t  device;        /* device the arrays are uploaded to, -1 if none                 */
+    uint32_t k_tile;        /* rows per K-tile of a K-tiled matrix, else 0                   */
+    uint32_t n_tiles;       /* number of K-tiles, else 0                                     */
 } sptmm_weights_info;
 
 const char *sptmm_last_error(void);
@@ -104,6 +106,19 @@ int sptmm_ternarise_absmean(const void *W, uint32_t dtype, uint32_t K, uint32_t 
  *          the other formats ignore it. */
 int sptmm_encode(const int8_t *W, uint32_t K, uint32_t N, uint32_t format, uint32_t split,
                  uint32_t S, sptmm_weights **out);
+/* The same matrix cut along K ("chunked for split-K"): tile t holds rows t*k_tile .. of W as a
+ * native u16 matrix of its own, row numbers counted from the tile's first row (k_tile a multiple
+ * of 16).  The reference splits K only by striding lanes over one list (main.cu:581-584).
+ *  - sptmm_gemv on the handle multiplies tile after tile on the stream, the first storing C and
+ *    the others adding to it: the activation tile in shared memory is k_tile rows long instead of
+ *    K, so up to sixteen rows of X share one pass over the indices however long K is (int sums
+ *    exact as ever; float sums are added tile by tile).
+ *  - sptmm_weights_tile hands out one tile as a handle of its own (owned by the parent), e.g. for
+ *    the rank that owns that K range in sptmm_gemv_reduce: one encoding serves every rank, each
+ *    uploads only its tile.
+ * sptmm_weights_upload on the parent uploads every tile; save/load take single tiles. */
+int sptmm_encode_ktiled(const int8_t *W, uint32_t K, uint32_t N, uint32_t k_tile, sptmm_weights **out);
+int sptmm_weights_tile(const sptmm_weights *w, uint32_t tile, sptmm_weights **out);
 int sptmm_weights_info_get(const sptmm_weights *w, sptmm_weights_info *info);
 /* Encoded array `i` on the host (byte-for-byte what is uploaded).  For U16_DIV: 0 = +1 lists,
  * 1 = -1 lists; DELTA_DIV256 likewise.  Native formats: 0 = payload, then metadata arrays. */

@@ -41,7 +41,7 @@ class WeightsInfo(C.Structure):
     _fields_ = [("K", C.c_uint32), ("N", C.c_uint32), ("format", C.c_uint32), ("split", C.c_uint32),
                 ("S", C.c_uint32), ("max_count", C.c_uint32), ("nnz", C.c_uint64),
                 ("stream_bytes", C.c_uint64), ("lossy_entries", C.c_uint64), ("n_arrays", C.c_uint32),
-                ("device", C.c_int32)]
+                ("device", C.c_int32), ("k_tile", C.c_uint32), ("n_tiles", C.c_uint32)]
 
 
 def _load() -> C.CDLL:
@@ -57,6 +57,8 @@ def _load() -> C.CDLL:
         "sptmm_gen_ternary_iid": (i32, [u32, u32, C.c_double, u64, vp]),
         "sptmm_ternarise_absmean": (i32, [vp, u32, u32, u32, vp, C.POINTER(C.c_float)]),
         "sptmm_encode": (i32, [vp, u32, u32, u32, u32, u32, C.POINTER(vp)]),
+        "sptmm_encode_ktiled": (i32, [vp, u32, u32, u32, C.POINTER(vp)]),
+        "sptmm_weights_tile": (i32, [vp, u32, C.POINTER(vp)]),
         "sptmm_weights_info_get": (i32, [vp, C.POINTER(WeightsInfo)]),
         "sptmm_weights_array": (i32, [vp, u32, C.POINTER(vp), C.POINTER(vp), C.POINTER(u64), C.POINTER(C.c_char_p)]),
         "sptmm_weights_upload": (i32, [vp]),
@@ -121,7 +123,7 @@ def _load() -> C.CDLL:
 
 lib = _load()
 EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptmm_gen_ternary_iid", "sptmm_ternarise_absmean",
-           "sptmm_encode", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
+           "sptmm_encode", "sptmm_encode_ktiled", "sptmm_weights_tile", "sptmm_weights_info_get", "sptmm_weights_array", "sptmm_weights_upload",
            "sptmm_weights_upload_replicas", "sptmm_weights_free", "sptmm_weights_save", "sptmm_weights_load", "sptmm_gemv", "sptmm_gemv_status", "sptmm_quantize_absmax", "sptmm_gemv_scaled", "sptmm_gemv_reduce", "sptmm_gemv_host", "sptmm_gemv_host_async", "sptmm_gemv_host_wait", "sptmm_gemv_host_batch",
            "sptmm_row_split3_small", "sptmm_row_split_delta2", "sptmm_dense_cublas_gemm", "sptmm_dense_cublas_gemm_f16",
            "sptmm_seq_create", "sptmm_seq_create_shared", "sptmm_seq_shared_bytes", "sptmm_seq_shared_bytes_for", "sptmm_seq_run", "sptmm_seq_run_static", "sptmm_seq_status", "sptmm_seq_set_wait_limit", "sptmm_seq_free",
@@ -184,13 +186,19 @@ def ternarise_absmean(W: np.ndarray) -> tuple[np.ndarray, float]:
 class Weights:
     """An encoded ternary matrix (host-owned handle; optionally uploaded to the current device)."""
 
-    def __init__(self, W_colmajor: np.ndarray, fmt: int = FMT_U16_V256, split: int = 32, S: int = 0):
+    def __init__(self, W_colmajor: np.ndarray, fmt: int = FMT_U16_V256, split: int = 32, S: int = 0, k_tile: int = 0):
+        """k_tile > 0: the matrix is cut into K-tiles of that many rows (native u16 format only)."""
         W = np.ascontiguousarray(W_colmajor, dtype=np.int8)
         if W.ndim != 2:
             raise ValueError("W must be 2-D with shape (N, K): one row per column of the K x N matrix")
         N, K = W.shape
         h = C.c_void_p()
-        check(lib.sptmm_encode(W.ctypes.data, K, N, fmt, split, S, C.byref(h)))
+        if k_tile:
+            if fmt != FMT_U16_V256:
+                raise ValueError("K-tiles come in the native u16 format only")
+            check(lib.sptmm_encode_ktiled(W.ctypes.data, K, N, k_tile, C.byref(h)))
+        else:
+            check(lib.sptmm_encode(W.ctypes.data, K, N, fmt, split, S, C.byref(h)))
         self._h = h
         self.info = self._info()
 
@@ -212,6 +220,12 @@ class Weights:
         self._h = h
         self.info = self._info()
         return self
+
+    def tile(self, t: int) -> "Weights":
+        """K-tile `t` of a K-tiled matrix as a handle of its own (owned by this object)."""
+        h = C.c_void_p()
+        check(lib.sptmm_weights_tile(self._h, t, C.byref(h)))
+        return Weights.borrow(h)
 
     def save(self, path: str) -> None:
         check(lib.sptmm_weights_save(self._h, os.fsencode(path)))

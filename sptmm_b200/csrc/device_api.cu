@@ -110,6 +110,14 @@ extern "C" int sptmm_weights_upload_replicas(sptmm_weights *w, uint32_t copies)
 {
     if (!w) return fail(SPTMM_ERR_INVALID, "weights_upload: null handle");
     if (copies == 0 || copies > 4096) return fail(SPTMM_ERR_INVALID, "weights_upload: copies=%u", copies);
+    if (w->k_tile) {                        // a K-tiled matrix: every tile, to the same device
+        for (sptmm_weights *t : w->tiles) {
+            const int rc = sptmm_weights_upload_replicas(t, copies);
+            if (rc != SPTMM_OK) return rc;
+        }
+        w->device = w->tiles.empty() ? -1 : w->tiles[0]->device;
+        return SPTMM_OK;
+    }
     free_device_side(w);
     int dev = 0, sms = 0;
     SPTMM_CUDA_TRY(cudaGetDevice(&dev));
@@ -145,6 +153,8 @@ extern "C" int sptmm_weights_upload(sptmm_weights *w) { return sptmm_weights_upl
 extern "C" int sptmm_weights_free(sptmm_weights *w)
 {
     if (!w) return SPTMM_OK;
+    for (sptmm_weights *t : w->tiles) sptmm_weights_free(t);
+    w->tiles.clear();
     free_device_side(w);
     delete w;
     return SPTMM_OK;
@@ -156,6 +166,22 @@ static int gemv_dispatch(const sptmm_weights *w, const void *X, uint32_t dtype, 
     if (!w || !X || !C) return fail(SPTMM_ERR_INVALID, "gemv: null pointer");
     if (M == 0) return fail(SPTMM_ERR_INVALID, "gemv: M must be at least 1");
     if (dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv: unknown dtype %u", dtype);
+    if (w->k_tile) {
+        // tile after tile on the stream: the first stores, the others add; each reads its own K range of X
+        const size_t es = dtype_size(dtype);
+        for (size_t t = 0; t < w->tiles.size(); t++) {
+            const sptmm_weights *tw = w->tiles[t];
+            if (tw->device < 0 || tw->dev.empty()) return fail(SPTMM_ERR_STATE, "gemv: tile %zu of the K-tiled weights is not uploaded", t);
+            if (replica >= tw->dev.size()) return fail(SPTMM_ERR_INVALID, "gemv: replica %u of %zu", replica, tw->dev.size());
+            const size_t k0 = t * (size_t)w->k_tile;
+            const char *xt = static_cast<const char *>(X) + ((flags & SPTMM_X_COLMAJOR) ? k0 * M : k0) * es;
+            GemvArgs a{tw, tw->dev[replica].data(), xt, C, dtype, M, flags, stream};
+            a.status = status; a.ldx = w->K; a.accumulate = t > 0;
+            const int rc = launch_native_u16(a);
+            if (rc != SPTMM_OK) return rc;
+        }
+        return SPTMM_OK;
+    }
     if (w->device < 0 || w->dev.empty()) return fail(SPTMM_ERR_STATE, "gemv: weights are not uploaded");
     if (replica >= w->dev.size()) return fail(SPTMM_ERR_INVALID, "gemv: replica %u of %zu", replica, w->dev.size());
     int dev = -1;
@@ -189,8 +215,8 @@ extern "C" int sptmm_gemv_scaled(const sptmm_weights *w, const int8_t *X, uint32
 {
     if (!w || !X || !C) return fail(SPTMM_ERR_INVALID, "gemv_scaled: null pointer");
     if (M == 0) return fail(SPTMM_ERR_INVALID, "gemv_scaled: M must be at least 1");
-    if (w->format != SPTMM_FMT_U16_V256 && w->format != SPTMM_FMT_DELTA_LANE)
-        return fail(SPTMM_ERR_UNSUPPORTED, "gemv_scaled: weights must be in a native format");
+    if ((w->format != SPTMM_FMT_U16_V256 && w->format != SPTMM_FMT_DELTA_LANE) || w->k_tile)
+        return fail(SPTMM_ERR_UNSUPPORTED, "gemv_scaled: weights must be one matrix in a native format");
     if (w->device < 0 || w->dev.empty()) return fail(SPTMM_ERR_STATE, "gemv_scaled: weights are not uploaded");
     if (replica >= w->dev.size()) return fail(SPTMM_ERR_INVALID, "gemv_scaled: replica %u of %zu", replica, w->dev.size());
     int dev = -1;
@@ -210,7 +236,7 @@ extern "C" int sptmm_gemv_reduce(const sptmm_weights *w, const void *X, uint32_t
     for (uint32_t r = 0; r < n_peers; r++)
         if (!C_peers[r]) return fail(SPTMM_ERR_INVALID, "gemv_reduce: no output buffer for rank %u", r);
     if (M == 0 || dtype > SPTMM_F32) return fail(SPTMM_ERR_INVALID, "gemv_reduce: bad M or dtype");
-    if (w->format != SPTMM_FMT_U16_V256) return fail(SPTMM_ERR_UNSUPPORTED, "gemv_reduce: weights must be in the native u16 format");
+    if (w->format != SPTMM_FMT_U16_V256 || w->k_tile) return fail(SPTMM_ERR_UNSUPPORTED, "gemv_reduce: weights must be one native u16 matrix (for a K-tiled one, the rank's own tile)");
     if (flags & SPTMM_C_COLMAJOR) return fail(SPTMM_ERR_UNSUPPORTED, "gemv_reduce: the per-rank outputs are row-major");
     if (w->N < n_peers) return fail(SPTMM_ERR_INVALID, "gemv_reduce: N=%u columns for %u ranks", w->N, n_peers);
     if (w->device < 0 || w->dev.empty()) return fail(SPTMM_ERR_STATE, "gemv_reduce: weights are not uploaded");
@@ -237,6 +263,16 @@ static int read_gemv_status(const sptmm_weights *w, uint32_t *word)
 extern "C" int sptmm_gemv_status(const sptmm_weights *w, uint32_t *status)
 {
     if (!w || !status) return fail(SPTMM_ERR_INVALID, "gemv_status: null pointer");
+    if (w->k_tile) {                        // a K-tiled matrix: any tile's word
+        *status = 0;
+        for (const sptmm_weights *t : w->tiles) {
+            uint32_t word = 0;
+            const int rc = sptmm_gemv_status(t, &word);
+            if (rc != SPTMM_OK) return rc;
+            *status |= word;
+        }
+        return SPTMM_OK;
+    }
     if (w->device < 0) return fail(SPTMM_ERR_STATE, "gemv_status: weights are not uploaded");
     int dev = -1;
     SPTMM_CUDA_TRY(cudaGetDevice(&dev));

@@ -213,8 +213,10 @@ __device__ __forceinline__ void transpose_bytes4(const uint32_t (&w)[MT], uint32
 // BIASED (int8 only): store x+128 as an unsigned byte, the form LaneAcc's packed sums expect.
 template <int DT, int MT, bool BIASED = false>
 __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint32_t K, uint32_t M,
-                                        uint32_t m0, uint32_t mv, bool x_colmajor)
+                                        uint32_t m0, uint32_t mv, bool x_colmajor, uint32_t ldx = 0)
 {
+    // ldx: elements between rows of a row-major X (0 = K); a K-tile of a wider matrix passes the full width
+    const size_t LD = ldx ? ldx : K;
     static_assert(!BIASED || DT == SPTMM_I8, "only int8 tiles are biased");
     using elem = typename ActTraits<DT>::elem;
     [[maybe_unused]] const auto biased = [](elem v) -> elem {
@@ -225,12 +227,12 @@ __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint3
     elem *dst = reinterpret_cast<elem *>(xs);
     const elem *X = reinterpret_cast<const elem *>(Xv);
     const uint32_t tid = threadIdx.x, nt = blockDim.x;
-    if (MT == 1 && !x_colmajor && ((reinterpret_cast<uintptr_t>(X + (size_t)m0 * K) & 15) == 0)) {
+    if (MT == 1 && !x_colmajor && ((reinterpret_cast<uintptr_t>(X + (size_t)m0 * LD) & 15) == 0)) {
         const uint32_t vec = (K * ES) / 16;
-        const uint4 *src = reinterpret_cast<const uint4 *>(X + (size_t)m0 * K);
+        const uint4 *src = reinterpret_cast<const uint4 *>(X + (size_t)m0 * LD);
         for (uint32_t i = tid; i < vec; i += nt) reinterpret_cast<uint4 *>(xs)[i] = __ldg(src + i);
-        for (uint32_t k = vec * (16 / ES) + tid; k < K; k += nt) dst[k] = X[(size_t)m0 * K + k];
-    } else if (MT > 1 && !x_colmajor && (K % (4 / ES)) == 0 && (reinterpret_cast<uintptr_t>(X) & 3) == 0) {
+        for (uint32_t k = vec * (16 / ES) + tid; k < K; k += nt) dst[k] = X[(size_t)m0 * LD + k];
+    } else if (MT > 1 && !x_colmajor && (K % (4 / ES)) == 0 && (LD % (4 / ES)) == 0 && (reinterpret_cast<uintptr_t>(X) & 3) == 0) {
         // One thread takes one 32-bit word (KP = 4/ES consecutive k) from each of the MT rows --
         // coalesced along k -- transposes the MT x KP elements in registers and writes the KP
         // finished tile rows (MT*4 contiguous bytes) with vector stores.
@@ -240,7 +242,7 @@ __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint3
             uint32_t w[MT];
 #pragma unroll
             for (int m = 0; m < MT; m++)
-                w[m] = (uint32_t)m < mv ? __ldg(reinterpret_cast<const uint32_t *>(X + (size_t)(m0 + m) * K) + pc) : 0u;
+                w[m] = (uint32_t)m < mv ? __ldg(reinterpret_cast<const uint32_t *>(X + (size_t)(m0 + m) * LD) + pc) : 0u;
             uint32_t o[MT];                      // o[i*(MT/KP) + j]: word j of tile row k0+i
             if constexpr (ES == 4) {
 #pragma unroll
@@ -277,7 +279,7 @@ __device__ __forceinline__ void stage_x(unsigned char *xs, const void *Xv, uint3
         for (uint32_t m = 0; m < (uint32_t)MT; m++) {
             if (m < mv) {
                 for (uint32_t k = tid; k < K; k += nt)
-                    dst[(size_t)k * MT + m] = biased(x_colmajor ? X[(size_t)k * M + m0 + m] : X[(size_t)(m0 + m) * K + k]);
+                    dst[(size_t)k * MT + m] = biased(x_colmajor ? X[(size_t)k * M + m0 + m] : X[(size_t)(m0 + m) * LD + k]);
             } else {
                 for (uint32_t k = tid; k < K; k += nt) dst[(size_t)k * MT + m] = biased(elem(0));
             }

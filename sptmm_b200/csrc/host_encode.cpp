@@ -456,12 +456,51 @@ extern "C" int sptmm_encode(const int8_t *W, uint32_t K, uint32_t N, uint32_t fo
     return SPTMM_OK;
 }
 
+// A K-tiled matrix: the rows are cut into tiles of k_tile rows and every tile is encoded as a
+// native u16 matrix of its own (row numbers counted from the tile's first row).  The reference's
+// "split-K" is lane striding over one list (main.cu:581-584); a K range that can be multiplied on
+// its own is what a kernel needs to keep sixteen rows of a long activation in shared memory, and
+// what a GPU needs to own one K range of a matrix split across GPUs.
+extern "C" int sptmm_encode_ktiled(const int8_t *W, uint32_t K, uint32_t N, uint32_t k_tile, sptmm_weights **out)
+{
+    if (!W || !out) return fail(SPTMM_ERR_INVALID, "encode_ktiled: null pointer");
+    *out = nullptr;
+    if (K == 0 || N == 0 || K >= 65536) return fail(SPTMM_ERR_INVALID, "encode_ktiled: bad shape K=%u N=%u", K, N);
+    if (k_tile == 0 || (k_tile & 15)) return fail(SPTMM_ERR_INVALID, "encode_ktiled: k_tile=%u must be a positive multiple of 16", k_tile);
+    sptmm_weights *w = new (std::nothrow) sptmm_weights();
+    if (!w) return fail(SPTMM_ERR_NOMEM, "encode_ktiled: out of host memory");
+    w->K = K; w->N = N; w->format = SPTMM_FMT_U16_V256; w->split = 32; w->k_tile = k_tile;
+    std::vector<int8_t> slice;
+    for (uint32_t k0 = 0; k0 < K; k0 += k_tile) {
+        const uint32_t kt = std::min(k_tile, K - k0);
+        slice.resize((size_t)kt * N);
+        for (uint32_t c = 0; c < N; c++) memcpy(slice.data() + (size_t)c * kt, W + (size_t)c * K + k0, kt);
+        sptmm_weights *t = nullptr;
+        const int rc = sptmm_encode(slice.data(), kt, N, SPTMM_FMT_U16_V256, 32, 0, &t);
+        if (rc != SPTMM_OK) { sptmm_weights_free(w); return rc; }
+        w->tiles.push_back(t);
+        w->nnz += t->nnz; w->stream_bytes += t->stream_bytes;
+        w->max_count = std::max(w->max_count, t->max_count);
+    }
+    *out = w;
+    return SPTMM_OK;
+}
+
+extern "C" int sptmm_weights_tile(const sptmm_weights *w, uint32_t tile, sptmm_weights **out)
+{
+    if (!w || !out) return fail(SPTMM_ERR_INVALID, "weights_tile: null pointer");
+    if (tile >= w->tiles.size()) return fail(SPTMM_ERR_INVALID, "weights_tile: tile %u of %zu", tile, w->tiles.size());
+    *out = w->tiles[tile];
+    return SPTMM_OK;
+}
+
 extern "C" int sptmm_weights_info_get(const sptmm_weights *w, sptmm_weights_info *info)
 {
     if (!w || !info) return fail(SPTMM_ERR_INVALID, "weights_info: null pointer");
     info->K = w->K; info->N = w->N; info->format = w->format; info->split = w->split; info->S = w->S;
     info->max_count = w->max_count; info->nnz = w->nnz; info->stream_bytes = w->stream_bytes;
     info->lossy_entries = w->lossy; info->n_arrays = (uint32_t)w->arrays.size(); info->device = w->device;
+    info->k_tile = w->k_tile; info->n_tiles = (uint32_t)w->tiles.size();
     return SPTMM_OK;
 }
 

@@ -44,6 +44,10 @@ struct sptmm_weights {
     uint32_t entries_per_block = 0;
     uint32_t uniform_nbl = 0;         // blocks per list if every list has the same count, else 0
     std::vector<sptmm::HostArray> arrays;
+    // A K-tiled matrix (sptmm_encode_ktiled) carries no arrays itself: tile t is a native u16 matrix
+    // of rows [t*k_tile, min(K, (t+1)*k_tile)), with its own lists, owned by this handle.
+    uint32_t k_tile = 0;
+    std::vector<sptmm_weights *> tiles;
 
     int device = -1;
     uint32_t sm_count = 0;
@@ -91,6 +95,8 @@ struct GemvArgs {
     void *const *C_peers = nullptr;   // split-K: per-rank output buffers the partial sums are added to
     uint32_t n_peers = 0;
     uint32_t *status = nullptr;       // where a bounded wait that ran out is reported (null: the handle's device word)
+    uint32_t ldx = 0;                 // elements between rows of a row-major X (0 = K)
+    bool accumulate = false;          // add to C instead of storing
     bool scaled = false;              // int8 activations, float output: C = sum * row_scale[m] * out_scale
     const float *row_scale = nullptr; // device float[M], or null for 1
     float out_scale = 1.0f;

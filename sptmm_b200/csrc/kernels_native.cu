@@ -62,6 +62,8 @@ struct NativeParams {
     uint32_t scaled;
     const float *row_scale;      // per row of X, or null for 1
     float out_scale;
+    uint32_t ldx;                // elements between rows of a row-major X (a K-tile of a wider matrix: the full width)
+    uint32_t accumulate;         // 1: add to C instead of storing (the second and later K-tiles of a matrix)
     uint32_t half_blocks;        // blocks per half of a warp's staging area
     uint32_t stage_blocks;       // blocks of staging area per warp (one or two halves)
     uint32_t stage_off;          // byte offset of the staging area in dynamic shared memory
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
     const uint32_t m0 = blockIdx.y * MT;
     const uint32_t mv = min((uint32_t)MT, p.M - m0);
     constexpr uint32_t ES = ActTraits<DT>::size;
-    const unsigned char *xrow = reinterpret_cast<const unsigned char *>(p.X) + (size_t)m0 * p.K * ES;
+    const unsigned char *xrow = reinterpret_cast<const unsigned char *>(p.X) + (size_t)m0 * p.ldx * ES;
     const uint32_t xvec = (p.K * ES) / 16;
     const bool x_regs = MT == 1 && p.x_early && !p.x_colmajor && (p.K * ES) % 16 == 0 &&
                         (reinterpret_cast<uintptr_t>(xrow) & 15) == 0 && xvec <= 2 * blockDim.x;
@@ -234,7 +236,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             if (tid < ES) xs[(size_t)p.K * ES + tid] = 0;                     // the zero row
         }
     } else {
-        stage_x<DT, MT, LaneAcc<DT, MT>::kBiased>(xs, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0);
+        stage_x<DT, MT, LaneAcc<DT, MT>::kBiased>(xs, p.X, p.K, p.M, m0, mv, p.x_colmajor != 0, p.ldx);
     }
     if (x_first) request_weights();
     __syncthreads();
@@ -474,7 +476,8 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
                 continue;
             }
         }
-        C[o] = v;
+        if (p.accumulate) C[o] += v;        // K-tiles of one matrix run one after the other on the stream
+        else C[o] = v;
     }
     SPTMM_STAMP(4);
 }
@@ -632,6 +635,7 @@ static int launch_native(const GemvArgs &a, const bool delta)
     }
     prm.col_bound[8] = a.n_peers ? w.N : 0;
     if (a.n_peers) prm.col_bound[a.n_peers] = w.N;
+    prm.ldx = a.ldx ? a.ldx : w.K; prm.accumulate = a.accumulate ? 1u : 0u;
     prm.scaled = a.scaled ? 1u : 0u; prm.row_scale = a.row_scale; prm.out_scale = a.out_scale;
     prm.half_blocks = half;
     prm.stage_blocks = halves * half;

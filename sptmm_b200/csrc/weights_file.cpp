@@ -58,6 +58,7 @@ struct FileCloser { void operator()(FILE *f) const { if (f) fclose(f); } };
 extern "C" int sptmm_weights_save(const sptmm_weights *w, const char *path)
 {
     if (!w || !path) return fail(SPTMM_ERR_INVALID, "weights_save: null pointer");
+    if (w->k_tile) return fail(SPTMM_ERR_UNSUPPORTED, "weights_save: a K-tiled matrix is saved tile by tile (sptmm_weights_tile)");
     std::vector<uint8_t> head;
     head.insert(head.end(), kMagic, kMagic + 8);
     put<uint32_t>(head, kVersion);

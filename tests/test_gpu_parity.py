@@ -137,6 +137,49 @@ def test_native_u16_float(dtype, rtol, K, N, M):
     assert torch.equal(out, out2)
 
 
+# ---------------------------------------------------------------- K-tiled matrices
+
+@pytest.mark.parametrize("K,N,kt", [(400, 24, 128), (2560, 640, 1024), (6912, 320, 2304)])
+@pytest.mark.parametrize("M", [1, 4, 16, 37])
+def test_k_tiled_matrix_int8(K, N, kt, M):
+    """A matrix cut into K-tiles (sptmm_encode_ktiled): tile after tile, the first storing and the
+    others adding, gives the same int32 results as the whole matrix -- bit-exact against the dense
+    oracle, also when the last tile is shorter, for both layouts of X and with several replicas."""
+    W = sp.gen_ternary_iid(K, N, 0.5, 31)
+    w = sp.Weights(W, sp.FMT_U16_V256, k_tile=kt).upload(2)
+    X = O.gen_x_i8(M * K, 8)
+    want = O.gemv_i8_dense(X, W).reshape(M, N)
+    out = torch.full((M, N), -7, dtype=torch.int32, device="cuda")
+    w.gemv(dev(X), M, out, sp.I8, replica=1)
+    torch.cuda.synchronize()
+    assert (out.cpu().numpy() == want).all()
+    xc = np.ascontiguousarray(X.reshape(M, K).T)                  # X column-major: X(m,k) at k*M+m
+    out.fill_(-7)
+    w.gemv(dev(xc), M, out, sp.I8, sp.X_COLMAJOR | sp.LAUNCH_PDL)
+    torch.cuda.synchronize()
+    assert (out.cpu().numpy() == want).all()
+    assert w.status() == 0
+    got = w.gemv_host(X.reshape(M, K), sp.I8)                     # host buffers in and out
+    assert (got == want).all()
+
+
+@pytest.mark.parametrize("M", [4, 16, 64])
+def test_k_tiled_matrix_fp16_long_rows(M):
+    """K = 28672 fp16 rows do not fit shared memory sixteen at a time; K-tiles of 4096 do.  Within
+    the fp16 tolerance of the double-precision sum, like the untiled path."""
+    K, N = 28672, 96
+    W, Xh, ref, dbl, ab = _float_case(K, N, M, 0.5, sp.F16)
+    out = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    for kt in (4096, 8192):
+        w = sp.Weights(W, sp.FMT_U16_V256, k_tile=kt).upload()
+        out.zero_()
+        w.gemv(dev(Xh), M, out, sp.F16)
+        torch.cuda.synchronize()
+        err = np.abs(out.cpu().numpy().astype(np.float64) - dbl)
+        assert (err <= FP16_RTOL * ab + 1e-30).all(), "max err/scale = %g" % (err / np.maximum(ab, 1e-30)).max()
+        w.close()
+
+
 # ---------------------------------------------------------------- native lane-delta format
 
 @pytest.mark.parametrize("p0", [1 / 3, 0.5, 0.75, 0.97, 1.0])

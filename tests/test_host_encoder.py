@@ -214,3 +214,31 @@ def test_gemv_without_upload_fails_loudly():
     with pytest.raises(sp.SptmmError) as e:
         w.gemv(x, 1, out)
     assert e.value.code == -6 and "not uploaded" in e.value.message
+
+
+def test_k_tiled_encoding_partitions_the_rows(tmp_path):
+    """sptmm_encode_ktiled: every tile is a native matrix of its own K range; together they hold
+    every non-zero once; tiles come out as handles; the parent cannot be saved as one file."""
+    K, N, kt = 400, 24, 128                                       # the last tile is shorter (16 rows)
+    W = sp.gen_ternary_iid(K, N, 0.4, 5)
+    w = sp.Weights(W, sp.FMT_U16_V256, k_tile=kt)
+    assert (w.info.k_tile, w.info.n_tiles, w.info.K, w.info.N) == (kt, 4, K, N)
+    assert w.info.nnz == int((W != 0).sum())
+    total = 0
+    for t in range(4):
+        tile = w.tile(t)
+        k0, k1 = t * kt, min(K, (t + 1) * kt)
+        ref = sp.Weights(np.ascontiguousarray(W[:, k0:k1]), sp.FMT_U16_V256)
+        assert (tile.info.K, tile.info.N, tile.info.nnz) == (k1 - k0, N, ref.info.nnz)
+        for i in range(ref.info.n_arrays):
+            assert (tile.array(i)[1] == ref.array(i)[1]).all()
+        total += tile.info.stream_bytes
+    assert total == w.info.stream_bytes
+    with pytest.raises(sp.SptmmError):
+        w.tile(4)
+    with pytest.raises(sp.SptmmError):
+        w.save(str(tmp_path / "w.sptmm"))
+    w.tile(1).save(str(tmp_path / "t1.sptmm"))                    # single tiles are ordinary matrices
+    assert sp.Weights.load(str(tmp_path / "t1.sptmm")).info.K == kt
+    with pytest.raises(sp.SptmmError):
+        sp.Weights(W, sp.FMT_U16_V256, k_tile=100)                # not a multiple of 16

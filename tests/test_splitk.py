@@ -75,6 +75,32 @@ def test_fused_reduce_scatter_with_emulated_ranks(M, dtype, ranks):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M,ranks", [(1, 2), (7, 4)])
+def test_fused_reduce_scatter_from_one_k_tiled_encoding(M, ranks):
+    """The same with ONE encoding of the matrix cut into K-tiles: every emulated rank takes its tile
+    out of it (sptmm_weights_tile), uploads only that, and adds its partial sums to the owners."""
+    import torch
+    torch.cuda.set_device(0)
+    K, N = 1024, 200
+    kt = K // ranks
+    W = sp.gen_ternary_iid(K, N, 0.5, 41)
+    X = O.gen_x_i8(M * K, 43).reshape(M, K)
+    want = O.gemv_i8_dense(X.reshape(-1), W).reshape(M, N)
+    whole = sp.Weights(W, sp.FMT_U16_V256, k_tile=kt)
+    cols = [SK.col_range(N, r, ranks) for r in range(ranks)]
+    bufs = [torch.zeros(M, c1 - c0, dtype=torch.int32, device="cuda") for c0, c1 in cols]
+    for r in range(ranks):
+        tile = whole.tile(r)
+        tile.upload()
+        xs = torch.from_numpy(np.ascontiguousarray(X[:, r * kt:(r + 1) * kt])).cuda()
+        tile.gemv_reduce(xs, M, bufs, sp.I8)
+        torch.cuda.synchronize()
+    assert (np.concatenate([b.cpu().numpy() for b in bufs], axis=1) == want).all()
+    with pytest.raises(sp.SptmmError):
+        whole.gemv_reduce(xs, M, bufs, sp.I8)                  # the parent is not one matrix
+
+
+@pytest.mark.gpu
 def test_gemv_reduce_is_validated():
     import torch
     torch.cuda.set_device(0)
