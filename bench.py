@@ -710,6 +710,13 @@ def large_sweep(args, sp, O, torch, dist, rank, world):
             us = float(t.item())
         return us
 
+    def all_ranks(flag: bool) -> bool:
+        if world == 1:
+            return flag
+        t = torch.tensor([0.0 if flag else 1.0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) == 0.0
+
     for Kl, Nl in shapes:
         W = sp.gen_ternary_iid(Kl, Nl, 0.5, 7)
         rng = np.random.default_rng(8)
@@ -717,20 +724,36 @@ def large_sweep(args, sp, O, torch, dist, rank, world):
         res[key] = {}
         c0, c1 = SK.col_range(Nl, rank, world)
         wn = sp.Weights(np.ascontiguousarray(W[c0:c1]), sp.FMT_U16_V256).upload()
+        wk = sp.Weights(np.ascontiguousarray(W[c0:c1]), sp.FMT_U16_V256, k_tile=4096).upload()
         for m in (1, 8, 64):
             X = rng.standard_normal((m, Kl)).astype(np.float16)
             xd = torch.from_numpy(X).cuda()
+            # two fp16 results of the same product may differ by the tolerance each has against the
+            # exact sum: 1e-3 of the sum of |x| over the row, as in the parity tests
+            scale = np.abs(X.astype(np.float64)).sum(axis=1)[:, None]
             out = torch.zeros(m, c1 - c0, dtype=torch.float32, device="cuda")
             entry = {"n_sharded_us": timed(lambda: wn.gemv(xd, m, out, sp.F16, sp.LAUNCH_PDL, stream=st.cuda_stream)),
                      "encoded_MB_per_rank": wn.stream_bytes / 1e6}
+            base = out.cpu().numpy().astype(np.float64)
+            outk = torch.zeros_like(out)
+            entry["n_sharded_k_tiles_4096_us"] = timed(lambda: wk.gemv(xd, m, outk, sp.F16, sp.LAUNCH_PDL, stream=st.cuda_stream))
             mm = SK.SplitKMatmul(W, m, sp.F16, rank, world)
             xs = torch.from_numpy(np.ascontiguousarray(X[:, mm.k0:mm.k1])).cuda()
             entry["split_k_fused_us"] = timed(lambda: mm.forward(xs))
+            torch.cuda.synchronize()
+            same = (np.abs(outk.cpu().numpy() - base) <= 2e-3 * scale).all() and \
+                   (np.abs(mm.out.cpu().numpy() - base) <= 2e-3 * scale).all()
             if world > 1 and Nl % world == 0:
                 entry["split_k_nccl_us"] = timed(lambda: mm.forward_nccl(xs))
+                torch.cuda.synchronize()
+                same = same and (np.abs(mm.rs_out.cpu().numpy() - base) <= 2e-3 * scale).all()
+            if not all_ranks(bool(same)):
+                raise SystemExit("parity failure in the large sweep (%s, M=%d): K-tiled, split-K and column-sharded results disagree" % (key, m))
+            entry["parity"] = "column-sharded, K-tiled and split-K results agree within 2e-3 of sum|x| (fp16), on every rank"
             del mm
             res[key]["M%d" % m] = entry
         wn.close()
+        wk.close()
         if world == 1:
             wi = sp.Weights(W, sp.FMT_I2S).upload()
             for m in (1, 8):
@@ -747,6 +770,55 @@ def large_sweep(args, sp, O, torch, dist, rank, world):
             del wd
         del W
     return res
+
+
+def run_case(args):
+    """A short run of ONE configuration, for a profiler to capture: `--case` names it
+    (m1_i8, m4_i8, m4_f16, m16_i8: the per-call kernel on the 6912x2560 matrix over rotating weight
+    copies; stack_m1, stack_m4, stack_m16: a six-layer stack through the persistent kernel).
+    Prints the case and the time per call or pass; nothing here is a bench value."""
+    import torch
+    import sptmm_b200 as sp
+    import oracle_lib as O
+    torch.cuda.set_device(0)
+    name = args.case
+    st = torch.cuda.Stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if name.startswith("stack_m"):
+        from sptmm_b200 import stack as SM
+        m = int(name[len("stack_m"):])
+        stk = SM.TernaryStack(6, 2560, 6912, 640, M=m, p_zero=1 / 3, seed=0)
+        stk.set_input(O.gen_x_i8(m * 2560, 5).reshape(m, 2560))
+        with torch.cuda.stream(st):
+            for _ in range(3):
+                stk.forward(st.cuda_stream)
+            e0.record(st)
+            for _ in range(4):
+                stk.forward(st.cuda_stream)
+            e1.record(st)
+            st.synchronize()
+        assert stk.status() == 0
+        print(json.dumps({"case": name, "exchange": stk.exchange, "us_per_pass_of_6_layers": e0.elapsed_time(e1) * 1e3 / 4}))
+        return
+    m, dt = {"m1_i8": (1, sp.I8), "m4_i8": (4, sp.I8), "m4_f16": (4, sp.F16), "m16_i8": (16, sp.I8)}[name]
+    W = sp.gen_ternary_fixed(K, N, S)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload(16)
+    if dt == sp.I8:
+        x = torch.from_numpy(O.gen_x_i8(m * K, 1)).cuda()
+        out = torch.zeros(4, m * N, dtype=torch.int32, device="cuda")
+    else:
+        x = torch.from_numpy(np.random.default_rng(2).standard_normal((m, K)).astype(np.float16)).cuda()
+        out = torch.zeros(4, m * N, dtype=torch.float32, device="cuda")
+    n = 64
+    with torch.cuda.stream(st):
+        for i in range(16):
+            w.gemv(x, m, out[i % 4], dt, sp.LAUNCH_PDL, replica=i % 16, stream=st.cuda_stream)
+        e0.record(st)
+        for i in range(n):
+            w.gemv(x, m, out[i % 4], dt, sp.LAUNCH_PDL, replica=i % 16, stream=st.cuda_stream)
+        e1.record(st)
+        st.synchronize()
+    print(json.dumps({"case": name, "us_per_call_one_stream": e0.elapsed_time(e1) * 1e3 / n, "launches": n + 16}))
 
 
 def main():
@@ -770,8 +842,12 @@ def main():
     ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
     ap.add_argument("--large", nargs="?", const="one", default=None, choices=["one", "all"],
                     help="also run the large-matrix sweep (column-sharded and split-K over all ranks); 'all' = three shapes")
+    ap.add_argument("--case", default=None, choices=["m1_i8", "m4_i8", "m4_f16", "m16_i8", "stack_m1", "stack_m4", "stack_m16"],
+                    help="run one configuration briefly (for a profiler) instead of the benchmark")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
