@@ -821,6 +821,80 @@ def run_case(args):
     print(json.dumps({"case": name, "us_per_call_one_stream": e0.elapsed_time(e1) * 1e3 / n, "launches": n + 16}))
 
 
+def run_timeline(args):
+    """Where a step of the 30-layer stack spends its time, from timestamps every CTA records inside
+    the persistent kernel (the TUNING build of the library: python sptmm_b200/build.py --tuning).
+    For the four steps of layer 25 and every rank: minimum / median / maximum over the CTAs of the
+    moments they finished the previous gather, saw their input arrive, passed the local counters,
+    had the tile staged and finished the gather, in ns after the rank's LAST CTA finished the
+    previous gather.  Works under torchrun (one rank per GPU); not a bench value."""
+    os.environ["SPTMM_B200_TUNING"] = "1"
+    import torch
+    import torch.distributed as dist
+    import sptmm_b200 as sp
+    import oracle_lib as O
+    from sptmm_b200 import stack as SM
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    m = args.timeline
+    stk = SM.TernaryStack(30, 2560, 6912, 640, M=m, p_zero=1 / 3, seed=0, rank=rank, world=world,
+                          settled=True if args.stack_settled else None, tagged=True if args.stack_tagged else None)
+    stk.set_input(O.gen_x_i8(m * 2560, 5).reshape(m, 2560))
+    for _ in range(3):
+        if world > 1:
+            dist.barrier()
+        stk.forward()
+        torch.cuda.synchronize()
+    assert stk.status() == 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    e0.record()
+    for _ in range(10):
+        stk.forward()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 10
+    trace = torch.zeros(16384, dtype=torch.int64, device="cuda")
+    stk.seq.set_trace(trace)
+    if world > 1:
+        dist.barrier()
+    stk.forward()
+    torch.cuda.synchronize()
+    stk.seq.set_trace(None)
+    t = trace.cpu().numpy()
+    G = torch.cuda.get_device_properties(local).multi_processor_count
+
+    def arr(base):
+        return t[base:base + 1024].reshape(4, 256)[:, :G].astype(np.int64)
+
+    wait, staged, gathered = arr(2048), arr(3072), arr(4096)
+    marks = [arr(5120), arr(6144), arr(7168)]
+    lines = ["rank %d of %d, M=%d, exchange %d: %.1f us per pass (%.2f us per step)" % (rank, world, m, stk.exchange, us, us / 120),
+             "  step  prev-gather-end | past-wait | input arrived | counter 1 | counter 2 / row loaded | staged | gathered   (min/median/max over %d CTAs, ns)" % G]
+    for i, name in ((1, "o"), (2, "gu"), (3, "down")):
+        ref = gathered[i - 1].max()
+
+        def q(a):
+            if a.max() == 0:
+                return "-"
+            a = a - ref
+            return "%d/%d/%d" % (a.min(), np.median(a), a.max())
+
+        lines.append("  %-4s  %s | %s | %s | %s | %s | %s | %s" % (name, q(gathered[i - 1]), q(wait[i]), q(marks[0][i]), q(marks[1][i]),
+                                                                  q(marks[2][i]), q(staged[i]), q(gathered[i])))
+    for r in range(world):
+        if r == rank:
+            print("\n".join(lines), flush=True)
+        if world > 1:
+            dist.barrier()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -844,8 +918,12 @@ def main():
                     help="also run the large-matrix sweep (column-sharded and split-K over all ranks); 'all' = three shapes")
     ap.add_argument("--case", default=None, choices=["m1_i8", "m4_i8", "m4_f16", "m16_i8", "stack_m1", "stack_m4", "stack_m16"],
                     help="run one configuration briefly (for a profiler) instead of the benchmark")
+    ap.add_argument("--timeline", type=int, default=0, metavar="M",
+                    help="print the per-step timeline of the 30-layer stack at M rows (needs the tuning build of the library)")
     args = ap.parse_args()
-    if args.case:
+    if args.timeline:
+        run_timeline(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)
