@@ -550,7 +550,9 @@ def stack_leg(args, sp, O, torch, dist, st, rank, world):
         entry = {"us_per_pass": us, "tokens_per_s": m_rows / (us * 1e-6), "encoded_GB": total_bytes / 1e9,
                  "GBps_all_gpus": total_bytes / (us * 1e-6) / 1e9, "status_ok": ok, "layers": args.stack_layers,
                  "steps_per_pass": stk.n_steps,
-                 "exchange": "settled (one watcher per word, local counters)" if stk.settled else ("tagged words" if stk.tagged else "step counters")}
+                 "exchange": {1: "step counters", 2: "tagged words polled by every reader", 3: "step counters + row maxima",
+                              4: "producer-side quantiser", 5: "settled (one watcher per word, local counters)",
+                              6: "settled, two half-batches with alternating steps"}.get(stk.exchange, str(stk.exchange))}
         info["M%d" % m_rows] = entry
         # the same weights as launch-per-matmul: per-call kernels + (NCCL all-gather) + quantiser kernel, one CUDA graph per pass
         ns = SM.NcclStack(wts, M=m_rows)

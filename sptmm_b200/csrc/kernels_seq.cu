@@ -691,6 +691,7 @@ __device__ __forceinline__ void stage_x_packed(unsigned char *xs, const uint32_t
                     o[q] ^= 0x80808080u;
                 }
                 if constexpr (MT == 4) *reinterpret_cast<uint32_t *>(xs + (size_t)k * 4) = o[0];
+                else if constexpr (MT == 8) *reinterpret_cast<uint2 *>(xs + (size_t)k * 8) = make_uint2(o[0], o[1]);
                 else *reinterpret_cast<uint4 *>(xs + (size_t)k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
@@ -814,6 +815,7 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
                 o[q] ^= 0x80808080u;
             }
             if constexpr (MT == 4) *reinterpret_cast<uint32_t *>(tile_g + (size_t)k * 4) = o[0];
+            else if constexpr (MT == 8) *reinterpret_cast<uint2 *>(tile_g + (size_t)k * 8) = make_uint2(o[0], o[1]);
             else *reinterpret_cast<uint4 *>(tile_g + (size_t)k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
         }
         settle_barrier(c2, p.target_local, failed, p.status, p.poll_limit);
@@ -1327,7 +1329,10 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
     sptmm_seq *q = new (std::nothrow) sptmm_seq();
     if (!q) return fail(SPTMM_ERR_NOMEM, "seq_create: out of host memory");
     q->device = dev; q->nsteps = n; q->M = M; q->G = (uint32_t)sms;
-    q->mt = M == 1 ? 1 : (M <= 4 ? 4 : 16);
+    // rows per activation tile: 1, 4 or 16; sequences of the settled exchange also have an 8-row kernel
+    bool any_settled = false;
+    for (uint32_t s = 0; s < n; s++) any_settled = any_settled || steps[s].x_kind == 5;
+    q->mt = M == 1 ? 1 : (M <= 4 ? 4 : ((M <= 8 && any_settled) ? 8 : 16));
     std::vector<SeqDesc> desc(n);
     std::vector<uint32_t> blk, col, tb, tc;
     uint32_t kmax = 0;
@@ -1610,6 +1615,7 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     switch (q->mt) {
         case 1: return seq_launch<1>(q, prm, st);
         case 4: return seq_launch<4>(q, prm, st);
+        case 8: return seq_launch_as<8, 2>(q, prm, st);          // settled sequences only (see seq_create_impl)
         case 16: return seq_launch<16>(q, prm, st);
     }
     return fail(SPTMM_ERR_INVALID, "internal: row tile %u", q->mt);

@@ -55,13 +55,13 @@ struct sptmm_stack_weights {
 
 struct sptmm_stack {
     sptmm_stack_weights *weights = nullptr;  // not owned
-    uint32_t M = 0, exchange = 0, n_steps = 0;
+    uint32_t M = 0, exchange = 0, n_steps = 0, chains = 1, rows = 0;
     bool tagged = false;                     // the intermediate buffers hold tagged words
     sptmm_seq *seq = nullptr;
     void *own_arena = nullptr;               // allocated here (one rank, no arena given)
     char *mine = nullptr;                    // this rank's arena
     uint64_t off_counters = 0, off_x = 0, off_scales = 0;
-    uint64_t off_buf[5] = {};                // qkv, o, gu, down, out
+    uint64_t off_buf[2][5] = {};             // per half-batch: qkv, o, gu, down, out
     uint32_t width[5] = {};
     ~sptmm_stack()
     {
@@ -147,43 +147,55 @@ extern "C" int sptmm_stack_weights_free(sptmm_stack_weights *w)
 
 // Which exchange a stack uses when the caller leaves it open (exchange 0): measured on B200, the
 // settled exchange wins across GPUs at every M and on one GPU from eight rows upward; below that the
-// step counters with the reader-side quantiser do.
+// step counters with the reader-side quantiser do.  Across GPUs, from four rows upward the rows are
+// run as two half-batches whose steps alternate: while one half's outputs travel and settle, the
+// kernel gathers the other half.
 static uint32_t pick_exchange(uint32_t exchange, uint32_t M, uint32_t world)
 {
     if (exchange) return exchange;
+    if (world > 1 && M >= 4 && M % 2 == 0) return SPTMM_STACK_SETTLED_HALVES;
     return (world > 1 || M >= 8) ? SPTMM_STACK_SETTLED : SPTMM_STACK_COUNTERS;
 }
 
 struct StackPlan {                 // everything that depends on the configuration, M and the exchange only
+    uint32_t chains = 1, rows = 0;              // independent half-batches and the rows of each
     std::vector<sptmm_seq_step> steps;          // X / C hold OFFSETS into a rank's arena until create() adds the base
     std::vector<uint64_t> c_off;                // per step: offset of this rank's first output column
-    uint64_t off_counters = 0, off_x = 0, off_scales = 0, off_buf[5] = {}, bytes = 0;
+    uint64_t off_counters = 0, off_x = 0, off_scales = 0, off_buf[2][5] = {}, bytes = 0;
     uint32_t width[5] = {};
 };
 
 static int make_plan(const sptmm_stack_weights *sw, uint32_t M, uint32_t exchange, StackPlan &pl)
 {
     const sptmm_stack_config &c = sw->cfg;
-    const uint32_t n_steps = 4 * c.layers, hidden = c.hidden, ffn = c.ffn;
+    const uint32_t layer_steps = 4 * c.layers, hidden = c.hidden, ffn = c.ffn;
     const auto shapes = layer_shapes(hidden, ffn, c.kv);
     uint32_t xk, xw;               // readers of part of a row / of a whole row
+    pl.chains = 1;
     switch (exchange) {
         case SPTMM_STACK_COUNTERS: xk = xw = 1; break;
         case SPTMM_STACK_TAGGED: xk = xw = 2; break;
         case SPTMM_STACK_ROW_MAXIMA: xk = 1; xw = 3; break;
         case SPTMM_STACK_PRODUCER_QUANT: xk = xw = 4; break;
         case SPTMM_STACK_SETTLED: xk = xw = 5; break;
+        case SPTMM_STACK_SETTLED_HALVES:
+            xk = xw = 5; pl.chains = 2;
+            if (M < 2 || (M & 1)) return fail(SPTMM_ERR_INVALID, "stack: two half-batches need an even number of rows (M=%u)", M);
+            break;
         default: return fail(SPTMM_ERR_INVALID, "stack: unknown exchange %u", exchange);
     }
+    const uint32_t chains = pl.chains, rows = M / chains, n_steps = layer_steps * chains;
+    pl.rows = rows;
     pl.width[0] = shapes[0].N; pl.width[1] = hidden; pl.width[2] = ffn; pl.width[3] = hidden; pl.width[4] = hidden;
     pl.steps.assign(n_steps, sptmm_seq_step{});
     pl.c_off.assign(n_steps, 0);
-    // sizes first: the synchronisation area depends on the step kinds and shapes only
-    for (uint32_t s = 0; s < n_steps; s++) {
-        sptmm_seq_step &st = pl.steps[s];
-        const uint32_t i = s % 4;
+    // Step t = chains * s + h is layer step s of half-batch h; it reads what step t - chains wrote.
+    // Sizes first: the synchronisation area depends on the step kinds and shapes only.
+    for (uint32_t t = 0; t < n_steps; t++) {
+        sptmm_seq_step &st = pl.steps[t];
+        const uint32_t s = t / chains, i = s % 4;
         st.w = sw->w[s];
-        st.dep = (int32_t)s - 1;
+        st.dep = s == 0 ? -1 : (int32_t)(t - chains);
         st.x_kind = s == 0 ? 0 : (i == 1 ? xk : xw);
         st.c_kind = i == 2 ? 1 : 0;
         st.X = reinterpret_cast<const void *>((uintptr_t)16);       // placeholders: the layout does not look at addresses
@@ -191,36 +203,37 @@ static int make_plan(const sptmm_stack_weights *sw, uint32_t M, uint32_t exchang
     }
     uint64_t cur = 0;
     pl.off_counters = cur;
-    cur += sptmm_seq_shared_bytes_for(pl.steps.data(), n_steps, M);
-    for (int b = 0; b < 5; b++) {
-        cur = align256(cur);
-        pl.off_buf[b] = cur;
-        cur += (uint64_t)M * pl.width[b] * 4;
-    }
+    cur += sptmm_seq_shared_bytes_for(pl.steps.data(), n_steps, rows);
+    for (uint32_t h = 0; h < chains; h++)
+        for (int b = 0; b < 5; b++) {
+            cur = align256(cur);
+            pl.off_buf[h][b] = cur;
+            cur += (uint64_t)rows * pl.width[b] * 4;
+        }
     cur = align256(cur);
-    pl.off_x = cur; cur += (uint64_t)M * hidden;
+    pl.off_x = cur; cur += align256((uint64_t)rows * hidden) * chains;
     cur = align256(cur);
-    pl.off_scales = cur; cur += (uint64_t)n_steps * M * 4;
+    pl.off_scales = cur; cur += (uint64_t)n_steps * rows * 4;
     pl.bytes = align256(cur);
     // the steps, with offsets where addresses will go
     static const int src_of[4] = {3, 0, 1, 2};       // qkv reads down, o reads qkv, gu reads o, down reads gu
-    for (uint32_t s = 0; s < n_steps; s++) {
-        sptmm_seq_step &st = pl.steps[s];
-        const uint32_t i = s % 4;
-        const int dst = s == n_steps - 1 ? 4 : (int)i;      // the last step's result: never tagged, no reader inside the kernel
+    for (uint32_t t = 0; t < n_steps; t++) {
+        sptmm_seq_step &st = pl.steps[t];
+        const uint32_t s = t / chains, h = t % chains, i = s % 4;
+        const int dst = s == layer_steps - 1 ? 4 : (int)i;  // the last step's result: never tagged, no reader inside the kernel
         uint32_t c0, c1;
         shard_range(shapes[i].N, c.rank, c.world, c0, c1);
         const uint32_t o0 = i == 2 ? c0 / 2 : c0;           // where this rank's first output column lands
-        pl.c_off[s] = pl.off_buf[dst] + (uint64_t)o0 * 4;
+        pl.c_off[t] = pl.off_buf[h][dst] + (uint64_t)o0 * 4;
         st.ldc = pl.width[dst];
         if (s == 0) {
-            st.X = reinterpret_cast<const void *>((uintptr_t)pl.off_x);
+            st.X = reinterpret_cast<const void *>((uintptr_t)(pl.off_x + h * align256((uint64_t)rows * hidden)));
             st.ldx = hidden;
         } else {
-            st.X = reinterpret_cast<const void *>((uintptr_t)pl.off_buf[src_of[i]]);
+            st.X = reinterpret_cast<const void *>((uintptr_t)pl.off_buf[h][src_of[i]]);
             st.ldx = pl.width[src_of[i]];
         }
-        st.scale_out = reinterpret_cast<float *>((uintptr_t)(pl.off_scales + (uint64_t)s * M * 4));
+        st.scale_out = reinterpret_cast<float *>((uintptr_t)(pl.off_scales + (uint64_t)t * rows * 4));
     }
     return SPTMM_OK;
 }
@@ -243,12 +256,13 @@ extern "C" int sptmm_stack_create(sptmm_stack_weights *w, uint32_t M, uint32_t e
     if (c.world > 1 && !arena_peers) return fail(SPTMM_ERR_INVALID, "stack_create: %u ranks need every rank's arena", c.world);
     std::unique_ptr<sptmm_stack> st(new (std::nothrow) sptmm_stack());
     if (!st) return fail(SPTMM_ERR_NOMEM, "stack_create: out of host memory");
-    st->weights = w; st->M = M; st->n_steps = 4 * c.layers;
+    st->weights = w; st->M = M;
     st->exchange = pick_exchange(exchange, M, c.world);
-    st->tagged = st->exchange == SPTMM_STACK_TAGGED || st->exchange == SPTMM_STACK_SETTLED;
+    st->tagged = st->exchange == SPTMM_STACK_TAGGED || st->exchange == SPTMM_STACK_SETTLED || st->exchange == SPTMM_STACK_SETTLED_HALVES;
     StackPlan pl;
     int rc = make_plan(w, M, st->exchange, pl);
     if (rc != SPTMM_OK) return rc;
+    st->n_steps = (uint32_t)pl.steps.size(); st->chains = pl.chains; st->rows = pl.rows;
     std::vector<char *> bases(c.world, nullptr);
     if (arena_peers) {
         for (uint32_t r = 0; r < c.world; r++) {
@@ -265,7 +279,9 @@ extern "C" int sptmm_stack_create(sptmm_stack_weights *w, uint32_t M, uint32_t e
     }
     st->mine = bases[c.rank];
     st->off_counters = pl.off_counters; st->off_x = pl.off_x; st->off_scales = pl.off_scales;
-    for (int b = 0; b < 5; b++) { st->off_buf[b] = pl.off_buf[b]; st->width[b] = pl.width[b]; }
+    for (int h = 0; h < 2; h++)
+        for (int b = 0; b < 5; b++) st->off_buf[h][b] = pl.off_buf[h][b];
+    for (int b = 0; b < 5; b++) st->width[b] = pl.width[b];
     std::vector<void *> c_peers((size_t)st->n_steps * c.world), counter_peers(c.world);
     for (uint32_t s = 0; s < st->n_steps; s++) {
         sptmm_seq_step &sd = pl.steps[s];
@@ -276,9 +292,9 @@ extern "C" int sptmm_stack_create(sptmm_stack_weights *w, uint32_t M, uint32_t e
     }
     for (uint32_t r = 0; r < c.world; r++) counter_peers[r] = bases[r] + pl.off_counters;
     if (c.world > 1)
-        rc = sptmm_seq_create_shared(pl.steps.data(), st->n_steps, M, c_peers.data(), counter_peers.data(), c.world, c.rank, &st->seq);
+        rc = sptmm_seq_create_shared(pl.steps.data(), st->n_steps, pl.rows, c_peers.data(), counter_peers.data(), c.world, c.rank, &st->seq);
     else            // one rank: the sequence keeps its counters itself (device scope, no peer stores)
-        rc = sptmm_seq_create(pl.steps.data(), st->n_steps, M, &st->seq);
+        rc = sptmm_seq_create(pl.steps.data(), st->n_steps, pl.rows, &st->seq);
     if (rc != SPTMM_OK) return rc;
     *out = st.release();
     return SPTMM_OK;
@@ -287,7 +303,12 @@ extern "C" int sptmm_stack_create(sptmm_stack_weights *w, uint32_t M, uint32_t e
 extern "C" int sptmm_stack_set_input(sptmm_stack *st, const int8_t *x_host)
 {
     if (!st || !x_host) return fail(SPTMM_ERR_INVALID, "stack_set_input: null pointer");
-    return sptmm_memcpy_h2d(st->mine + st->off_x, x_host, (uint64_t)st->M * st->weights->cfg.hidden);
+    const uint64_t half = (uint64_t)st->rows * st->weights->cfg.hidden;      // rows 0..rows-1 go to the first half-batch, the rest to the second
+    for (uint32_t h = 0; h < st->chains; h++) {
+        const int rc = sptmm_memcpy_h2d(st->mine + st->off_x + h * align256(half), x_host + h * half, half);
+        if (rc != SPTMM_OK) return rc;
+    }
+    return SPTMM_OK;
 }
 
 extern "C" int sptmm_stack_forward(sptmm_stack *st, void *stream)
@@ -332,9 +353,10 @@ extern "C" int sptmm_stack_buffer(sptmm_stack *st, const char *name, int32_t *ho
     const int src = b == 3 ? 4 : b;                   // "down" = the stack's final result
     if (width) *width = st->width[src];
     if (!host_out) return SPTMM_OK;
-    const size_t n = (size_t)st->M * st->width[src];
+    const size_t n = (size_t)st->M * st->width[src], per_half = (size_t)st->rows * st->width[src];
     int rc = sptmm_device_sync();
-    if (rc == SPTMM_OK) rc = sptmm_memcpy_d2h(host_out, st->mine + st->off_buf[src], n * 4);
+    for (uint32_t h = 0; h < st->chains && rc == SPTMM_OK; h++)
+        rc = sptmm_memcpy_d2h(host_out + h * per_half, st->mine + st->off_buf[h][src], per_half * 4);
     if (rc != SPTMM_OK) return rc;
     if (st->tagged && src != 4)
         for (size_t i = 0; i < n; i++) host_out[i] = (int32_t)((uint32_t)host_out[i] << 8) >> 8;     // drop the tag byte, sign-extend 24 bits

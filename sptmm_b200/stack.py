@@ -54,7 +54,7 @@ class StackConfig(C.Structure):
                 ("p_zero", C.c_double), ("seed", C.c_uint64), ("rank", C.c_uint32), ("world", C.c_uint32)]
 
 
-AUTO, COUNTERS, TAGGED, ROW_MAXIMA, PRODUCER_QUANT, SETTLED = 0, 1, 2, 3, 4, 5      # sptmm.h: SPTMM_STACK_*
+AUTO, COUNTERS, TAGGED, ROW_MAXIMA, PRODUCER_QUANT, SETTLED, SETTLED_HALVES = 0, 1, 2, 3, 4, 5, 6      # sptmm.h: SPTMM_STACK_*
 
 
 class StackWeights:
@@ -127,7 +127,7 @@ class TernaryStack:
         self.weights, self.stream_bytes, self.params, self.dense = weights.weights, weights.stream_bytes, weights.params, weights.dense
         nbytes = int(sp.lib.sptmm_stack_arena_bytes(weights._h, M, exchange))
         if nbytes == 0:
-            raise ValueError("sptmm_stack_arena_bytes: bad M or exchange")
+            raise sp.SptmmError(-1, "sptmm_stack_arena_bytes: " + sp.lib.sptmm_last_error().decode("utf-8", "replace"))
         h = C.c_void_p()
         if world > 1:
             import torch.distributed as dist
@@ -146,8 +146,8 @@ class TernaryStack:
         ex = C.c_uint32()
         sp.check(sp.lib.sptmm_stack_exchange(h, C.byref(ex)))
         self.exchange = ex.value
-        self.tagged, self.settled, self.producer_quant = ex.value in (TAGGED, SETTLED), ex.value == SETTLED, ex.value == PRODUCER_QUANT
-        self.n_steps = 4 * layers
+        self.tagged, self.settled, self.producer_quant = ex.value in (TAGGED, SETTLED, SETTLED_HALVES), ex.value in (SETTLED, SETTLED_HALVES), ex.value == PRODUCER_QUANT
+        self.n_steps = 4 * layers * (2 if ex.value == SETTLED_HALVES else 1)
         sh = C.c_void_p()
         sp.check(sp.lib.sptmm_stack_sequence(h, C.byref(sh)))
         self.seq = sp.Sequence.borrow(sh)

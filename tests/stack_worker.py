@@ -50,9 +50,11 @@ def gpu_parity():
     layers, hidden, ffn, kv = 3, 256, 512, 64
     for M, tagged, row_maxima, pq in ((1, False, False, False), (4, False, True, False), (1, True, False, False), (4, True, False, False),
                                       (1, False, False, True), (4, False, False, True), (16, False, False, True),
-                                      (1, None, False, None), (3, None, False, None), (4, None, False, None), (16, None, False, None)):
-        st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, rank=rank, world=world, keep_dense=True,
-                            tagged=tagged, row_maxima=row_maxima, producer_quant=pq)
+                                      (1, None, False, None), (3, None, False, None), (4, None, False, None), (16, None, False, None),
+                                      (4, "settled", False, None), (16, "settled", False, None), (6, None, False, None)):
+        # None everywhere = the library's own choice (two half-batches from four even rows upward)
+        kw = dict(exchange=S.SETTLED) if tagged == "settled" else dict(tagged=tagged, row_maxima=row_maxima, producer_quant=pq)
+        st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, rank=rank, world=world, keep_dense=True, **kw)
         x = O.gen_x_i8(M * hidden, 9).reshape(M, hidden)
         st.set_input(x)
         want = S.reference_forward(st.dense, layers, hidden, ffn, kv, x, O.gemv_i8_dense, O.quant_absmax_i8)

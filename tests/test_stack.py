@@ -73,6 +73,28 @@ def test_small_stack_single_gpu(M, tagged, row_maxima, producer_quant):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M", [2, 4, 10, 16])
+def test_small_stack_two_half_batches(M):
+    """SETTLED_HALVES: the rows run as two half-batches whose steps alternate in the one kernel
+    (two, eight-row and sixteen-row tiles); same numbers as the oracle chain, row for row."""
+    import torch
+    torch.cuda.set_device(0)
+    layers, hidden, ffn, kv = 3, 256, 512, 64
+    st = S.TernaryStack(layers, hidden, ffn, kv, M=M, p_zero=1 / 3, seed=3, keep_dense=True, exchange=S.SETTLED_HALVES)
+    assert st.n_steps == 2 * 4 * layers
+    x = O.gen_x_i8(M * hidden, 9).reshape(M, hidden)
+    st.set_input(x)
+    want = _oracle_chain(st.dense, layers, hidden, ffn, kv, x)
+    for _ in range(3):
+        st.forward()
+        assert st.status() == 0
+        for name in ("qkv", "o", "gu", "down"):
+            assert (st.buffer(name) == want[name]).all(), name
+    with pytest.raises(sp.SptmmError):
+        S.TernaryStack(layers, hidden, ffn, kv, M=3, weights=st.shared_weights, exchange=S.SETTLED_HALVES)
+
+
+@pytest.mark.gpu
 def test_stack_multi_gpu_fused_exchange():
     import torch
     n = torch.cuda.device_count()
