@@ -820,7 +820,17 @@ def run_case(args):
             w.gemv(x, m, out[i % 4], dt, sp.LAUNCH_PDL, replica=i % 16, stream=st.cuda_stream)
         e1.record(st)
         st.synchronize()
-    print(json.dumps({"case": name, "us_per_call_one_stream": e0.elapsed_time(e1) * 1e3 / n, "launches": n + 16}))
+    info = {"case": name, "us_per_call_launch_bound_from_python": e0.elapsed_time(e1) * 1e3 / n, "launches": n + 16}
+    # parity of what was just computed: int8 exact; floats against the double-precision product, as a
+    # fraction of the sum of |x| over each column's non-zero rows (the tolerance is 1e-3 of that for fp16)
+    Wd = W.T.astype(np.float64)
+    xh = x.cpu().numpy().reshape(m, K).astype(np.float64)
+    got = out[(n - 1) % 4].cpu().numpy().reshape(m, N).astype(np.float64)
+    if dt == sp.I8:
+        info["mismatches"] = int((got != xh @ Wd).sum())
+    else:
+        info["max_err_over_sum_abs_x"] = float((np.abs(got - xh @ Wd) / np.maximum(np.abs(xh) @ np.abs(Wd), 1e-30)).max())
+    print(json.dumps(info))
 
 
 def run_timeline(args):

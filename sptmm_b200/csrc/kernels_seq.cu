@@ -526,9 +526,14 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
 
 // x_kind 3: the rows' largest magnitudes are already known (recorded by the producing step), so
 // one pass over X quantises it: q = clamp(rint(v * (127 / amax)), -127, 127) as in stage_x_quant.
-template <int MT>
+// UNTAG: the source words carry a tag byte to strip (the settled exchange's reader of a few rows).
+template <int MT, bool UNTAG = false>
 __device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc &d, uint32_t M, const uint32_t *amax, bool write_scale)
 {
+    [[maybe_unused]] const auto clean = [](int4 v) {
+        if constexpr (UNTAG) return make_int4((v.x << 8) >> 8, (v.y << 8) >> 8, (v.z << 8) >> 8, (v.w << 8) >> 8);
+        else return v;
+    };
     const uint32_t tid = threadIdx.x, nt = 512;                       // consumer threads only
     float scale[MT];
 #pragma unroll
@@ -542,7 +547,7 @@ __device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc 
         const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
         if (vec) {
             for (uint32_t q = tid; q < d.K / 4; q += nt) {
-                const int4 v = __ldcg(reinterpret_cast<const int4 *>(A) + q);
+                const int4 v = clean(__ldcg(reinterpret_cast<const int4 *>(A) + q));
                 const uint32_t w = (uint32_t)(quant1(v.x, scale[0]) & 0xff) | ((uint32_t)(quant1(v.y, scale[0]) & 0xff) << 8) |
                                    ((uint32_t)(quant1(v.z, scale[0]) & 0xff) << 16) | ((uint32_t)(quant1(v.w, scale[0]) & 0xff) << 24);
                 reinterpret_cast<uint32_t *>(xs)[q] = w;
@@ -565,7 +570,7 @@ __device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc 
                         int4 v[4];
 #pragma unroll
                         for (int r = 0; r < 4; r++)
-                            v[r] = (uint32_t)(4 * g + r) < M ? __ldcg(A + (size_t)(4 * g + r) * lda + q) : make_int4(0, 0, 0, 0);
+                            v[r] = (uint32_t)(4 * g + r) < M ? clean(__ldcg(A + (size_t)(4 * g + r) * lda + q)) : make_int4(0, 0, 0, 0);
                         uint32_t o[4];
 #define SPTMM_PACK4(f) ((uint32_t)(quant1(v[0].f, scale[4 * g]) & 0xff) | ((uint32_t)(quant1(v[1].f, scale[4 * g + 1]) & 0xff) << 8) | \
                         ((uint32_t)(quant1(v[2].f, scale[4 * g + 2]) & 0xff) << 16) | ((uint32_t)(quant1(v[3].f, scale[4 * g + 3]) & 0xff) << 24))
@@ -797,6 +802,14 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
         if (tid < p.M && rowmax_s[tid]) atomicMax(amax_g + tid, (uint32_t)rowmax_s[tid]);
         settle_barrier(c1, p.target_local, failed, p.status, p.poll_limit);
         SEQ_MARK(p, s, 1, failed);
+        if constexpr (MT == 4) {
+            // Up to four rows: every word has arrived and the maxima are known, so each CTA reads the rows
+            // itself (at most 4 x K ints out of L2) and rounds them in one pass -- cheaper than a second
+            // counter and a tile copy, which is what wider tiles take below.
+            stage_x_scaled<MT, true>(xs, d, p.M, amax_g, write_scale);
+            SEQ_MARK(p, s, 2, failed);
+            return;
+        }
         float *scale_s = reinterpret_cast<float *>(red);
         if (tid < (uint32_t)MT) {
             const uint32_t a = tid < p.M ? __ldcg(amax_g + tid) : 0u;

@@ -147,13 +147,14 @@ extern "C" int sptmm_stack_weights_free(sptmm_stack_weights *w)
 
 // Which exchange a stack uses when the caller leaves it open (exchange 0): measured on B200, the
 // settled exchange wins across GPUs at every M and on one GPU from eight rows upward; below that the
-// step counters with the reader-side quantiser do.  Across GPUs, from four rows upward the rows are
-// run as two half-batches whose steps alternate: while one half's outputs travel and settle, the
-// kernel gathers the other half.
+// step counters with the reader-side quantiser do.  (Running the rows as two half-batches whose
+// steps alternate, SPTMM_STACK_SETTLED_HALVES, was measured slower at 2 GPUs -- M=4 2 505 against
+// 1 463 us per pass, M=16 3 143 against 2 597: a CTA sits inside the second half's counters and tile
+// copy just as it does inside the first's, so only the words' flight overlaps the other half's
+// gather, and every step's weights are streamed twice.  It stays available by name.)
 static uint32_t pick_exchange(uint32_t exchange, uint32_t M, uint32_t world)
 {
     if (exchange) return exchange;
-    if (world > 1 && M >= 4 && M % 2 == 0) return SPTMM_STACK_SETTLED_HALVES;
     return (world > 1 || M >= 8) ? SPTMM_STACK_SETTLED : SPTMM_STACK_COUNTERS;
 }
 

@@ -495,6 +495,29 @@ def test_row_split_delta2_lossy_matches_reference_semantics():
     assert (run_i8(w, X, 1).reshape(1, N) == want).all()
 
 
+def test_row_split3_small_clamps_indices_beyond_k():
+    """A caller-built reference layout may hold anything: an index past K reads the zero row instead
+    of addressing shared memory beyond the activation tile."""
+    K, N, S, split = 256, 32, 128, 32
+    W = sp.gen_ternary_fixed(K, N, S)
+    pos, neg, _, _ = O.build_lists(W, S // 2, K)
+    wp, wn = O.encode_div(pos, split).copy(), O.encode_div(neg, split).copy()
+    rng = np.random.default_rng(5)
+    bad = rng.choice(wp.size, 40, replace=False)
+    X = O.gen_x_i8(K, 1)
+    good = O.gemv_i8_div(X, wp, wn, 1, K, N, S, split).reshape(-1).astype(np.int64)
+    # what the clamped entries contributed before they were overwritten
+    flat = wp.reshape(-1)
+    cols = (bad % (split * N)) // split
+    lost = np.zeros(N, dtype=np.int64)
+    np.add.at(lost, cols, X[flat[bad]].astype(np.int64))
+    flat[bad] = 65535
+    out = torch.zeros(N, dtype=torch.int32, device="cuda")
+    sp.row_split3_small(dev(X), dev(wp), dev(wn), out, 1, K, N, S, split)
+    torch.cuda.synchronize()
+    assert (out.cpu().numpy() == good - lost).all()
+
+
 def test_launch_errors():
     K, N, S = 512, 48, 256
     W = O.gen_fixed(K, N, S)

@@ -242,3 +242,19 @@ def test_k_tiled_encoding_partitions_the_rows(tmp_path):
     assert sp.Weights.load(str(tmp_path / "t1.sptmm")).info.K == kt
     with pytest.raises(sp.SptmmError):
         sp.Weights(W, sp.FMT_U16_V256, k_tile=100)                # not a multiple of 16
+
+
+def test_status_and_wait_entry_points_validate_their_arguments():
+    """Host plumbing of the per-call status word (no GPU, no kernel): null pointers and weights that
+    were never uploaded are refused with the right codes."""
+    import ctypes as C
+    w = sp.Weights(sp.gen_ternary_iid(64, 16, 0.5, 1), sp.FMT_U16_V256)
+    word = C.c_uint32(7)
+    assert sp.lib.sptmm_gemv_status(None, C.byref(word)) == -1
+    assert sp.lib.sptmm_gemv_status(w._h, None) == -1
+    assert sp.lib.sptmm_gemv_status(w._h, C.byref(word)) == -6          # not uploaded
+    assert b"not uploaded" in sp.lib.sptmm_last_error()
+    assert sp.lib.sptmm_gemv_host_wait(w._h, 99) == -1                   # no such slot
+    assert sp.lib.sptmm_gemv_host_wait(w._h, 0) == 0                     # an idle slot has nothing to wait for
+    assert sp.lib.sptmm_seq_set_wait_limit(None, 1) == -1
+    assert sp.lib.sptmm_seq_shared_bytes_for(None, 3, 1) == 0

@@ -73,3 +73,27 @@ def test_static_scratch_call_rejects_what_does_not_fit():
         sp.run_sequence_static([{"w": w, "X": x, "C": c}], M=17)
     assert sp.run_sequence_static([{"w": w, "X": x, "C": c}]) == 0      # still usable afterwards
     assert np.array_equal(c.cpu().numpy(), O.gemv_i8_dense(O.gen_x_i8(256, 1), W).reshape(-1))
+
+
+def test_static_scratch_call_refuses_a_capturing_stream():
+    """The call copies its step tables from host memory that dies with the call, so it must not be
+    recorded into a CUDA graph: on a stream under capture it returns an error and records nothing;
+    the capture itself stays valid and the entry point keeps working afterwards."""
+    torch.cuda.set_device(0)
+    W = sp.gen_ternary_iid(256, 64, 0.5, 0)
+    w = sp.Weights(W, sp.FMT_U16_V256).upload()
+    x = torch.from_numpy(O.gen_x_i8(256, 1)).cuda()
+    c = torch.zeros(64, dtype=torch.int32, device="cuda")
+    assert sp.run_sequence_static([{"w": w, "X": x, "C": c}]) == 0      # the first call on the device: outside any capture
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+        with pytest.raises(sp.SptmmError) as e:
+            sp.run_sequence_static([{"w": w, "X": x, "C": c}], stream=torch.cuda.current_stream().cuda_stream, wait=False)
+        assert e.value.code == -6 and "captured" in e.value.message
+        c.add_(0)                                                        # something harmless so the graph is not empty
+    graph.replay()
+    torch.cuda.synchronize()
+    c.zero_()
+    assert sp.run_sequence_static([{"w": w, "X": x, "C": c}]) == 0
+    assert np.array_equal(c.cpu().numpy(), O.gemv_i8_dense(O.gen_x_i8(256, 1), W).reshape(-1))
