@@ -534,6 +534,7 @@ __device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc 
         if constexpr (UNTAG) return make_int4((v.x << 8) >> 8, (v.y << 8) >> 8, (v.z << 8) >> 8, (v.w << 8) >> 8);
         else return v;
     };
+    [[maybe_unused]] const auto clean1 = [](int v) { return UNTAG ? (v << 8) >> 8 : v; };
     const uint32_t tid = threadIdx.x, nt = 512;                       // consumer threads only
     float scale[MT];
 #pragma unroll
@@ -553,7 +554,7 @@ __device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc 
                 reinterpret_cast<uint32_t *>(xs)[q] = w;
             }
         } else {
-            for (uint32_t k = tid; k < d.K; k += nt) xs[k] = (unsigned char)quant1(__ldcg(A + k), scale[0]);
+            for (uint32_t k = tid; k < d.K; k += nt) xs[k] = (unsigned char)quant1(clean1(__ldcg(A + k)), scale[0]);
         }
         if (tid == 0) xs[d.K] = 0;
     } else {
@@ -593,7 +594,7 @@ __device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc 
             const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
             for (uint32_t m = 0; m < (uint32_t)MT; m++)
                 for (uint32_t k = tid; k < d.K; k += nt)
-                    dst[(size_t)k * MT + m] = tile_byte<MT>(m < M ? quant1(__ldcg(A + (size_t)m * d.ldx + k), scale[m]) : 0);
+                    dst[(size_t)k * MT + m] = tile_byte<MT>(m < M ? quant1(clean1(__ldcg(A + (size_t)m * d.ldx + k)), scale[m]) : 0);
         }
         if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);
     }
