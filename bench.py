@@ -727,6 +727,8 @@ def large_sweep(args, sp, O, torch, dist, rank, world):
         c0, c1 = SK.col_range(Nl, rank, world)
         wn = sp.Weights(np.ascontiguousarray(W[c0:c1]), sp.FMT_U16_V256).upload()
         wk = sp.Weights(np.ascontiguousarray(W[c0:c1]), sp.FMT_U16_V256, k_tile=4096).upload()
+        k0, k1 = SK.k_range(Kl, rank, world)
+        ws = sp.Weights(np.ascontiguousarray(W[:, k0:k1]), sp.FMT_U16_V256).upload()      # this rank's K range, encoded once
         for m in (1, 8, 64):
             X = rng.standard_normal((m, Kl)).astype(np.float16)
             xd = torch.from_numpy(X).cuda()
@@ -739,7 +741,7 @@ def large_sweep(args, sp, O, torch, dist, rank, world):
             base = out.cpu().numpy().astype(np.float64)
             outk = torch.zeros_like(out)
             entry["n_sharded_k_tiles_4096_us"] = timed(lambda: wk.gemv(xd, m, outk, sp.F16, sp.LAUNCH_PDL, stream=st.cuda_stream))
-            mm = SK.SplitKMatmul(W, m, sp.F16, rank, world)
+            mm = SK.SplitKMatmul(W, m, sp.F16, rank, world, weights=ws)
             xs = torch.from_numpy(np.ascontiguousarray(X[:, mm.k0:mm.k1])).cuda()
             entry["split_k_fused_us"] = timed(lambda: mm.forward(xs))
             torch.cuda.synchronize()
@@ -756,6 +758,7 @@ def large_sweep(args, sp, O, torch, dist, rank, world):
             res[key]["M%d" % m] = entry
         wn.close()
         wk.close()
+        ws.close()
         if world == 1:
             wi = sp.Weights(W, sp.FMT_I2S).upload()
             for m in (1, 8):

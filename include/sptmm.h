@@ -300,7 +300,10 @@ typedef struct sptmm_seq_step {
                                 values per row, C[m][j] = result[2j] + result[2j+1] (a fused
                                 "gate | up" matrix with its columns interleaved hands the next
                                 step one source instead of two); N even, ldc counts output
-                                elements                                                          */
+                                elements.  2: the de-quantising epilogue -- C holds FLOATS,
+                                C[m][n] = float(result) * s[m] with s[m] the absmax/127 this step's
+                                input stage quantised row m with (1 for int8 inputs, x_kind 0); for
+                                the last step of a chain, whose output no later step reads      */
 } sptmm_seq_step;
 
 int sptmm_seq_create(const sptmm_seq_step *steps, uint32_t n_steps, uint32_t M, sptmm_seq **out);

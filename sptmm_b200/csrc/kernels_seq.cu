@@ -199,6 +199,10 @@ __device__ __forceinline__ bool seq_bounded_wait(uint32_t bar, uint32_t parity)
 template <int MT> constexpr uint32_t kTileBias = MT > 1 ? 0x80808080u : 0u;
 template <int MT> __device__ __forceinline__ int8_t tile_byte(int q) { return (int8_t)(MT > 1 ? (q ^ 0x80) : q); }
 
+// absmax/127 of the rows the current step's input stage quantised (1 for int8 inputs): every input
+// stage leaves it here for the de-quantising epilogue (c_kind 2)
+__shared__ float seq_xscale_s[16];
+
 constexpr int kRedInts = 32 + 16 * 16 + 16;      // scratch ints behind the column sums (see stage_x_quant_rows)
 
 __device__ __forceinline__ int absmax4(int4 v) { return max(max(abs(v.x), abs(v.y)), max(abs(v.z), abs(v.w))); }
@@ -300,6 +304,7 @@ __device__ __forceinline__ void stage_x_quant_rows(unsigned char *xs, const SeqD
     for (int m = 0; m < MT; m++) {
         const int a = amax_s[m];
         scale[m] = a ? 127.0f / (float)a : 0.0f;
+        if (tid == (uint32_t)m) seq_xscale_s[m] = (float)a / 127.0f;
         if (write_scale && d.scale_out && tid == (uint32_t)m && (uint32_t)m < M) d.scale_out[m] = (float)a / 127.0f;
     }
 
@@ -392,6 +397,7 @@ __device__ __forceinline__ void quant_row_vec(unsigned char *xs, const int32_t *
         }
     }
     if (tid == 0) xs[K] = 0;
+    if (tid == 0) seq_xscale_s[0] = (float)amax / 127.0f;
     if (scale_out && tid == 0) scale_out[0] = (float)amax / 127.0f;
 }
 
@@ -489,6 +495,7 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
                     dst[(size_t)k * MT + m] = tile_byte<MT>(q);
                 }
             }
+            if (tid == 0) seq_xscale_s[m] = (float)amax / 127.0f;
             if (write_scale && d.scale_out && tid == 0) d.scale_out[m] = (float)amax / 127.0f;
         }
         if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);      // the zero row
@@ -519,6 +526,7 @@ __device__ __forceinline__ void stage_x_quant(unsigned char *xs, const SeqDesc &
             q = max(-127, min(127, q));
             dst[(size_t)k * MT + m] = tile_byte<MT>(q);
         }
+        if (tid == 0) seq_xscale_s[m] = (float)amax / 127.0f;
         if (write_scale && d.scale_out && tid == 0) d.scale_out[m] = (float)amax / 127.0f;
     }
     if (tid < (uint32_t)MT) dst[(size_t)d.K * MT + tid] = tile_byte<MT>(0);          // the zero row
@@ -541,6 +549,7 @@ __device__ __forceinline__ void stage_x_scaled(unsigned char *xs, const SeqDesc 
     for (int m = 0; m < MT; m++) {
         const uint32_t a = (uint32_t)m < M ? __ldcg(amax + m) : 0u;
         scale[m] = a ? 127.0f / (float)a : 0.0f;
+        if (tid == (uint32_t)m) seq_xscale_s[m] = (float)a / 127.0f;
         if (write_scale && d.scale_out && tid == (uint32_t)m && (uint32_t)m < M) d.scale_out[m] = (float)a / 127.0f;
     }
     const bool vec = (d.K & 3) == 0 && (d.ldx & 3) == 0 && (reinterpret_cast<uintptr_t>(d.X) & 15) == 0;
@@ -815,6 +824,7 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
         if (tid < (uint32_t)MT) {
             const uint32_t a = tid < p.M ? __ldcg(amax_g + tid) : 0u;
             scale_s[tid] = a ? 127.0f / (float)a : 0.0f;
+            seq_xscale_s[tid] = (float)a / 127.0f;
             if (write_scale && d.scale_out && tid < p.M) d.scale_out[tid] = (float)a / 127.0f;
         }
         consumer_sync();
@@ -885,6 +895,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     __shared__ uint32_t failed;              // a bounded wait ran out somewhere in this CTA
     __shared__ __align__(16) uint32_t desc_s[2][(sizeof(SeqDesc) + 15) / 16 * 4];   // this and the next step's descriptor
     __shared__ uint32_t meta_s[2][4];        // their plan entries: b0, b1, c0, c1
+    __shared__ float xscale_keep[2][16];     // the input rows' scales of this and the previous step (c_kind 2)
     __shared__ __align__(8) unsigned long long xbar;        // completion of the activation tile's bulk copy (x_kind 5)
     const uint32_t xbar_a = (uint32_t)__cvta_generic_to_shared(&xbar);
     uint32_t xphase = 0;
@@ -1006,7 +1017,10 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         // (TAGGED kernels are the ones that also know row maxima: plain sequences carry neither)
         if (TAGS && p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
             p.amax[((p.run_parity ^ 1u) * p.nsteps + s) * 16 + tid] = 0u;
-        if (d.x_kind == 0) stage_x_i8<MT>(xs, d, p.M);
+        if (d.x_kind == 0) {
+            stage_x_i8<MT>(xs, d, p.M);
+            if (tid < 16) seq_xscale_s[tid] = 1.0f;          // int8 activations come as they are
+        }
         else if constexpr (SETTLED) {               // x_kind 5 (the host admits no other kind here)
             bool fresh = failed == 0;
             const uint32_t tag = seq_tag(p.run_mod, d.in_tag_m, d.in_tag_j);
@@ -1031,6 +1045,9 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
 #endif
         for (uint32_t i = tid; i < ncols * MT; i += kConsumerThreads) c_s[i] = 0;
         consumer_sync();
+        // the rows' scales, kept per step parity: the next step's input stage overwrites seq_xscale_s
+        // while slow threads may still be storing this step's results
+        if (tid < 16) xscale_keep[s & 1][tid] = seq_xscale_s[tid];
         if (held_slot >= 0) {                  // X is in: now the previous step's last slot may refill
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_a + held_slot * 8) : "memory");
             held_slot = -1;
@@ -1129,8 +1146,9 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
 
         // what goes out: every column's sum, or (c_kind 1) the sums of neighbouring column pairs;
         // the plan gives a pair-summing step even column boundaries
-        const uint32_t nout = d.c_kind ? ncols / 2 : ncols, o0 = d.c_kind ? c0 / 2 : c0;
-        auto value = [&](uint32_t j, uint32_t m) { return d.c_kind ? c_s[(2 * j) * MT + m] + c_s[(2 * j + 1) * MT + m] : c_s[j * MT + m]; };
+        const bool pairs = d.c_kind == 1;
+        const uint32_t nout = pairs ? ncols / 2 : ncols, o0 = pairs ? c0 / 2 : c0;
+        auto value = [&](uint32_t j, uint32_t m) { return pairs ? c_s[(2 * j) * MT + m] + c_s[(2 * j + 1) * MT + m] : c_s[j * MT + m]; };
 
         // ---- producer-side quantiser (see SeqDesc::q_n): two hand-overs, all consumer warps
         if (TAGGED && d.q_n) {
@@ -1216,7 +1234,9 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
             for (uint32_t i = first; i < nout * p.M; i += step) {
                 const uint32_t m = i / nout, j = i - m * nout;
                 const int val = value(j, m);
-                const int wv = tag_out ? (int)(otag | ((uint32_t)val & 0xffffffu)) : val;
+                // c_kind 2: the de-quantised result, float(sum) * (absmax / 127 of the input row), stored as a float
+                const int wv = d.c_kind == 2 ? __float_as_int((float)val * xscale_keep[s & 1][m])
+                                             : (tag_out ? (int)(otag | ((uint32_t)val & 0xffffffu)) : val);
                 if (p.n_peers == 0) d.C[(size_t)m * d.ldc + o0 + j] = wv;
                 else                  // the exchange: straight into every rank's buffer over NVLink (plain peer stores)
                     for (uint32_t r = 0; r < p.n_peers; r++) d.Cp[r][(size_t)m * d.ldc + o0 + j] = wv;
@@ -1364,7 +1384,10 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
             rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u (x_kind 5) needs K a multiple of 4 (at most 14336 for one row), X 16-byte aligned and ldx a multiple of 4", s);
         else if (st.x_kind == 4 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 4) needs a producer (dep) and takes no X2", s);
         else if (st.x_kind == 3 && (st.dep < 0 || st.X2)) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u (x_kind 3) needs a producer (dep) and takes no X2", s);
-        else if (st.c_kind > 1 || (st.c_kind == 1 && (w->N & 1))) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u c_kind %u (pair sums need an even N)", s, st.c_kind);
+        else if (st.c_kind > 2 || (st.c_kind == 1 && (w->N & 1))) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u c_kind %u (pair sums need an even N)", s, st.c_kind);
+        else if (st.x_kind != 0 && st.dep >= 0 && (uint32_t)st.dep < s && steps[(uint32_t)st.dep].c_kind == 2)
+            rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u quantises the output of step %d, which holds de-quantised floats", s, st.dep);
+        else if (st.c_kind == 2 && st.x_kind == 4) rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u: a de-quantised output needs the step to know its input's scale (not x_kind 4)", s);
         else if (st.x_kind == 2 && st.dep < 0) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u reads tagged words but names no producer (dep)", s);
         else if (st.dep >= (int32_t)s) rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u depends on step %d, which does not precede it", s, st.dep);
         if (rc != SPTMM_OK) { seq_release(q); return rc; }
@@ -1376,7 +1399,7 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         d.ldx = st.ldx ? st.ldx : w->K; d.ldx2 = st.ldx2 ? st.ldx2 : w->K; d.ldc = st.ldc ? st.ldc : w->N;
         d.uniform_nbl = w->uniform_nbl; d.x_kind = st.x_kind; d.dep = st.dep < 0 ? -1 : st.dep;
         d.c_kind = st.c_kind;
-        d.ldc = st.ldc ? st.ldc : (st.c_kind ? w->N / 2 : w->N);
+        d.ldc = st.ldc ? st.ldc : (st.c_kind == 1 ? w->N / 2 : w->N);
         for (uint32_t r = 0; r < kMaxPeers; r++) d.Cp[r] = r < n_peers ? (int32_t *)C_peers[(size_t)s * n_peers + r] : nullptr;
         if (n_peers) {
             for (uint32_t r = 0; r < n_peers; r++)
@@ -1384,7 +1407,7 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
             d.C = d.Cp[my_rank];
         }
         uint32_t mc = 1, mb = 0;
-        plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q->G, tb, tc, mc, mb, st.c_kind ? 2u : 1u);
+        plan_columns((const uint32_t *)w->arrays[1].data.data(), w->N, q->G, tb, tc, mc, mb, st.c_kind == 1 ? 2u : 1u);
         blk.insert(blk.end(), tb.begin(), tb.end());
         col.insert(col.end(), tc.begin(), tc.end());
         q->max_cols = std::max(q->max_cols, mc);
@@ -1402,7 +1425,9 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
         for (uint32_t s = 0; s < n && rc == SPTMM_OK; s++) {
             desc[s].release = tagged[s] ? 0 : 1;
             if (steps[s].x_kind == 3) { desc[(uint32_t)steps[s].dep].want_amax = 1; q->uses_amax = true; }
-            if (tagged[s] && desc[s].c_kind && desc[s].K > 33000)
+            if (tagged[s] && desc[s].c_kind == 2)
+                rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u stores de-quantised floats, but a later step reads its output as tagged integers", s);
+            if (tagged[s] && desc[s].c_kind == 1 && desc[s].K > 33000)
                 rc = fail(SPTMM_ERR_UNSUPPORTED, "seq_create: step %u: pair sums over K=%u rows do not fit a tagged word", s, desc[s].K);
             if (steps[s].x_kind != 2 && steps[s].x_kind != 5 && steps[s].x_kind != 4 && steps[s].dep >= 0 && tagged[(uint32_t)steps[s].dep])
                 rc = fail(SPTMM_ERR_INVALID, "seq_create: step %u waits for step %d, whose output is tagged for an x_kind 2 or 5 reader", s, steps[s].dep);

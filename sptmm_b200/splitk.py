@@ -29,14 +29,15 @@ def col_range(N: int, rank: int, world: int) -> tuple[int, int]:
 
 
 class SplitKMatmul:
-    def __init__(self, W: np.ndarray, M: int, dtype: int = sp.I8, rank: int = 0, world: int = 1, group=None):
+    def __init__(self, W: np.ndarray, M: int, dtype: int = sp.I8, rank: int = 0, world: int = 1, group=None, weights=None):
         """W: the full (N, K) int8 ternary matrix, identical on every rank; only this rank's K range
-        is encoded and uploaded."""
+        is encoded and uploaded -- or `weights`, an uploaded encoding of that range made earlier (for
+        example this rank's tile of a K-tiled encoding), is used as it is."""
         import torch
         self.torch, self.M, self.dtype, self.rank, self.world = torch, M, dtype, rank, world
         self.N, self.K = W.shape
         self.k0, self.k1 = k_range(self.K, rank, world)
-        self.w = sp.Weights(np.ascontiguousarray(W[:, self.k0:self.k1]), sp.FMT_U16_V256).upload()
+        self.w = weights if weights is not None else sp.Weights(np.ascontiguousarray(W[:, self.k0:self.k1]), sp.FMT_U16_V256).upload()
         self.out_dtype = torch.int32 if dtype == sp.I8 else torch.float32
         widths = [col_range(self.N, r, world)[1] - col_range(self.N, r, world)[0] for r in range(world)]
         self.width = widths[rank]

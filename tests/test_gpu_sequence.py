@@ -288,6 +288,41 @@ def test_settled_exchange(M):
                      {"w": w4, "X": c1, "ldx": N1, "C": c4, "x_kind": 1, "dep": 1}], M=M)
 
 
+@pytest.mark.parametrize("x_kind", [1, 2, 3, 5])
+@pytest.mark.parametrize("M", [1, 4, 11])
+def test_dequantising_epilogue_of_the_last_step(M, x_kind):
+    """c_kind 2: the last step of a chain stores float(sum) * (absmax/127 of its quantised input row),
+    bit-exact against the same fp32 product in numpy, whichever way its input arrived; an int8 input
+    (x_kind 0) has scale 1.  A step may not read such an output."""
+    K1, N1, N2 = 512, 384, 200
+    W1 = sp.gen_ternary_iid(K1, N1, 0.4, 1)
+    W2 = sp.gen_ternary_iid(N1, N2, 0.5, 2)
+    w1, w2 = (sp.Weights(W, sp.FMT_U16_V256).upload() for W in (W1, W2))
+    X = O.gen_x_i8(M * K1, 4)
+    c1 = torch.zeros((M, N1), dtype=torch.int32, device="cuda")
+    c1f = torch.zeros((M, N1), dtype=torch.float32, device="cuda")
+    c2 = torch.zeros((M, N2), dtype=torch.float32, device="cuda")
+    s2 = torch.zeros(M, dtype=torch.float32, device="cuda")
+    seq = sp.Sequence([{"w": w1, "X": dev(X), "C": c1},
+                       {"w": w2, "X": c1, "C": c2, "x_kind": x_kind, "dep": 0, "scale_out": s2, "c_kind": 2}], M=M)
+    r1 = O.gemv_i8_dense(X, W1)
+    q1, sc1 = O.quant_absmax_i8(r1)
+    r2 = O.gemv_i8_dense(q1.reshape(-1), W2).reshape(M, N2)
+    want = r2.astype(np.float32) * sc1.astype(np.float32)[:, None]
+    for _ in range(3):
+        seq.run()
+        assert seq.status() == 0
+        assert (c2.cpu().numpy() == want).all()
+        assert (s2.cpu().numpy() == sc1).all()
+    first = sp.Sequence([{"w": w1, "X": dev(X), "C": c1f, "c_kind": 2}], M=M)      # int8 input: the sums as floats
+    first.run()
+    assert first.status() == 0
+    assert (c1f.cpu().numpy() == r1.astype(np.float32)).all()
+    with pytest.raises(sp.SptmmError):
+        sp.Sequence([{"w": w1, "X": dev(X), "C": c1f, "c_kind": 2},
+                     {"w": w2, "X": c1f, "C": c2, "x_kind": 1, "dep": 0}], M=M)
+
+
 def test_tagged_exchange_is_validated():
     W = sp.gen_ternary_iid(256, 256, 0.5, 0)
     w = sp.Weights(W, sp.FMT_U16_V256).upload()
