@@ -538,7 +538,8 @@ def stack_leg(args, sp, O, torch, dist, st, rank, world):
     for m_rows in (1, 4, 16):
         x = O.gen_x_i8(m_rows * 2560, 5).reshape(m_rows, 2560)
         stk = SM.TernaryStack(*shape, M=m_rows, rank=rank, world=world, weights=wts, settled=True if args.stack_settled else None,
-                              tagged=True if args.stack_tagged else None)
+                              tagged=True if args.stack_tagged else None,
+                              exchange=SM.SETTLED_HALVES if (args.stack_halves and m_rows % 2 == 0) else None)
         stk.set_input(x)
         us = timed(lambda: stk.forward(st.cuda_stream))
         ok = all_ranks(stk.status() == 0)
@@ -856,7 +857,8 @@ def run_timeline(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     m = args.timeline
     stk = SM.TernaryStack(30, 2560, 6912, 640, M=m, p_zero=1 / 3, seed=0, rank=rank, world=world,
-                          settled=True if args.stack_settled else None, tagged=True if args.stack_tagged else None)
+                          settled=True if args.stack_settled else None, tagged=True if args.stack_tagged else None,
+                          exchange=SM.SETTLED_HALVES if args.stack_halves else None)
     stk.set_input(O.gen_x_i8(m * 2560, 5).reshape(m, 2560))
     for _ in range(3):
         if world > 1:
@@ -890,7 +892,8 @@ def run_timeline(args):
     marks = [arr(5120), arr(6144), arr(7168)]
     lines = ["rank %d of %d, M=%d, exchange %d: %.1f us per pass (%.2f us per step)" % (rank, world, m, stk.exchange, us, us / 120),
              "  step  prev-gather-end | past-wait | input arrived | counter 1 | counter 2 / row loaded | staged | gathered   (min/median/max over %d CTAs, ns)" % G]
-    for i, name in ((1, "o"), (2, "gu"), (3, "down")):
+    names = ((1, "gu B"), (2, "down A"), (3, "down B")) if stk.exchange == SM.SETTLED_HALVES else ((1, "o"), (2, "gu"), (3, "down"))
+    for i, name in names:
         ref = gathered[i - 1].max()
 
         def q(a):
@@ -899,7 +902,7 @@ def run_timeline(args):
             a = a - ref
             return "%d/%d/%d" % (a.min(), np.median(a), a.max())
 
-        lines.append("  %-4s  %s | %s | %s | %s | %s | %s | %s" % (name, q(gathered[i - 1]), q(wait[i]), q(marks[0][i]), q(marks[1][i]),
+        lines.append("  %-6s  %s | %s | %s | %s | %s | %s | %s" % (name, q(gathered[i - 1]), q(wait[i]), q(marks[0][i]), q(marks[1][i]),
                                                                   q(marks[2][i]), q(staged[i]), q(gathered[i])))
     for r in range(world):
         if r == rank:
@@ -927,6 +930,7 @@ def main():
     ap.add_argument("--no-reference-gpu", action="store_true", help="skip running the reference's own GPU program (README commands)")
     ap.add_argument("--stack-layers", type=int, default=30)
     ap.add_argument("--stack-tagged", action="store_true", help="layer stack hands activations on as tagged words (x_kind 2)")
+    ap.add_argument("--stack-halves", action="store_true", help="layer stack runs its rows as two interleaved half-batches (pipelined settled exchange)")
     ap.add_argument("--stack-settled", action="store_true", help="layer stack uses the settled exchange (x_kind 5) at every M and GPU count")
     ap.add_argument("--extra", action="store_true", help="also time M=4, the reference layouts and the comparators")
     ap.add_argument("--large", nargs="?", const="one", default=None, choices=["one", "all"],

@@ -381,7 +381,8 @@ typedef struct sptmm_stack_config {
 
 /* how a step's int32 output becomes the next step's int8 input (sptmm_seq_step::x_kind) */
 enum {
-    SPTMM_STACK_AUTO = 0,            /* settled across GPUs and from eight rows upward, else counters */
+    SPTMM_STACK_AUTO = 0,            /* across GPUs: settled, as two half-batches from twelve (even) rows
+                                        upward; one GPU: settled from eight rows upward, else counters */
     SPTMM_STACK_COUNTERS = 1,        /* x_kind 1: step counters, readers quantise                    */
     SPTMM_STACK_TAGGED = 2,          /* x_kind 2: tagged words polled by every reader                */
     SPTMM_STACK_ROW_MAXIMA = 3,      /* x_kind 3 for readers of whole rows (1 otherwise)             */
@@ -389,8 +390,9 @@ enum {
     SPTMM_STACK_SETTLED = 5,         /* x_kind 5: one watcher per word, local counters, int8 tile    */
     SPTMM_STACK_SETTLED_HALVES = 6   /* the same with the M rows (even) run as two half-batches whose
                                         steps alternate in the one kernel: while one half's outputs
-                                        travel, the other half is gathered (each step's weights are then
-                                        streamed twice; measured slower than 5, see csrc/stack.cpp) */
+                                        travel and settle -- in warps of their own, one step ahead -- the
+                                        other half is gathered (each step's weights are streamed twice;
+                                        pays at M=16 across GPUs, see csrc/stack.cpp)                  */
 };
 
 typedef struct sptmm_stack_weights sptmm_stack_weights;   /* this rank's shard of every matrix, uploaded */

@@ -43,10 +43,12 @@ __device__ __forceinline__ unsigned char *tile_base(unsigned char *dyn_smem)
     return dyn_smem + (kXsAbs - (uint32_t)__cvta_generic_to_shared(dyn_smem));
 }
 
+// `off`: byte offset of the tile from the fixed address (0 for the kernels that have one tile; the
+// compiler folds it away there)
 template <int RB>
-__device__ __forceinline__ void load_row(uint32_t row, uint32_t (&r)[RowWords<RB>::n])
+__device__ __forceinline__ void load_row(uint32_t row, uint32_t (&r)[RowWords<RB>::n], uint32_t off = 0)
 {
-    const uint32_t a = row * RB;
+    const uint32_t a = row * RB + off;
     if constexpr (RB == 1) asm volatile("ld.shared.s8 %0, [%1+2048];" : "=r"(r[0]) : "r"(a));
     else if constexpr (RB == 2) asm volatile("ld.shared.u16 %0, [%1+2048];" : "=r"(r[0]) : "r"(a));
     else if constexpr (RB == 4) asm volatile("ld.shared.u32 %0, [%1+2048];" : "=r"(r[0]) : "r"(a));
@@ -60,11 +62,11 @@ __device__ __forceinline__ void load_row(uint32_t row, uint32_t (&r)[RowWords<RB
 }
 
 template <int DT, int MT>
-__device__ __forceinline__ void gather_add(typename ActTraits<DT>::acc (&acc)[MT], uint32_t row)
+__device__ __forceinline__ void gather_add(typename ActTraits<DT>::acc (&acc)[MT], uint32_t row, uint32_t off = 0)
 {
     constexpr int RB = MT * ActTraits<DT>::size;
     uint32_t r[RowWords<RB>::n];
-    load_row<RB>(row, r);
+    load_row<RB>(row, r, off);
     if constexpr (DT == SPTMM_I8 && MT == 1) {
         acc[0] += (int32_t)r[0];                                     // the load sign-extends
     } else if constexpr (DT == SPTMM_I8) {
@@ -109,13 +111,15 @@ struct LaneAcc {
     using acc_t = typename ActTraits<DT>::acc;
     static constexpr bool kBiased = false;
     acc_t v[MT];
-    __device__ __forceinline__ void clear(uint32_t /*one*/)
+    uint32_t off;                                  // byte offset of the tile read from (see load_row)
+    __device__ __forceinline__ void clear(uint32_t /*one*/, uint32_t off_ = 0)
     {
+        off = off_;
 #pragma unroll
         for (int m = 0; m < MT; m++) v[m] = acc_t(0);
     }
     __device__ __forceinline__ void reserve(uint32_t) {}
-    __device__ __forceinline__ void add(uint32_t row) { gather_add<DT, MT>(v, row); }
+    __device__ __forceinline__ void add(uint32_t row) { gather_add<DT, MT>(v, row, off); }
     __device__ __forceinline__ void finish() {}
 };
 
@@ -128,9 +132,10 @@ struct LaneAcc<SPTMM_I8, MT, true> {
     uint32_t pk[NP];
     uint32_t n;                                // gathers held in the 16-bit fields
     uint32_t one;                              // the value 1, unknown to the compiler (see add())
-    __device__ __forceinline__ void clear(uint32_t one_)
+    uint32_t off;                              // byte offset of the tile read from (see load_row)
+    __device__ __forceinline__ void clear(uint32_t one_, uint32_t off_ = 0)
     {
-        one = one_;
+        one = one_; off = off_;
 #pragma unroll
         for (int m = 0; m < MT; m++) v[m] = 0;
 #pragma unroll
@@ -164,7 +169,7 @@ struct LaneAcc<SPTMM_I8, MT, true> {
     __device__ __forceinline__ void add(uint32_t row)
     {
         uint32_t r[RowWords<MT>::n];
-        load_row<MT>(row, r);
+        load_row<MT>(row, r, off);
         // The permutes run on the integer ALU pipe; plain adds would too, and with 16 rows that
         // pipe, not shared memory, bounds the kernel.  Written as multiply-adds by a 1 the
         // compiler cannot see through, the additions go to the FMA pipe instead and the two

@@ -159,6 +159,11 @@ __device__ __forceinline__ unsigned long long seq_ns(const volatile uint32_t *an
 
 // Every CTA's timestamp at a point inside the input stage, for steps 100..103 (tuning build only).
 #ifdef SPTMM_TUNING
+#define SEQ_MARK_BY(prm, step, slot, anchor, who)                                                            \
+    do {                                                                                                     \
+        if ((prm).trace != nullptr && threadIdx.x == (who) && (step) >= 100 && (step) < 104)                  \
+            (prm).trace[5120 + (slot) * 1024 + ((step) - 100) * 256 + blockIdx.x] = seq_ns(anchor);           \
+    } while (0)
 #define SEQ_MARK(prm, step, slot, anchor)                                                                   \
     do {                                                                                                     \
         if ((prm).trace != nullptr && threadIdx.x == 33 && (step) >= 100 && (step) < 104)                     \
@@ -166,6 +171,7 @@ __device__ __forceinline__ unsigned long long seq_ns(const volatile uint32_t *an
     } while (0)
 #else
 #define SEQ_MARK(prm, step, slot, anchor) do { } while (0)
+#define SEQ_MARK_BY(prm, step, slot, anchor, who) do { } while (0)
 #endif
 
 __device__ __forceinline__ void seq_bulk_fetch(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar)
@@ -722,11 +728,14 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;
 // One arrival of this CTA at a local counter, then wait until every CTA of this GPU has arrived
 // (thread 0 polls, bounded; the others wait at the CTA barrier).  The release covers what the
 // CTA's threads wrote before the barrier in front of it.
-__device__ __forceinline__ void settle_barrier(unsigned long long *ctr, unsigned long long target, uint32_t *failed, uint32_t *status,
-                                               uint32_t poll_limit)
+// BAR / COUNT name the CTA barrier of the threads that take part (the consumers, or the settle warps
+// of the pipelined kernel); `leader` is the one thread that arrives and polls.
+template <int BAR, int COUNT>
+__device__ __forceinline__ void settle_barrier_on(unsigned long long *ctr, unsigned long long target, uint32_t *failed, uint32_t *status,
+                                                  uint32_t poll_limit, bool leader)
 {
-    consumer_sync();
-    if (threadIdx.x == 0) {
+    asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(COUNT) : "memory");
+    if (leader) {
         asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
         if (!*failed) {
             unsigned long long v = 0;
@@ -737,7 +746,12 @@ __device__ __forceinline__ void settle_barrier(unsigned long long *ctr, unsigned
             if (v < target) { *failed = 1; atomicOr(status, 16u); }
         }
     }
-    consumer_sync();
+    asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(COUNT) : "memory");
+}
+__device__ __forceinline__ void settle_barrier(unsigned long long *ctr, unsigned long long target, uint32_t *failed, uint32_t *status,
+                                               uint32_t poll_limit)
+{
+    settle_barrier_on<1, 512>(ctr, target, failed, status, poll_limit, threadIdx.x == 0);
 }
 
 // x_kind 5, the settled exchange.  The producing step stored tagged int32 words (into every rank's
@@ -812,14 +826,6 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
         if (tid < p.M && rowmax_s[tid]) atomicMax(amax_g + tid, (uint32_t)rowmax_s[tid]);
         settle_barrier(c1, p.target_local, failed, p.status, p.poll_limit);
         SEQ_MARK(p, s, 1, failed);
-        if constexpr (MT == 4) {
-            // Up to four rows: every word has arrived and the maxima are known, so each CTA reads the rows
-            // itself (at most 4 x K ints out of L2) and rounds them in one pass -- cheaper than a second
-            // counter and a tile copy, which is what wider tiles take below.
-            stage_x_scaled<MT, true>(xs, d, p.M, amax_g, write_scale);
-            SEQ_MARK(p, s, 2, failed);
-            return;
-        }
         float *scale_s = reinterpret_cast<float *>(red);
         if (tid < (uint32_t)MT) {
             const uint32_t a = tid < p.M ? __ldcg(amax_g + tid) : 0u;
@@ -864,16 +870,138 @@ __device__ __forceinline__ void stage_x_settled(unsigned char *xs, const SeqDesc
     }
 }
 
+// ---- the pipelined variant of the settled exchange (XV = 3) ------------------------------------
+// Two extra warps per CTA (the settle warps) run the whole settle phase of a step -- watch this CTA's
+// columns arrive, meet at the local counters, quantise the columns, fetch the finished tile -- into a
+// SECOND tile buffer while the sixteen consumer warps are still gathering the step before.  The
+// consumers never wait at a counter; they wait for "tile ready" and announce "tile free".  It pays
+// when the step list interleaves independent chains (a step's input then comes from the step before
+// the previous one and has usually arrived while the previous step is being gathered).
+constexpr uint32_t kSettleThreads = 64;
+constexpr uint32_t kPipeThreads = kConsumerThreads + 32 + kSettleThreads;
+
+__device__ __forceinline__ void settler_sync() { asm volatile("bar.sync 2, 64;" ::: "memory"); }
+
+// One step's input tile, by the 64 settle threads: `xs` is the tile buffer of this step, `ready_a`
+// its "tile ready" barrier.  st = 0..63 numbers the settle threads.
+template <int MT>
+__device__ __forceinline__ void settle_ahead(unsigned char *xs, uint32_t ready_a, const SeqDesc &d, const SeqParams &p, uint32_t s,
+                                             uint32_t st, int *rowmax_s, float *scale_s, float *xscale_out, uint32_t *failed)
+{
+    static_assert(MT >= 4, "the pipelined exchange is for tiles of several rows");
+    const uint32_t cta = blockIdx.x, lane = st & 31;
+    const bool sys = p.n_peers != 0;
+    if (d.x_kind == 0) {
+        // int8 activations as they are: transpose them into the tile (only the first steps of a chain)
+        const int8_t *X = reinterpret_cast<const int8_t *>(d.X);
+        for (uint32_t i = st; i < d.K * (uint32_t)MT; i += kSettleThreads) {
+            const uint32_t k = i / MT, m = i - k * MT;
+            xs[i] = (unsigned char)tile_byte<MT>(m < p.M ? (int)__ldcg(X + (size_t)m * d.ldx + k) : 0);
+        }
+        if (st < (uint32_t)MT) xs[(size_t)d.K * MT + st] = (unsigned char)tile_byte<MT>(0);      // the zero row
+        if (st < 16) xscale_out[st] = 1.0f;
+        settler_sync();
+        if (st == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready_a) : "memory");
+        return;
+    }
+    const uint32_t tag = seq_tag(p.run_mod, d.in_tag_m, d.in_tag_j);
+    const uint32_t k0 = (uint32_t)(((uint64_t)d.K * cta) / p.G), k1 = (uint32_t)(((uint64_t)d.K * (cta + 1)) / p.G), nk = k1 - k0;
+    const int32_t *A = reinterpret_cast<const int32_t *>(d.X);
+    unsigned long long *c1 = p.settle + 2 * (size_t)s, *c2 = c1 + 1;
+    uint32_t *amax_g = p.amax + ((size_t)p.run_parity * p.nsteps + s) * 16;
+    unsigned char *tile_g = p.xq + (size_t)(s & 1) * p.xq_stride;
+    bool ok = *failed == 0;
+    if (st < 16) rowmax_s[st] = 0;
+    settler_sync();
+    // my columns: st, st + 64, ...; the first one's values stay in registers
+    int v[MT], am[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) { v[m] = 0; am[m] = 0; }
+    for (uint32_t c = st; c < nk; c += kSettleThreads) {
+        const uint32_t k = k0 + c;
+        int w[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) w[m] = (uint32_t)m < p.M ? __ldcg(A + (size_t)m * d.ldx + k) : (int)(tag << 24);
+        for (uint32_t it = 0; ok; it++) {
+            bool stale = false;
+#pragma unroll
+            for (int m = 0; m < MT; m++)
+                if (((uint32_t)w[m] >> 24) != tag) { stale = true; w[m] = ld_fresh(A + (size_t)m * d.ldx + k, sys); }
+            if (!stale) break;
+            if (it >= p.poll_limit) ok = false;
+        }
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            w[m] = untag(w[m]);
+            am[m] = max(am[m], abs(w[m]));
+            if (c == st) v[m] = w[m];
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        const int a = __reduce_max_sync(0xffffffffu, am[m]);
+        if (lane == 0 && a) atomicMax(rowmax_s + m, a);
+    }
+    if (!ok && !*failed) { *failed = 1; atomicOr(p.status, 2u); }
+    settler_sync();
+    SEQ_MARK_BY(p, s, 0, failed, kConsumerThreads + 33);
+    if (st < p.M && rowmax_s[st]) atomicMax(amax_g + st, (uint32_t)rowmax_s[st]);
+    settle_barrier_on<2, 64>(c1, p.target_local, failed, p.status, p.poll_limit, st == 0);
+    SEQ_MARK_BY(p, s, 1, failed, kConsumerThreads + 33);
+    if (st < (uint32_t)MT) {
+        const uint32_t a = st < p.M ? __ldcg(amax_g + st) : 0u;
+        scale_s[st] = a ? 127.0f / (float)a : 0.0f;
+        xscale_out[st] = (float)a / 127.0f;
+        if (cta == 0 && d.scale_out && st < p.M) d.scale_out[st] = (float)a / 127.0f;
+    }
+    settler_sync();
+    for (uint32_t c = st; c < nk; c += kSettleThreads) {
+        const uint32_t k = k0 + c;
+        uint32_t o[MT / 4];
+#pragma unroll
+        for (int q = 0; q < MT / 4; q++) {
+            o[q] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int m = 4 * q + i;
+                const int val = c == st ? v[m] : ((uint32_t)m < p.M ? untag(__ldcg(A + (size_t)m * d.ldx + k)) : 0);
+                o[q] |= ((uint32_t)quant1(val, scale_s[m]) & 0xffu) << (8 * i);
+            }
+            o[q] ^= 0x80808080u;
+        }
+        if constexpr (MT == 4) *reinterpret_cast<uint32_t *>(tile_g + (size_t)k * 4) = o[0];
+        else if constexpr (MT == 8) *reinterpret_cast<uint2 *>(tile_g + (size_t)k * 8) = make_uint2(o[0], o[1]);
+        else *reinterpret_cast<uint4 *>(tile_g + (size_t)k * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    settle_barrier_on<2, 64>(c2, p.target_local, failed, p.status, p.poll_limit, st == 0);
+    SEQ_MARK_BY(p, s, 2, failed, kConsumerThreads + 33);
+    if (st < (uint32_t)MT) xs[(size_t)d.K * MT + st] = (unsigned char)tile_byte<MT>(0);      // the zero row
+    settler_sync();
+    if (st == 0) {
+        const uint32_t bytes = d.K * MT;
+        asm volatile("fence.proxy.async;" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ready_a), "r"(bytes) : "memory");
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(xs);
+        for (uint32_t o = 0; o < bytes; o += 65536u) {
+            const uint32_t n = min(65536u, bytes - o);
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dst + o), "l"(tile_g + o), "r"(n), "r"(ready_a) : "memory");
+        }
+    }
+}
+
 // XV selects what a kernel variant knows about (each carries only its own code, which keeps the
 // registers of the input stages it does not need out of the gather loop's way):
 //   0  int8 inputs and the counter hand-over (x_kind 0, 1)
 //   1  also tagged words polled by every reader, row maxima, the producer-side quantiser (x_kind 2, 3, 4)
 //   2  int8 inputs and the settled exchange (x_kind 0, 5)
+//   3  the same with the settle phase in two warps of its own, one step ahead of the gather (see settle_ahead)
 template <int MT, int XV>
-__global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_constant__ SeqParams p)
+__global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32, 1) k_seq(const __grid_constant__ SeqParams p)
 {
     constexpr bool TAGGED = XV == 1;          // the polling exchanges
     constexpr bool SETTLED = XV == 2;
+    constexpr bool PIPE = XV == 3;
     constexpr bool TAGS = XV != 0;            // outputs may carry tags
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     unsigned char *smem = tile_base(dyn_smem);     // the tile's fixed address; all offsets count from it
@@ -882,11 +1010,12 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     const uint32_t slot_blocks = p.slot_blocks, slot_bytes = slot_blocks * 512;
     const bool producer = warp == kConsumers;
 
-    // ---- shared memory: X tile | column sums (two buffers) | scratch | barriers | rings
+    // ---- shared memory: X tile (two of them in the pipelined variant) | column sums (two buffers) | scratch | barriers | rings
     unsigned char *xs = smem;
-    int *c_base = reinterpret_cast<int *>(smem + p.xs_bytes);
+    const size_t tiles_bytes = PIPE ? 2 * (size_t)p.xs_bytes : (size_t)p.xs_bytes;
+    int *c_base = reinterpret_cast<int *>(smem + tiles_bytes);
     int *red = c_base + 2 * (size_t)p.max_cols * MT;
-    size_t o = p.xs_bytes + (2 * (size_t)p.max_cols * MT + kRedInts) * 4;
+    size_t o = tiles_bytes + (2 * (size_t)p.max_cols * MT + kRedInts) * 4;
     o = (o + 7) & ~(size_t)7;
     const uint32_t bars_a = (uint32_t)__cvta_generic_to_shared(smem + o);     // [warp][full R | empty R]
     o += (size_t)kConsumers * 2 * R * 8;
@@ -899,11 +1028,19 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     __shared__ __align__(8) unsigned long long xbar;        // completion of the activation tile's bulk copy (x_kind 5)
     const uint32_t xbar_a = (uint32_t)__cvta_generic_to_shared(&xbar);
     uint32_t xphase = 0;
+    // pipelined variant: per tile buffer, "ready" (filled by the settle warps) and "free" (gathered by the consumers)
+    __shared__ __align__(8) unsigned long long tile_bar[4];
+    __shared__ float xscale_buf[2][16];
+    __shared__ int settle_rowmax_s[16];
+    __shared__ float settle_scale_s[16];
+    const uint32_t ready_a = (uint32_t)__cvta_generic_to_shared(&tile_bar[0]), free_a = ready_a + 16;
     if (tid == 0) {
         failed = 0;
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(xbar_a) : "memory");
+        if constexpr (PIPE)
+            for (uint32_t i = 0; i < 4; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ready_a + 8 * i) : "memory");
     }
-    if (!producer && lane == 0) {
+    if (warp < kConsumers && lane == 0) {
         for (uint32_t i = 0; i < 2 * R; i++)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars_a + (warp * 2 * R + i) * 8) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -955,6 +1092,24 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         return;
     }
 
+    // ================= settle warps (pipelined variant): one step ahead of the consumers =================
+    if constexpr (PIPE) {
+        if (warp > kConsumers) {
+            const uint32_t st = tid - (kConsumerThreads + 32);
+            uint32_t free_phase[2] = {0, 0};
+            for (uint32_t t = 0; t < p.nsteps; t++) {
+                const uint32_t b = t & 1;
+                if (t >= 2) {            // the buffer's previous tile must have been gathered
+                    if (!seq_bounded_wait(free_a + 8 * b, free_phase[b]) && !failed) { failed = 1; atomicOr(p.status, 4u); }
+                    free_phase[b] ^= 1;
+                }
+                settle_ahead<MT>(xs + (size_t)b * p.xs_bytes, ready_a + 8 * b, p.desc[t], p, t, st, settle_rowmax_s, settle_scale_s,
+                                 xscale_buf[b], &failed);
+            }
+            return;
+        }
+    }
+
     // ================= consumer warps =================
     // the first threads carry one word each of a step's descriptor, threads 64..67 its plan entries
     auto load_step_word = [&](uint32_t st) -> uint32_t {
@@ -974,6 +1129,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
     const uint32_t full_a = bars_a + warp * 2 * R * 8, empty_a = full_a + R * 8;
     const uint4 *ring = reinterpret_cast<const uint4 *>(rings + (size_t)warp * R * slot_bytes);
     uint32_t cslot = 0, cpar = 0;            // consumer cursor: slot and phase parity
+    [[maybe_unused]] uint32_t ready_phase[2] = {0, 0};
     int held_slot = -1;                      // a consumed slot whose release is deferred (see below)
     bool ring_ok = true;
 
@@ -987,7 +1143,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         const bool tracing = p.trace != nullptr && cta == 0 && tid == 33 && s < 256;
 #endif
         // ---- wait until the step this one depends on has finished everywhere
-        if (d.dep >= 0 && !(TAGGED && (d.x_kind == 2 || d.x_kind == 4)) && !(SETTLED && d.x_kind == 5)) {     // tagged inputs are waited for word by word while staging
+        if (d.dep >= 0 && !(TAGGED && (d.x_kind == 2 || d.x_kind == 4)) && !((SETTLED || PIPE) && d.x_kind == 5)) {     // tagged inputs are waited for word by word while staging
             if (tid == 0 && !failed) {
                 const unsigned long long *ctr = p.counters + d.dep;
                 unsigned long long v = 0;
@@ -1017,7 +1173,14 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         // (TAGGED kernels are the ones that also know row maxima: plain sequences carry neither)
         if (TAGS && p.amax != nullptr && cta == 0 && tid < 16)        // the other half of the row maxima: clean for the next run
             p.amax[((p.run_parity ^ 1u) * p.nsteps + s) * 16 + tid] = 0u;
-        if (d.x_kind == 0) {
+        [[maybe_unused]] const uint32_t xoff = PIPE ? (s & 1) * p.xs_bytes : 0u;      // which tile buffer this step gathers from
+        if constexpr (PIPE) {
+            // the settle warps fill this step's tile (int8 inputs too); wait for it
+            if (!failed && !seq_bounded_wait(ready_a + 8 * (s & 1), ready_phase[s & 1])) { failed = 1; atomicOr(p.status, 1u); }
+            ready_phase[s & 1] ^= 1;
+            if (tid < 16) seq_xscale_s[tid] = xscale_buf[s & 1][tid];
+        }
+        else if (d.x_kind == 0) {
             stage_x_i8<MT>(xs, d, p.M);
             if (tid < 16) seq_xscale_s[tid] = 1.0f;          // int8 activations come as they are
         }
@@ -1079,7 +1242,7 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
                 bound = __ldg(d.blk_off + 2 * (size_t)c0 + li + 1);
             }
             LaneAcc<SPTMM_I8, MT> acc;
-            acc.clear(p.one);
+            acc.clear(p.one, xoff);
             bool dirty = false;
             auto flush = [&]() {
                 const uint32_t col = li >> 1;
@@ -1139,6 +1302,9 @@ __global__ void __launch_bounds__(kConsumerThreads + 32, 1) k_seq(const __grid_c
         }
         if (s + 1 < p.nsteps) store_step_word(s + 1, nxt);
         consumer_sync();
+        if constexpr (PIPE) {            // this step's tile is gathered: its buffer may take the tile after next
+            if (tid == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(free_a + 8 * (s & 1)) : "memory");
+        }
 #ifdef SPTMM_TUNING
         if (tracing) p.trace[s * 4 + 2] = seq_ns(&failed);
         if (p.trace != nullptr && tid == 33 && s >= 100 && s < 104) p.trace[4096 + (s - 100) * 256 + cta] = seq_ns(&failed);   // every CTA: gathered
@@ -1296,6 +1462,7 @@ struct sptmm_seq {
     bool tagged = false;             // some step reads tagged words: run the kernel variant that knows them
     bool uses_amax = false;          // some step is x_kind 3: the row-maxima area is in use
     bool settled = false;            // the steps with a producer are all x_kind 5: the kernel variant for that exchange
+    bool pipe = false;               // ... with the settle phase in warps of its own, one step ahead
     uint32_t poll_limit = 1u << 21;  // see sptmm_seq_set_wait_limit
     void *counter_peers[kMaxPeers] = {};
 };
@@ -1498,7 +1665,20 @@ static int seq_create_impl(const sptmm_seq_step *steps, uint32_t n, uint32_t M, 
     // shared memory: X tile, column sums + scratch, then as many 1 KB ring slots per warp as fit
     const uint32_t nwarps = 16;               // consumer warps (one more warp produces)
     q->xs_bytes = (uint32_t)xs_bytes(kmax, (int)q->mt);
-    size_t fixed = q->xs_bytes + (2 * (size_t)q->max_cols * q->mt + kRedInts) * 4;
+    // The settle phase runs in warps of its own, one step ahead, when that can overlap anything: tiles of
+    // several rows, settled exchange, and a step list in which some step reads the output of a step
+    // before the previous one (interleaved chains).  int8 inputs are then staged by the settle warps
+    // too, which do not wait for step counters.
+    {
+        bool ahead = false, plain_ok = true;
+        for (uint32_t s = 0; s < n; s++) {
+            if (steps[s].x_kind == 5 && steps[s].dep + 2 <= (int32_t)s) ahead = true;
+            if (steps[s].x_kind == 0 && steps[s].dep >= 0) plain_ok = false;
+        }
+        q->pipe = any_settled && q->mt >= 4 && ahead && plain_ok && 2 * (size_t)q->xs_bytes <= 120 * 1024;
+    }
+    const size_t tiles = q->pipe ? 2 * (size_t)q->xs_bytes : (size_t)q->xs_bytes;
+    size_t fixed = tiles + (2 * (size_t)q->max_cols * q->mt + kRedInts) * 4;
     fixed = (fixed + 7) & ~(size_t)7;
     const size_t avail = 223 * 1024;      // minus static shared memory and the gap before the tile
     // 4 KB slots stream best; halve them while three of them per warp do not fit beside the X tile
@@ -1594,6 +1774,9 @@ static int seq_launch(const sptmm_seq *q, const SeqParams &prm, cudaStream_t st)
 {
     // every kernel variant carries only the exchanges its sequence uses (see k_seq); the plain one is
     // 0.7 us per step faster on the 6912x2560 sequence than one that knows them all
+    if constexpr (MT >= 4) {
+        if (q->settled && q->pipe) return seq_launch_as<MT, 3>(q, prm, st);
+    }
     if (q->settled) return seq_launch_as<MT, 2>(q, prm, st);
     return (q->tagged || q->uses_amax) ? seq_launch_as<MT, 1>(q, prm, st) : seq_launch_as<MT, 0>(q, prm, st);
 }
@@ -1607,7 +1790,7 @@ static int seq_launch_as(const sptmm_seq *q, const SeqParams &prm, cudaStream_t 
         configured_device.store(q->device, std::memory_order_release);
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(q->G); cfg.blockDim = dim3(q->threads); cfg.dynamicSmemBytes = q->smem; cfg.stream = st;
+    cfg.gridDim = dim3(q->G); cfg.blockDim = dim3(XV == 3 ? kPipeThreads : q->threads); cfg.dynamicSmemBytes = q->smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeCooperative;      // all CTAs resident at once, or the launch fails
     attr[0].val.cooperative = 1;
@@ -1654,7 +1837,7 @@ extern "C" int sptmm_seq_run(sptmm_seq *q, void *stream)
     switch (q->mt) {
         case 1: return seq_launch<1>(q, prm, st);
         case 4: return seq_launch<4>(q, prm, st);
-        case 8: return seq_launch_as<8, 2>(q, prm, st);          // settled sequences only (see seq_create_impl)
+        case 8: return q->pipe ? seq_launch_as<8, 3>(q, prm, st) : seq_launch_as<8, 2>(q, prm, st);   // settled sequences only (see seq_create_impl)
         case 16: return seq_launch<16>(q, prm, st);
     }
     return fail(SPTMM_ERR_INVALID, "internal: row tile %u", q->mt);

@@ -145,16 +145,19 @@ extern "C" int sptmm_stack_weights_free(sptmm_stack_weights *w)
     return SPTMM_OK;
 }
 
-// Which exchange a stack uses when the caller leaves it open (exchange 0): measured on B200, the
-// settled exchange wins across GPUs at every M and on one GPU from eight rows upward; below that the
-// step counters with the reader-side quantiser do.  (Running the rows as two half-batches whose
-// steps alternate, SPTMM_STACK_SETTLED_HALVES, was measured slower at 2 GPUs -- M=4 2 505 against
-// 1 463 us per pass, M=16 3 143 against 2 597: a CTA sits inside the second half's counters and tile
-// copy just as it does inside the first's, so only the words' flight overlaps the other half's
-// gather, and every step's weights are streamed twice.  It stays available by name.)
+// Which exchange a stack uses when the caller leaves it open (exchange 0), from measurements on B200:
+// the settled exchange wins across GPUs at every M and on one GPU from eight rows upward; below that
+// the step counters with the reader-side quantiser do.  Across GPUs, twelve rows or more are run as
+// two half-batches whose steps alternate (SPTMM_STACK_SETTLED_HALVES): the settle phase of one half
+// then runs in warps of its own while the other half is gathered, which hides the hand-over almost
+// entirely (the tile is ready 6-10 us before it is needed) -- but two 8-row gathers cost 1.3x one
+// 16-row gather and every step's weights are streamed twice, so it nets 8-10 % at M=16 (2 GPUs 2 384
+// against 2 602 us per pass, 4 GPUs 1 888 against 2 109) and loses below (M=8: 1 566 against 1 521,
+// M=4: 1 592 against 1 371 at 4 GPUs).
 static uint32_t pick_exchange(uint32_t exchange, uint32_t M, uint32_t world)
 {
     if (exchange) return exchange;
+    if (world > 1 && M >= 12 && M % 2 == 0) return SPTMM_STACK_SETTLED_HALVES;
     return (world > 1 || M >= 8) ? SPTMM_STACK_SETTLED : SPTMM_STACK_COUNTERS;
 }
 
