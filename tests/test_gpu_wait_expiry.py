@@ -67,6 +67,38 @@ def test_missing_peer_ends_the_run_with_a_status(x_kind, M):
     assert (c1.cpu().numpy() == want).all()
 
 
+def test_missing_peer_with_the_settle_warps_running_ahead():
+    """Two interleaved chains make the sequence use the pipelined kernel (settle warps one step ahead,
+    two tile buffers): there, too, a peer that never delivers ends the run with a status instead of
+    hanging the settle warps or the consumers that wait for their tile."""
+    M, K, N = 4, 256, 128
+    W1 = sp.gen_ternary_iid(K, N, 0.4, 1)
+    W2 = sp.gen_ternary_iid(N, N, 0.5, 2)
+    w1 = sp.Weights(W1[: N // 2], sp.FMT_U16_V256).upload()
+    w2 = sp.Weights(W2[: N // 2], sp.FMT_U16_V256).upload()
+    xa, xb = dev(O.gen_x_i8(M * K, 3)), dev(O.gen_x_i8(M * K, 4))
+    bufs = [[torch.zeros((M, N), dtype=torch.int32, device="cuda") for _ in range(2)] for _ in range(6)]
+    steps = [{"w": w1, "X": xa, "ldc": N}, {"w": w1, "X": xb, "ldc": N},
+             {"w": w2, "X": bufs[0][0], "x_kind": 5, "dep": 0, "ldx": N, "ldc": N}, {"w": w2, "X": bufs[1][0], "x_kind": 5, "dep": 1, "ldx": N, "ldc": N},
+             {"w": w2, "X": bufs[2][0], "x_kind": 5, "dep": 2, "ldx": N, "ldc": N}, {"w": w2, "X": bufs[3][0], "x_kind": 5, "dep": 3, "ldx": N, "ldc": N}]
+    for s, st in enumerate(steps):
+        st["C_peers"] = [b.data_ptr() for b in bufs[s]]
+    nbytes = sp.seq_shared_bytes([dict(st, C=1) for st in steps], M)
+    areas = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    seq = sp.Sequence(steps, M=M, counter_peers=[a.data_ptr() for a in areas], rank=0)
+    seq.set_wait_limit(1 << 12)
+    seq.run()
+    status = seq.status()
+    assert status & 2 and status & ~(1 | 2 | 4 | 16) == 0, status
+    want = O.gemv_i8_dense(O.gen_x_i8(M * K, 3), W1[: N // 2]).reshape(M, N // 2)
+    assert ((((bufs[0][0].cpu().numpy()) << 8) >> 8)[:, : N // 2] == want).all()      # the first steps are complete
+    seq.close()
+    c1 = torch.zeros((M, N // 2), dtype=torch.int32, device="cuda")
+    ok = sp.Sequence([{"w": w1, "X": xa, "C": c1}], M=M)
+    ok.run()
+    assert ok.status() == 0 and (c1.cpu().numpy() == want).all()
+
+
 def test_wait_limit_rejects_a_null_handle_and_restores_the_default():
     W = sp.gen_ternary_iid(64, 32, 0.5, 1)
     w = sp.Weights(W, sp.FMT_U16_V256).upload()
