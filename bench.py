@@ -904,6 +904,18 @@ def run_timeline(args):
 
         lines.append("  %-6s  %s | %s | %s | %s | %s | %s | %s" % (name, q(gathered[i - 1]), q(wait[i]), q(marks[0][i]), q(marks[1][i]),
                                                                   q(marks[2][i]), q(staged[i]), q(gathered[i])))
+    if args.timeline_warps:
+        # the consumer warps of two CTAs: start and end of the gather after the CTA's tile was staged, time spent waiting for ring slots
+        wv = t[8192:8192 + 512].reshape(2, 4, 16, 4).astype(np.int64)
+        for ci, cta in enumerate((0, 100)):
+            for i, name in names:
+                w = wv[ci, i]
+                if w[:, 0].max() == 0:
+                    continue
+                t0 = staged[i][cta]
+                lines.append("  CTA %3d %-6s warps: start %s | end %s | waited for slots %s | slots %s" % (
+                    cta, name, " ".join("%d" % (x - t0) for x in w[:, 0]), " ".join("%d" % (x - t0) for x in w[:, 2]),
+                    " ".join("%d" % x for x in w[:, 1]), " ".join("%d" % x for x in w[:, 3])))
     for r in range(world):
         if r == rank:
             print("\n".join(lines), flush=True)
@@ -939,6 +951,7 @@ def main():
                     help="run one configuration briefly (for a profiler) instead of the benchmark")
     ap.add_argument("--timeline", type=int, default=0, metavar="M",
                     help="print the per-step timeline of the 30-layer stack at M rows (needs the tuning build of the library)")
+    ap.add_argument("--timeline-warps", action="store_true", help="with --timeline: also the consumer warps of two CTAs (gather start/end, time waiting for ring slots)")
     args = ap.parse_args()
     if args.timeline:
         run_timeline(args)

@@ -426,6 +426,46 @@ int sptmm_stack_sequence(sptmm_stack *st, sptmm_seq **seq);               /* the
 int sptmm_stack_wait_limit(sptmm_stack *st, uint32_t polls);              /* see sptmm_seq_set_wait_limit */
 int sptmm_stack_free(sptmm_stack *st);
 
+/* ---- split-K over the GPUs of one node as an object (csrc/splitk.cu) ------------------------ */
+/* The host side around sptmm_gemv_reduce: shard arithmetic, the per-rank arena and the phases of
+ * a pass.  No counterpart in the reference (one device, one stream, main.cu:1861; its only split
+ * of K is the lane striding of main.cu:581-584).
+ *  - sptmm_splitk_k_range: the rows of W (and elements of every row of X) rank r holds --
+ *    contiguous, boundaries on multiples of 16.  sptmm_splitk_col_range: the result columns rank r
+ *    owns after the reduce-scatter, N*r/world .. N*(r+1)/world.
+ *  - The arena of a rank (sptmm_splitk_arena_bytes; 256-byte aligned, zeroed by the caller, every
+ *    rank's mapped into every rank's address space like the stack's) holds the rank's result block
+ *    and one flag word per rank.  With one rank arena_peers may be NULL and the library allocates.
+ *  - `w`: this rank's K range encoded as a native u16 matrix and uploaded (or its tile of a K-tiled
+ *    encoding, sptmm_weights_tile); stays the caller's.
+ *  - sptmm_splitk_forward queues a whole pass on the stream: clear my block | barrier | add the
+ *    partial sums to their owners (sptmm_gemv_reduce) | barrier.  Every rank calls it the same
+ *    number of times.  The barrier is a one-warp kernel of this library -- each rank stores its pass
+ *    counter into every rank's flag words and polls its own -- so a pass needs no collective of
+ *    another library and no host round trip; its poll is bounded (sptmm_splitk_set_wait_limit,
+ *    reloads; 0 = default) and a poll that runs out sets bit 0 of sptmm_splitk_status (bit 1: the
+ *    matmul kernel's own status word, see sptmm_gemv_status).  Creation must have finished on every
+ *    rank before the first pass starts on any (a host-side barrier of the caller's).
+ *  - The phases are also callable one by one (clear, barrier, accumulate) for a caller that brings
+ *    its own barrier, or that runs several ranks one after another on one device, where the
+ *    library's barrier kernel must not be used: its ranks would wait for kernels queued behind them.
+ *  - sptmm_splitk_output: this rank's block, M x width row-major int32 / float, valid once the
+ *    stream has run the pass. */
+typedef struct sptmm_splitk sptmm_splitk;
+int sptmm_splitk_k_range(uint32_t K, uint32_t rank, uint32_t world, uint32_t *k0, uint32_t *k1);
+int sptmm_splitk_col_range(uint32_t N, uint32_t rank, uint32_t world, uint32_t *c0, uint32_t *c1);
+uint64_t sptmm_splitk_arena_bytes(uint32_t M, uint32_t N, uint32_t world);
+int sptmm_splitk_create(const sptmm_weights *w, uint32_t dtype, uint32_t M, uint32_t rank, uint32_t world,
+                        void *const *arena_peers, sptmm_splitk **out);
+int sptmm_splitk_forward(sptmm_splitk *s, const void *X_slice, uint32_t flags, void *stream);
+int sptmm_splitk_clear(sptmm_splitk *s, void *stream);
+int sptmm_splitk_barrier(sptmm_splitk *s, void *stream);
+int sptmm_splitk_accumulate(sptmm_splitk *s, const void *X_slice, uint32_t flags, void *stream);
+int sptmm_splitk_output(const sptmm_splitk *s, void **C, uint32_t *width);
+int sptmm_splitk_status(sptmm_splitk *s, uint32_t *status);
+int sptmm_splitk_set_wait_limit(sptmm_splitk *s, uint64_t polls);
+int sptmm_splitk_free(sptmm_splitk *s);
+
 /* ---- small device helpers so a C caller needs no CUDA headers ------------------------------ */
 int sptmm_device_count(int *count);
 int sptmm_set_device(int device);

@@ -102,6 +102,18 @@ def _load() -> C.CDLL:
         "sptmm_stack_sequence": (i32, [vp, C.POINTER(vp)]),
         "sptmm_stack_wait_limit": (i32, [vp, u32]),
         "sptmm_stack_free": (i32, [vp]),
+        "sptmm_splitk_k_range": (i32, [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]),
+        "sptmm_splitk_col_range": (i32, [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]),
+        "sptmm_splitk_arena_bytes": (u64, [u32, u32, u32]),
+        "sptmm_splitk_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp), C.POINTER(vp)]),
+        "sptmm_splitk_forward": (i32, [vp, vp, u32, vp]),
+        "sptmm_splitk_clear": (i32, [vp, vp]),
+        "sptmm_splitk_barrier": (i32, [vp, vp]),
+        "sptmm_splitk_accumulate": (i32, [vp, vp, u32, vp]),
+        "sptmm_splitk_output": (i32, [vp, C.POINTER(vp), C.POINTER(u32)]),
+        "sptmm_splitk_status": (i32, [vp, C.POINTER(u32)]),
+        "sptmm_splitk_set_wait_limit": (i32, [vp, u64]),
+        "sptmm_splitk_free": (i32, [vp]),
         "sptmm_device_count": (i32, [C.POINTER(C.c_int)]),
         "sptmm_set_device": (i32, [C.c_int]),
         "sptmm_dev_alloc": (i32, [C.POINTER(vp), u64]),
@@ -130,6 +142,9 @@ EXPORTS = ["sptmm_last_error", "sptmm_version", "sptmm_gen_ternary_fixed", "sptm
            "sptmm_stack_weights_create", "sptmm_stack_weights_info", "sptmm_stack_weights_matrix", "sptmm_stack_weights_free",
            "sptmm_stack_arena_bytes", "sptmm_stack_create", "sptmm_stack_set_input", "sptmm_stack_forward", "sptmm_stack_buffer",
            "sptmm_stack_status", "sptmm_stack_exchange", "sptmm_stack_sequence", "sptmm_stack_wait_limit", "sptmm_stack_free",
+           "sptmm_splitk_k_range", "sptmm_splitk_col_range", "sptmm_splitk_arena_bytes", "sptmm_splitk_create", "sptmm_splitk_forward",
+           "sptmm_splitk_clear", "sptmm_splitk_barrier", "sptmm_splitk_accumulate", "sptmm_splitk_output", "sptmm_splitk_status",
+           "sptmm_splitk_set_wait_limit", "sptmm_splitk_free",
            "sptmm_device_count", "sptmm_set_device", "sptmm_dev_alloc", "sptmm_dev_free",
            "sptmm_memcpy_h2d", "sptmm_memcpy_d2h", "sptmm_device_sync", "sptmm_stream_wait"]
 

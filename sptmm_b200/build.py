@@ -28,7 +28,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"] + ARCH
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-pthread"]
 
-LIB_SOURCES = ["host_encode.cpp", "weights_file.cpp", "stack.cpp", "ternarise.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "kernels_seq.cu", "kernels_quant.cu", "cublas_cmp.cu"]
+LIB_SOURCES = ["host_encode.cpp", "weights_file.cpp", "stack.cpp", "ternarise.cpp", "device_api.cu", "kernels_native.cu", "kernels_compat.cu", "kernels_seq.cu", "kernels_quant.cu", "splitk.cu", "cublas_cmp.cu"]
 HEADERS = ["internal.h", "device_common.cuh", "tuning.h", os.path.join(ROOT, "include", "sptmm.h")]
 
 

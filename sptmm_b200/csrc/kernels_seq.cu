@@ -174,6 +174,14 @@ __device__ __forceinline__ unsigned long long seq_ns(const volatile uint32_t *an
 #define SEQ_MARK_BY(prm, step, slot, anchor, who) do { } while (0)
 #endif
 
+// 16 bytes of a ring slot by shared-space address
+__device__ __forceinline__ uint4 lds_vec(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+
 __device__ __forceinline__ void seq_bulk_fetch(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -1127,7 +1135,7 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
     store_step_word(0, load_step_word(0));
     consumer_sync();
     const uint32_t full_a = bars_a + warp * 2 * R * 8, empty_a = full_a + R * 8;
-    const uint4 *ring = reinterpret_cast<const uint4 *>(rings + (size_t)warp * R * slot_bytes);
+    const uint32_t ring_sa = (uint32_t)__cvta_generic_to_shared(rings + (size_t)warp * R * slot_bytes) + lane * 16;
     uint32_t cslot = 0, cpar = 0;            // consumer cursor: slot and phase parity
     [[maybe_unused]] uint32_t ready_phase[2] = {0, 0};
     int held_slot = -1;                      // a consumed slot whose release is deferred (see below)
@@ -1265,11 +1273,35 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
                 acc.add(v.w & 0xffffu);
                 acc.add(v.w >> 16);
             };
+#ifdef SPTMM_TUNING
+            // per-warp view of the gather (two CTAs, steps 100..103): start, time spent waiting for ring slots, slots
+            const bool wtr = p.trace != nullptr && lane == 0 && s >= 100 && s < 104 && (cta == 0 || cta == 100);
+            unsigned long long w_t0 = wtr ? seq_ns(&failed) : 0ull, w_wait = 0ull;
+            uint32_t w_slots = 0;
+#endif
+            // two blocks of one list at a time: sixteen independent gathers in flight per lane
+            auto gather16 = [&](const uint4 v0, const uint4 v1) {
+                acc.reserve(16);
+                acc.add(v0.x & 0xffffu); acc.add(v1.x & 0xffffu);
+                acc.add(v0.x >> 16);     acc.add(v1.x >> 16);
+                acc.add(v0.y & 0xffffu); acc.add(v1.y & 0xffffu);
+                acc.add(v0.y >> 16);     acc.add(v1.y >> 16);
+                acc.add(v0.z & 0xffffu); acc.add(v1.z & 0xffffu);
+                acc.add(v0.z >> 16);     acc.add(v1.z >> 16);
+                acc.add(v0.w & 0xffffu); acc.add(v1.w & 0xffffu);
+                acc.add(v0.w >> 16);     acc.add(v1.w >> 16);
+            };
             for (uint32_t b = wb0; b < wb1;) {
                 const uint32_t cnt = min(slot_blocks, wb1 - b);
+#ifdef SPTMM_TUNING
+                const unsigned long long w_ta = wtr ? seq_ns(&failed) : 0ull;
+#endif
                 if (ring_ok) ring_ok = seq_bounded_wait(full_a + cslot * 8, cpar);
                 if (!ring_ok) break;
-                const uint4 *slot = ring + (size_t)cslot * (slot_bytes / 16) + lane;
+#ifdef SPTMM_TUNING
+                if (wtr) { w_wait += seq_ns(&failed) - w_ta; w_slots++; }
+#endif
+                const uint32_t slot_a = ring_sa + cslot * slot_bytes;           // this lane's vector of the slot's first block
                 // runs of blocks that stay inside one list go through a loop with no checks in it
                 for (uint32_t i = 0; i < cnt;) {
                     if (b + i >= bound) {
@@ -1280,8 +1312,9 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
                         } while (b + i >= bound);
                     }
                     const uint32_t run = min(cnt - i, bound - (b + i));
-#pragma unroll 2
-                    for (uint32_t j = 0; j < run; j++) gather8(slot[(i + j) * 32]);
+                    uint32_t a = slot_a + i * 512u, j = 0;
+                    for (; j + 2 <= run; j += 2, a += 1024u) gather16(lds_vec(a), lds_vec(a + 512u));
+                    if (j < run) gather8(lds_vec(a));
                     dirty = true;
                     i += run;
                 }
@@ -1299,6 +1332,12 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
             }
             if (!ring_ok && lane == 0) { failed = 1; atomicOr(p.status, 1u); }
             if (dirty) flush();
+#ifdef SPTMM_TUNING
+            if (wtr) {
+                unsigned long long *o = p.trace + 8192 + ((((cta != 0) * 4u + (s - 100)) * 16u + warp) * 4u);
+                o[0] = w_t0; o[1] = w_wait; o[2] = seq_ns(&failed); o[3] = w_slots;
+            }
+#endif
         }
         if (s + 1 < p.nsteps) store_step_word(s + 1, nxt);
         consumer_sync();
