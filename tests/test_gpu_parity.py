@@ -87,7 +87,7 @@ def test_native_u16_extreme_columns():
 
 @pytest.mark.parametrize("M", [1, 4])
 def test_native_u16_full_size_fixed_s4096(M):
-    # BASELINE configs 0/1 shape with the reference's own generator (-S=4096)
+    # the headline benchmark shape with the reference's own generator (-S=4096)
     K, N, S = 6912, 2560, 4096
     W = sp.gen_ternary_fixed(K, N, S)
     X = O.gen_x_i8(M * K, 1)
@@ -99,7 +99,7 @@ def test_native_u16_full_size_fixed_s4096(M):
 
 
 def test_native_u16_full_size_iid_third():
-    # BASELINE config 0: i.i.d. P=1/3 each, seed 0, M=1, int8 uniform
+    # headline configuration: i.i.d. P=1/3 each, seed 0, M=1, int8 uniform
     K, N = 6912, 2560
     W = sp.gen_ternary_iid(K, N, 1 / 3, 0)
     X = O.gen_x_i8(K, 1)
@@ -119,7 +119,7 @@ def _float_case(K, N, M, p0, dtype):
 @pytest.mark.parametrize("dtype,rtol", [(sp.F16, FP16_RTOL), (sp.F32, FP32_RTOL)])
 @pytest.mark.parametrize("K,N,M", [(700, 40, 1), (700, 40, 4), (6912, 2560, 4), (2560, 640, 16), (1024, 64, 9)])
 def test_native_u16_float(dtype, rtol, K, N, M):
-    # BASELINE config 1: M=4, K=6912, N=2560, fp16 N(0,1), fp32 accumulation
+    # the M=4 configuration: M=4, K=6912, N=2560, fp16 N(0,1), fp32 accumulation
     W, Xh, ref, dbl, ab = _float_case(K, N, M, 1 / 3, dtype)
     w = sp.Weights(W, sp.FMT_U16_V256).upload()
     out = torch.zeros((M, N), dtype=torch.float32, device="cuda")
@@ -199,7 +199,7 @@ def test_delta_lane_ragged_iid(p0, K, N):
 
 @pytest.mark.parametrize("S", [4608, 4096, 3456, 1728])
 def test_delta_lane_sparsity_sweep_full_size(S):
-    # BASELINE config 2 on the native narrow-integer format: bit-exact vs the undecoded u16 path
+    # the delta-format configuration on the native narrow-integer format: bit-exact vs the undecoded u16 path
     K, N = 6912, 2560
     W = sp.gen_ternary_fixed(K, N, S)
     X = O.gen_x_i8(K, 1)
@@ -465,7 +465,7 @@ def test_row_split_delta2_raw_pointers(S, M):
 
 @pytest.mark.parametrize("S", [4608, 4096, 3456, 1728])
 def test_row_split_delta2_sparsity_sweep(S):
-    # BASELINE config 2: M=1, 6912x2560, P(0) in {.33,.5,.75} <-> S in {4608,3456,1728};
+    # the delta-format sweep: M=1, 6912x2560, P(0) in {.33,.5,.75} <-> S in {4608,3456,1728};
     # the delta result must equal the undecoded u16 path bit for bit
     K, N = 6912, 2560
     W = sp.gen_ternary_fixed(K, N, S)
