@@ -4,6 +4,7 @@
 //  k_div       W_map_{8,16,32}_div, u16 [chunk][column][split]        (replaces main.cu:556-594)
 //  k_delta256  W_map_delta2_div256, u8 gaps [block][column][256]      (replaces main.cu:599-764)
 //  k_i2s       2-bit codes, 16 rows per word                          (replaces bitnet_kernels.cuh:75-111)
+//  k_i2s_row   the same for one row of X with its activations in registers
 //
 // Differences from the reference kernels: multi-warp CTAs that stage the activation tile
 // (transposed, up to 16 rows) in shared memory once, so the index stream is read once for all
@@ -231,6 +232,65 @@ __global__ void __launch_bounds__(256) k_i2s(const I2sParams p)
     }
 }
 
+// One row of X (M = 1), K a multiple of 64 and at most NV*2048: a warp owns whole columns and reads a
+// column's codes with full-width 16-byte loads (lane l takes vectors l, l+32, ...).  Since a lane
+// meets the same rows of X in every column, its 64 bytes of X per vector stay in registers: no
+// shared memory, no CTA barrier, and the next column's loads are in flight while this one is summed.
+template <int NV>
+__global__ void __launch_bounds__(128) k_i2s_row(const I2sParams p)
+{
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const uint32_t tw = gridDim.x * nwarps, nvec = p.K / 64;
+    uint32_t col = blockIdx.x * nwarps + warp;
+    const uint4 *w4 = reinterpret_cast<const uint4 *>(p.w);
+    pdl_launch_dependents();
+    uint4 nxt[NV];
+    auto load_col = [&](uint32_t c) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const uint32_t v = lane + 32u * i;
+            nxt[i] = (c < p.N && v < nvec) ? __ldg(w4 + (size_t)c * nvec + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    load_col(col);                           // the weights do not depend on the kernel before
+    pdl_wait_prior_grid();
+    uint4 x[NV][4];
+    int sumx = 0;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const uint32_t v = lane + 32u * i;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            x[i][w] = v < nvec ? __ldg(reinterpret_cast<const uint4 *>(p.X) + (size_t)v * 4 + w) : make_uint4(0u, 0u, 0u, 0u);
+            sumx = __dp4a((int)x[i][w].x, 0x01010101, sumx);
+            sumx = __dp4a((int)x[i][w].y, 0x01010101, sumx);
+            sumx = __dp4a((int)x[i][w].z, 0x01010101, sumx);
+            sumx = __dp4a((int)x[i][w].w, 0x01010101, sumx);
+        }
+    }
+    sumx = warp_sum(sumx);
+    for (; col < p.N; col += tw) {
+        uint4 cur[NV];
+#pragma unroll
+        for (int i = 0; i < NV; i++) cur[i] = nxt[i];
+        load_col(col + tw);
+        int acc = 0;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const uint32_t word[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                acc = __dp4a((int)x[i][w].x, (int)(word[w] & 0x03030303u), acc);
+                acc = __dp4a((int)x[i][w].y, (int)((word[w] >> 2) & 0x03030303u), acc);
+                acc = __dp4a((int)x[i][w].z, (int)((word[w] >> 4) & 0x03030303u), acc);
+                acc = __dp4a((int)x[i][w].w, (int)((word[w] >> 6) & 0x03030303u), acc);
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) p.C[col] = acc - 2 * sumx;
+    }
+}
+
 // --------------------------------------------------------------------------------------------
 template <auto kern, typename Prm>
 static int launch_generic(const Prm &prm, dim3 grid, size_t smem, bool pdl, cudaStream_t st, uint32_t threads = 256)
@@ -353,13 +413,24 @@ int launch_i2s(const GemvArgs &a)
     if (smem > 227 * 1024) return fail(SPTMM_ERR_UNSUPPORTED, "i2s: K=%u does not fit shared memory", w.K);
     I2sParams prm{(const uint32_t *)a.arrays[0], (const int8_t *)a.X, (int32_t *)a.C, w.K, w.N, a.M,
                   (a.flags & SPTMM_X_COLMAJOR) ? 1u : 0u, (a.flags & SPTMM_C_COLMAJOR) ? 1u : 0u};
-    // Four columns per warp.  Small matrices get small CTAs so that every SM has one (the 2560
-    // columns of the 2B shapes: 160 CTAs of 128 threads, the reference's own launch shape,
-    // bitnet_kernels.cuh:75-111); wide ones keep 256 threads, i.e. fewer copies of X per column.
-    const uint32_t threads = w.N <= 8192 ? 128u : 256u, cols_per_cta = threads / 8;
-    const dim3 grid((w.N + cols_per_cta - 1) / cols_per_cta, (a.M + mt - 1) / mt, 1);
     const bool pdl = (a.flags & SPTMM_LAUNCH_PDL) != 0;
     cudaStream_t st = (cudaStream_t)a.stream;
+    // One row, K a multiple of 64 up to 8192, X on a 16-byte boundary: the register form, a warp per
+    // column, four warps per CTA and about four columns per warp (X is fetched once per warp).
+    if (a.M == 1 && w.K % 64 == 0 && w.K <= 8192 && (reinterpret_cast<uintptr_t>(a.X) & 15) == 0) {
+        const uint32_t sms = w.sm_count ? w.sm_count : 148u;
+        const dim3 grid(std::max(1u, std::min((w.N + 15) / 16, 4 * sms)), 1, 1);
+        const uint32_t nv = (w.K / 64 + 31) / 32;
+        switch (nv) {
+            case 1: return launch_generic<k_i2s_row<1>>(prm, grid, 0, pdl, st, 128);
+            case 2: return launch_generic<k_i2s_row<2>>(prm, grid, 0, pdl, st, 128);
+            case 3: return launch_generic<k_i2s_row<3>>(prm, grid, 0, pdl, st, 128);
+            default: return launch_generic<k_i2s_row<4>>(prm, grid, 0, pdl, st, 128);
+        }
+    }
+    // Otherwise four columns per warp, eight lanes per column, X in shared memory.
+    const uint32_t threads = 256u, cols_per_cta = threads / 8;
+    const dim3 grid((w.N + cols_per_cta - 1) / cols_per_cta, (a.M + mt - 1) / mt, 1);
     switch (mt) {
         case 1: return launch_generic<k_i2s<1>>(prm, grid, smem, pdl, st, threads);
         case 2: return launch_generic<k_i2s<2>>(prm, grid, smem, pdl, st, threads);

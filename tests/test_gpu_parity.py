@@ -545,12 +545,28 @@ def test_launch_errors():
 
 # ---------------------------------------------------------------- comparators
 
-@pytest.mark.parametrize("K,N,M", [(64, 16, 1), (6912, 2560, 1), (6912, 2560, 4), (2560, 6912, 8), (1040, 50, 3)])
+@pytest.mark.parametrize("K,N,M", [(64, 16, 1), (6912, 2560, 1), (6912, 2560, 4), (2560, 6912, 8), (1040, 50, 3),
+                                   (2560, 3840, 1), (4096, 777, 1), (8192, 3000, 1), (1040, 50, 1), (10240, 96, 1), (6144, 5, 1)])
 def test_i2s_comparator(K, N, M):
+    """One row with K a multiple of 64 up to 8192 takes the register form of the kernel (one to four
+    16-byte vectors of codes per lane and column); everything else the shared-memory form."""
     W = sp.gen_ternary_iid(K, N, 1 / 3, 0)
     X = O.gen_x_i8(M * K, 1)
     w = sp.Weights(W, sp.FMT_I2S).upload()
     assert (run_i8(w, X, M).reshape(M, N) == O.gemv_i8_dense(X, W)).all()
+
+
+def test_i2s_comparator_with_activations_off_a_16_byte_boundary():
+    K, N = 2560, 300
+    W = sp.gen_ternary_iid(K, N, 0.5, 5)
+    X = O.gen_x_i8(K, 6)
+    w = sp.Weights(W, sp.FMT_I2S).upload()
+    buf = torch.zeros(K + 16, dtype=torch.int8, device="cuda")
+    buf[4:4 + K] = torch.from_numpy(X).cuda()
+    out = torch.zeros(N, dtype=torch.int32, device="cuda")
+    w.gemv(buf[4:4 + K], 1, out)                      # 4 bytes off: the register form needs 16-byte loads of X
+    torch.cuda.synchronize()
+    assert (out.cpu().numpy() == O.gemv_i8_dense(X, W).reshape(-1)).all()
 
 
 def test_cublas_comparator():
