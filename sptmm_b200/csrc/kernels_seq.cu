@@ -1108,7 +1108,9 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
             for (uint32_t t = 0; t < p.nsteps; t++) {
                 const uint32_t b = t & 1;
                 if (t >= 2) {            // the buffer's previous tile must have been gathered
-                    if (!seq_bounded_wait(free_a + 8 * b, free_phase[b]) && !failed) { failed = 1; atomicOr(p.status, 4u); }
+                    // (after a failure nothing waits any more: the consumers stop waiting for their tiles
+                    // too, so the two sides' phases no longer line up and a wait here would only run out)
+                    if (!failed && !seq_bounded_wait(free_a + 8 * b, free_phase[b])) { failed = 1; atomicOr(p.status, 4u); }
                     free_phase[b] ^= 1;
                 }
                 settle_ahead<MT>(xs + (size_t)b * p.xs_bytes, ready_a + 8 * b, p.desc[t], p, t, st, settle_rowmax_s, settle_scale_s,

@@ -99,10 +99,12 @@ class TernaryStack:
 
     def __init__(self, layers=30, hidden=2560, ffn=6912, kv=640, M=1, p_zero=1 / 3, seed=0,
                  rank=0, world=1, group=None, keep_dense=False, tagged=None, row_maxima=False, producer_quant=None,
-                 settled=None, weights=None, exchange=None):
+                 settled=None, weights=None, exchange=None, arena_peers=None):
         """weights: a StackWeights built for the same shapes, rank and world (else one is built here).
-        exchange: one of AUTO, COUNTERS, TAGGED, ROW_MAXIMA, PRODUCER_QUANT, SETTLED; the boolean
-        arguments are the older way of naming the same choice."""
+        exchange: one of AUTO, COUNTERS, TAGGED, ROW_MAXIMA, PRODUCER_QUANT, SETTLED, SETTLED_HALVES;
+        the boolean arguments are the older way of naming the same choice.  arena_peers: addresses of
+        every rank's zeroed arena (arena_bytes() each) for a caller that has mapped them itself; by
+        default they come from torch's symmetric memory."""
         import torch
         self.torch = torch
         self.layers, self.hidden, self.ffn, self.kv, self.M = layers, hidden, ffn, kv, M
@@ -129,7 +131,12 @@ class TernaryStack:
         if nbytes == 0:
             raise sp.SptmmError(-1, "sptmm_stack_arena_bytes: " + sp.lib.sptmm_last_error().decode("utf-8", "replace"))
         h = C.c_void_p()
-        if world > 1:
+        self.arena_bytes = nbytes
+        if arena_peers is not None:
+            self.arena = None
+            bases = (C.c_void_p * world)(*[int(p) for p in arena_peers])
+            sp.check(sp.lib.sptmm_stack_create(weights._h, M, exchange, bases, C.byref(h)))
+        elif world > 1:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm
             self.arena = symm.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
