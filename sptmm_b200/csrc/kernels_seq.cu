@@ -1122,6 +1122,7 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
 
     // ================= consumer warps =================
     // the first threads carry one word each of a step's descriptor, threads 64..67 its plan entries
+    static_assert(sizeof(SeqDesc) % 4 == 0 && sizeof(SeqDesc) / 4 <= 64, "a descriptor travels in the first 64 threads");
     auto load_step_word = [&](uint32_t st) -> uint32_t {
         if (tid < sizeof(SeqDesc) / 4) return __ldg(reinterpret_cast<const uint32_t *>(p.desc + st) + tid);
         if (tid >= 64 && tid < 68) {
