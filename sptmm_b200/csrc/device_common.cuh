@@ -187,6 +187,36 @@ struct LaneAcc<SPTMM_I8, MT, true> {
 };
 
 __device__ __forceinline__ int32_t warp_sum(int32_t v) { return __reduce_add_sync(0xffffffffu, v); }
+
+// Integer sums of finished lists on their way to the CTA's column sums in shared memory.  Adding a
+// list's MT sums one by one (reduce over the warp, lane 0 adds, next row) is a chain of dependent
+// steps that costs more than gathering a block; here the MT reductions of a list are independent
+// instructions, each result is parked in one lane's register (MT lanes per list), and when all 32
+// lanes are taken -- or the warp runs out of lists -- ONE atomic instruction adds them all.
+template <int MT>
+struct PendingSums {
+    static constexpr uint32_t kLists = 32 / MT;
+    int keep;
+    uint32_t at, pend;
+    __device__ __forceinline__ void clear() { keep = 0; at = 0; pend = 0; }
+    __device__ __forceinline__ void drain(int *c_s, uint32_t lane)
+    {
+        if (lane < pend * MT) atomicAdd(c_s + at, keep);
+        pend = 0;
+    }
+    // every lane calls this with its partial sums of the list that just ended; v is zeroed
+    __device__ __forceinline__ void push(int32_t (&v)[MT], uint32_t col, bool negative, int *c_s, uint32_t lane)
+    {
+        const uint32_t first = pend * MT;
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            const int s = __reduce_add_sync(0xffffffffu, v[m]);
+            if (lane == first + m) { keep = negative ? -s : s; at = col * MT + m; }
+            v[m] = 0;
+        }
+        if (++pend == kLists) drain(c_s, lane);
+    }
+};
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll

@@ -266,20 +266,22 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
         acc.clear(p.one);
         bool dirty = false;
 
+        [[maybe_unused]] PendingSums<MT> done;          // integer sums only (see device_common.cuh)
+        done.clear();
         auto flush = [&]() {
             const uint32_t col = li >> 1;
             acc.finish();
+            if constexpr (kInt) {
+                done.push(acc.v, col, (li & 1) != 0, reinterpret_cast<int *>(c_s), lane);
+            } else {
 #pragma unroll
-            for (int m = 0; m < MT; m++) {
-                acc_t v = warp_sum(acc.v[m]);
-                v = (li & 1) ? -v : v;
-                if constexpr (kInt) {
-                    if (lane == 0) atomicAdd(reinterpret_cast<int *>(c_s) + col * MT + m, (int)v);
-                } else {
+                for (int m = 0; m < MT; m++) {
+                    acc_t v = warp_sum(acc.v[m]);
+                    v = (li & 1) ? -v : v;
                     acc_t *dst = col == first_col ? head_s + warp * MT : (col == last_col ? tail_s + warp * MT : c_s + col * MT);
                     if (lane == 0) dst[m] += v;
+                    acc.v[m] = acc_t(0);
                 }
-                acc.v[m] = acc_t(0);
             }
         };
         auto consume = [&](const uint4 v, const uint32_t b) {
@@ -437,6 +439,7 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
         // in mapped host memory, where atomics are not available on every platform)
         if (!ok && lane == 0 && p.status) *reinterpret_cast<volatile uint32_t *>(p.status) = 1u;
         if (dirty) flush();
+        if constexpr (kInt) done.drain(reinterpret_cast<int *>(c_s), lane);
     } else if (!kInt && lane == 0) {
         hcol_s[warp] = 0xffffffffu; tcol_s[warp] = 0xffffffffu;
     }

@@ -1255,15 +1255,11 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
             LaneAcc<SPTMM_I8, MT> acc;
             acc.clear(p.one, xoff);
             bool dirty = false;
+            PendingSums<MT> done;
+            done.clear();
             auto flush = [&]() {
-                const uint32_t col = li >> 1;
                 acc.finish();
-#pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    int v = __reduce_add_sync(0xffffffffu, acc.v[m]);
-                    if (lane == 0) atomicAdd(c_s + col * MT + m, (li & 1) ? -v : v);
-                    acc.v[m] = 0;
-                }
+                done.push(acc.v, li >> 1, (li & 1) != 0, c_s, lane);
             };
             auto gather8 = [&](const uint4 v) {
                 acc.reserve(8);
@@ -1335,6 +1331,7 @@ __global__ void __launch_bounds__(XV == 3 ? kPipeThreads : kConsumerThreads + 32
             }
             if (!ring_ok && lane == 0) { failed = 1; atomicOr(p.status, 1u); }
             if (dirty) flush();
+            done.drain(c_s, lane);
 #ifdef SPTMM_TUNING
             if (wtr) {
                 unsigned long long *o = p.trace + 8192 + ((((cta != 0) * 4u + (s - 100)) * 16u + warp) * 4u);
