@@ -188,35 +188,66 @@ struct LaneAcc<SPTMM_I8, MT, true> {
 
 __device__ __forceinline__ int32_t warp_sum(int32_t v) { return __reduce_add_sync(0xffffffffu, v); }
 
+// Sum N values per lane over the 32 lanes of a warp so that the lanes end up holding DIFFERENT
+// sums: each round exchanges half of the values with the lane `off` away and keeps the other half
+// (a transposing butterfly: N/2 + N/4 + ... shuffles instead of N full reductions).  On return
+// lane l holds the sum of value l / (32/N).
+template <int N>
+struct TransposeSum {
+    static __device__ __forceinline__ int run(const int (&v)[N], uint32_t lane, uint32_t off)
+    {
+        int w[N / 2];
+        const bool up = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < N / 2; i++) {
+            const int send = up ? v[i] : v[i + N / 2];
+            const int mine = up ? v[i + N / 2] : v[i];
+            w[i] = mine + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+        return TransposeSum<N / 2>::run(w, lane, off >> 1);
+    }
+};
+template <>
+struct TransposeSum<1> {
+    static __device__ __forceinline__ int run(const int (&v)[1], uint32_t, uint32_t off)
+    {
+        int s = v[0];
+        for (uint32_t o = off; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        return s;
+    }
+};
+
 // Integer sums of finished lists on their way to the CTA's column sums in shared memory.  Adding a
 // list's MT sums one by one (reduce over the warp, lane 0 adds, next row) is a chain of dependent
-// steps that costs more than gathering a block; here the MT reductions of a list are independent
-// instructions, each result is parked in one lane's register (MT lanes per list), and when all 32
-// lanes are taken -- or the warp runs out of lists -- ONE atomic instruction adds them all.
+// steps that costs more than gathering a block; and MT full warp reductions keep the reduction unit
+// busy for longer than the gathers of a short list take.  Here a list's sums are reduced by the
+// transposing butterfly above (lane l ends with row l / (32/MT)), one lane per row parks its sum in
+// a register, and when every lane is taken -- or the warp runs out of lists -- ONE atomic
+// instruction adds up to 32 sums to their columns.
 template <int MT>
 struct PendingSums {
-    static constexpr uint32_t kLists = 32 / MT;
+    static constexpr uint32_t kLists = 32 / MT;      // lists that fit the warp's lanes; also the lanes per row
     int keep;
     uint32_t at, pend;
     __device__ __forceinline__ void clear() { keep = 0; at = 0; pend = 0; }
     __device__ __forceinline__ void drain(int *c_s, uint32_t lane)
     {
-        if (lane < pend * MT) atomicAdd(c_s + at, keep);
+        if ((lane & (kLists - 1)) < pend) atomicAdd(c_s + at, keep);
         pend = 0;
     }
     // every lane calls this with its partial sums of the list that just ended; v is zeroed
     __device__ __forceinline__ void push(int32_t (&v)[MT], uint32_t col, bool negative, int *c_s, uint32_t lane)
     {
-        const uint32_t first = pend * MT;
+        int s;
+        if constexpr (MT == 1) s = __reduce_add_sync(0xffffffffu, v[0]);
+        else s = TransposeSum<MT>::run(v, lane, 16);
+        if ((lane & (kLists - 1)) == pend) { keep = negative ? -s : s; at = col * MT + lane / kLists; }
 #pragma unroll
-        for (int m = 0; m < MT; m++) {
-            const int s = __reduce_add_sync(0xffffffffu, v[m]);
-            if (lane == first + m) { keep = negative ? -s : s; at = col * MT + m; }
-            v[m] = 0;
-        }
+        for (int m = 0; m < MT; m++) v[m] = 0;
         if (++pend == kLists) drain(c_s, lane);
     }
 };
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll
