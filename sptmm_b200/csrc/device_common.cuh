@@ -192,26 +192,26 @@ __device__ __forceinline__ int32_t warp_sum(int32_t v) { return __reduce_add_syn
 // sums: each round exchanges half of the values with the lane `off` away and keeps the other half
 // (a transposing butterfly: N/2 + N/4 + ... shuffles instead of N full reductions).  On return
 // lane l holds the sum of value l / (32/N).
-template <int N>
+template <typename T, int N>
 struct TransposeSum {
-    static __device__ __forceinline__ int run(const int (&v)[N], uint32_t lane, uint32_t off)
+    static __device__ __forceinline__ T run(const T (&v)[N], uint32_t lane, uint32_t off)
     {
-        int w[N / 2];
+        T w[N / 2];
         const bool up = (lane & off) != 0;
 #pragma unroll
         for (int i = 0; i < N / 2; i++) {
-            const int send = up ? v[i] : v[i + N / 2];
-            const int mine = up ? v[i + N / 2] : v[i];
+            const T send = up ? v[i] : v[i + N / 2];
+            const T mine = up ? v[i + N / 2] : v[i];
             w[i] = mine + __shfl_xor_sync(0xffffffffu, send, off);
         }
-        return TransposeSum<N / 2>::run(w, lane, off >> 1);
+        return TransposeSum<T, N / 2>::run(w, lane, off >> 1);
     }
 };
-template <>
-struct TransposeSum<1> {
-    static __device__ __forceinline__ int run(const int (&v)[1], uint32_t, uint32_t off)
+template <typename T>
+struct TransposeSum<T, 1> {
+    static __device__ __forceinline__ T run(const T (&v)[1], uint32_t, uint32_t off)
     {
-        int s = v[0];
+        T s = v[0];
         for (uint32_t o = off; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         return s;
     }
@@ -240,7 +240,7 @@ struct PendingSums {
     {
         int s;
         if constexpr (MT == 1) s = __reduce_add_sync(0xffffffffu, v[0]);
-        else s = TransposeSum<MT>::run(v, lane, 16);
+        else s = TransposeSum<int, MT>::run(v, lane, 16);
         if ((lane & (kLists - 1)) == pend) { keep = negative ? -s : s; at = col * MT + lane / kLists; }
 #pragma unroll
         for (int m = 0; m < MT; m++) v[m] = 0;

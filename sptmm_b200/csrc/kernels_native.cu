@@ -274,14 +274,15 @@ __global__ void __launch_bounds__(512, MINB) k_u16_v256(const __grid_constant__ 
             if constexpr (kInt) {
                 done.push(acc.v, col, (li & 1) != 0, reinterpret_cast<int *>(c_s), lane);
             } else {
+                // floats: the same butterfly (a fixed order of additions, so results repeat from run to
+                // run); lane l ends with row l / (32/MT), and one lane per row adds it where it belongs
+                constexpr uint32_t G = 32 / MT;
+                acc_t sum = TransposeSum<acc_t, MT>::run(acc.v, lane, 16);
+                sum = (li & 1) ? -sum : sum;
+                acc_t *dst = col == first_col ? head_s + warp * MT : (col == last_col ? tail_s + warp * MT : c_s + col * MT);
+                if ((lane & (G - 1)) == 0) dst[lane / G] += sum;
 #pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    acc_t v = warp_sum(acc.v[m]);
-                    v = (li & 1) ? -v : v;
-                    acc_t *dst = col == first_col ? head_s + warp * MT : (col == last_col ? tail_s + warp * MT : c_s + col * MT);
-                    if (lane == 0) dst[m] += v;
-                    acc.v[m] = acc_t(0);
-                }
+                for (int m = 0; m < MT; m++) acc.v[m] = acc_t(0);
             }
         };
         auto consume = [&](const uint4 v, const uint32_t b) {
